@@ -1,0 +1,23 @@
+"""B200-native INT8 W8A8 linear layer (drop-in for fish-audio-cpp's kernel boundary).
+
+The product is the CUDA library ``lib/libw8a8.so`` (C ABI in ``include/w8a8.h``); this
+package is its thin host-side binding plus the seeded synthetic workloads the tests and the
+benchmark share. There is no CPU or PyTorch fallback: without the built library every call
+raises.
+"""
+from .capi import (  # noqa: F401
+    ACT_PER_TOKEN,
+    ACT_PER_TOKEN_GROUP,
+    EPI_NONE,
+    EPI_RESIDUAL,
+    EPI_SWIGLU,
+    KERNEL_AUTO,
+    KERNEL_GEMM,
+    KERNEL_GEMV,
+    KERNEL_GENERIC,
+    Context,
+    W8A8Error,
+    library_path,
+    load_library,
+    num_groups,
+)

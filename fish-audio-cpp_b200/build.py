@@ -1,0 +1,82 @@
+"""Builds libw8a8.so in-tree with nvcc for sm_100a.
+
+Every .cu under csrc/ is compiled to an object in _build/ (only when it or a header is
+newer than the object) and linked into lib/libw8a8.so. No JIT cache is involved, so the
+built library travels with the source tree.
+"""
+from __future__ import annotations
+
+import os
+import shutil
+import subprocess
+import sys
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+HERE = Path(__file__).resolve().parent
+CSRC = HERE / "csrc"
+OBJ = HERE / "_build"
+LIB = HERE / "lib" / "libw8a8.so"
+INCLUDE = HERE.parent / "include"
+
+ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
+NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
+              "--expt-relaxed-constexpr", "-DW8A8_BUILDING"]
+
+
+def nvcc() -> str:
+    cand = os.environ.get("NVCC") or shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not Path(cand).exists():
+        raise RuntimeError("nvcc not found; set NVCC")
+    return cand
+
+
+def _newest_header() -> float:
+    hs = list(CSRC.glob("*.h")) + list(CSRC.glob("*.cuh")) + list(INCLUDE.glob("*.h"))
+    return max(h.stat().st_mtime for h in hs)
+
+
+def sources() -> list[Path]:
+    return sorted(CSRC.glob("*.cu"))
+
+
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
+    OBJ.mkdir(exist_ok=True)
+    LIB.parent.mkdir(exist_ok=True)
+    hdr = _newest_header()
+    defines = []
+    if (CSRC / "w8a8_gemm_sm100.cu").exists():
+        defines.append("-DW8A8_HAVE_GEMM_SM100")
+    jobs = []
+    for src in sources():
+        obj = OBJ / (src.stem + ".o")
+        stale = force or not obj.exists() or obj.stat().st_mtime < max(src.stat().st_mtime, hdr)
+        if stale:
+            cmd = [nvcc(), *ARCH, *NVCC_FLAGS, *defines, "-c", str(src), "-o", str(obj)]
+            if ptxas_info:
+                cmd[1:1] = ["-Xptxas", "-v"]
+            jobs.append((src, cmd))
+
+    def run(job):
+        src, cmd = job
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        return src, r
+
+    with ThreadPoolExecutor(max_workers=min(8, max(1, len(jobs)))) as ex:
+        for src, r in ex.map(run, jobs):
+            if verbose or r.returncode != 0 or ptxas_info:
+                sys.stderr.write(f"[nvcc] {src.name}\n{r.stdout}{r.stderr}")
+            if r.returncode != 0:
+                raise RuntimeError(f"nvcc failed on {src.name}")
+    objs = [str(OBJ / (s.stem + ".o")) for s in sources()]
+    if jobs or not LIB.exists():
+        cmd = [nvcc(), *ARCH, "-shared", "-o", str(LIB), *objs, "-cudart", "static"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            sys.stderr.write(r.stdout + r.stderr)
+            raise RuntimeError("link failed")
+    return LIB
+
+
+if __name__ == "__main__":
+    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, ptxas_info="--ptxas" in sys.argv))

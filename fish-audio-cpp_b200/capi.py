@@ -1,0 +1,192 @@
+"""ctypes binding of include/w8a8.h. Pointers are plain integers (``tensor.data_ptr()``)."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+ACT_PER_TOKEN_GROUP, ACT_PER_TOKEN = 0, 1
+EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_GEMV, KERNEL_GEMM = 0, 1, 2, 3
+
+_LIB = None
+
+
+class W8A8Error(RuntimeError):
+    def __init__(self, status: int, where: str, message: str):
+        super().__init__(f"{where}: status {status}: {message}")
+        self.status = status
+
+
+class LinearOpts(C.Structure):
+    _fields_ = [
+        ("act_mode", C.c_int),
+        ("epilogue", C.c_int),
+        ("residual", C.c_void_p),
+        ("dump_group_sums", C.c_void_p),
+        ("kernel", C.c_int),
+        ("split_k", C.c_int),
+    ]
+
+
+def library_path() -> Path:
+    return Path(__file__).resolve().parent / "lib" / "libw8a8.so"
+
+
+def load_library() -> C.CDLL:
+    """Loads libw8a8.so; raises if it has not been built (there is no fallback path)."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not path.exists():
+        raise W8A8Error(-1, "load_library", f"{path} is missing: run __graft_entry__.build() first")
+    lib = C.CDLL(str(path))
+    P, I, L, Z, F = C.c_void_p, C.c_int, C.c_long, C.c_size_t, C.c_float
+    sigs = {
+        "w8a8_status_string": (C.c_char_p, [I]),
+        "w8a8_last_error": (C.c_char_p, []),
+        "w8a8_create": (I, [C.POINTER(P), I, Z]),
+        "w8a8_destroy": (I, [P]),
+        "w8a8_workspace_bytes": (Z, [I, I, I, I]),
+        "w8a8_ctx_workspace_bytes": (Z, [P]),
+        "w8a8_check_device_status": (I, [P, P]),
+        "w8a8_quantize": (I, [P, P, P, P, I, I, I, I, P, P, P]),
+        "w8a8_rms_norm": (I, [P, P, P, P, I, I, F, P]),
+        "w8a8_rmsnorm_quantize": (I, [P, P, P, P, F, P, P, I, I, I, I, P, P, P, P]),
+        "w8a8_silu": (I, [P, P, L, P]),
+        "w8a8_mul": (I, [P, P, P, L, P]),
+        "w8a8_residual_add": (I, [P, P, P, L, P]),
+        "w8a8_linear": (I, [P, P, P, I, P, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
+        "w8a8_linear_q": (I, [P, P, P, I, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
+        "w8a8_pack_gate_up": (I, [P, P, P, P, P, I, I, I, P, P, P]),
+        "fish_shim_int8_dequant_gemm_fp16": (I, [P, P, I, P, P, P, P, I, I, I, P, C.c_char_p, I]),
+    }
+    for name, (res, args) in sigs.items():
+        fn = getattr(lib, name)
+        fn.restype, fn.argtypes = res, args
+    _LIB = lib
+    return lib
+
+
+EXPORTS = [
+    "w8a8_status_string", "w8a8_last_error", "w8a8_create", "w8a8_destroy", "w8a8_workspace_bytes",
+    "w8a8_ctx_workspace_bytes", "w8a8_check_device_status", "w8a8_quantize", "w8a8_rms_norm",
+    "w8a8_rmsnorm_quantize", "w8a8_silu", "w8a8_mul", "w8a8_residual_add", "w8a8_linear", "w8a8_linear_q",
+    "w8a8_pack_gate_up",
+]
+
+
+def num_groups(K: int, group_size: int) -> int:
+    g = K if group_size <= 0 or group_size > K else group_size
+    return (K + g - 1) // g
+
+
+def _ptr(x) -> int | None:
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return x
+    return x.data_ptr()
+
+
+def _stream(stream) -> int | None:
+    if stream is None:
+        import torch
+
+        return torch.cuda.current_stream().cuda_stream or None
+    return stream or None
+
+
+class Context:
+    """Owns one w8a8_ctx. Use one per stream."""
+
+    def __init__(self, device: int = 0, workspace_bytes: int = 0):
+        self.lib = load_library()
+        h = C.c_void_p()
+        self._check(self.lib.w8a8_create(C.byref(h), device, workspace_bytes), "w8a8_create")
+        self.handle = h
+        self.device = device
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.w8a8_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def _check(self, status: int, where: str):
+        if status != 0:
+            raise W8A8Error(status, where, self.lib.w8a8_last_error().decode())
+
+    @property
+    def workspace_bytes(self) -> int:
+        return self.lib.w8a8_ctx_workspace_bytes(self.handle)
+
+    def check_device_status(self, stream=None):
+        self._check(self.lib.w8a8_check_device_status(self.handle, _stream(stream)), "w8a8_check_device_status")
+
+    def quantize(self, X, M, K, group_size, Xq, Xs, smooth_inv=None, act_scale=None,
+                 act_mode=ACT_PER_TOKEN_GROUP, stream=None):
+        self._check(self.lib.w8a8_quantize(self.handle, _ptr(X), _ptr(smooth_inv), _ptr(act_scale), M, K,
+                                           group_size, act_mode, _ptr(Xq), _ptr(Xs), _stream(stream)),
+                    "w8a8_quantize")
+
+    def rms_norm(self, x, weight, out, tokens, dim, eps, stream=None):
+        self._check(self.lib.w8a8_rms_norm(self.handle, _ptr(x), _ptr(weight), _ptr(out), tokens, dim, eps,
+                                           _stream(stream)), "w8a8_rms_norm")
+
+    def rmsnorm_quantize(self, x, weight, eps, M, K, group_size, Xq, Xs, residual=None, smooth_inv=None,
+                         act_scale=None, act_mode=ACT_PER_TOKEN_GROUP, normed_out=None, stream=None):
+        self._check(self.lib.w8a8_rmsnorm_quantize(self.handle, _ptr(x), _ptr(residual), _ptr(weight), eps,
+                                                   _ptr(smooth_inv), _ptr(act_scale), M, K, group_size, act_mode,
+                                                   _ptr(normed_out), _ptr(Xq), _ptr(Xs), _stream(stream)),
+                    "w8a8_rmsnorm_quantize")
+
+    def silu(self, a, n, stream=None):
+        self._check(self.lib.w8a8_silu(self.handle, _ptr(a), n, _stream(stream)), "w8a8_silu")
+
+    def mul(self, a, b, n, stream=None):
+        self._check(self.lib.w8a8_mul(self.handle, _ptr(a), _ptr(b), n, _stream(stream)), "w8a8_mul")
+
+    def residual_add(self, a, b, n, stream=None):
+        self._check(self.lib.w8a8_residual_add(self.handle, _ptr(a), _ptr(b), n, _stream(stream)),
+                    "w8a8_residual_add")
+
+    @staticmethod
+    def _opts(act_mode, epilogue, residual, dump, kernel, split_k):
+        if (act_mode, epilogue, residual, dump, kernel, split_k) == (0, 0, None, None, 0, 0):
+            return None
+        return C.byref(LinearOpts(act_mode, epilogue, _ptr(residual), _ptr(dump), kernel, split_k))
+
+    def linear(self, W, w_scale, group_size, X, Y, M, N, K, act_scale=None, smooth_inv=None,
+               act_mode=ACT_PER_TOKEN_GROUP, epilogue=EPI_NONE, residual=None, dump=None, kernel=KERNEL_AUTO,
+               split_k=0, stream=None):
+        self._check(self.lib.w8a8_linear(self.handle, _ptr(W), _ptr(w_scale), group_size, _ptr(act_scale),
+                                         _ptr(smooth_inv), _ptr(X), _ptr(Y), M, N, K,
+                                         self._opts(act_mode, epilogue, residual, dump, kernel, split_k),
+                                         _stream(stream)), "w8a8_linear")
+
+    def linear_q(self, W, w_scale, group_size, Xq, Xs, Y, M, N, K, epilogue=EPI_NONE, residual=None, dump=None,
+                 kernel=KERNEL_AUTO, split_k=0, stream=None):
+        self._check(self.lib.w8a8_linear_q(self.handle, _ptr(W), _ptr(w_scale), group_size, _ptr(Xq), _ptr(Xs),
+                                           _ptr(Y), M, N, K, self._opts(0, epilogue, residual, dump, kernel, split_k),
+                                           _stream(stream)), "w8a8_linear_q")
+
+    def pack_gate_up(self, w_gate, s_gate, w_up, s_up, inter, K, G, W_out, scale_out, stream=None):
+        self._check(self.lib.w8a8_pack_gate_up(self.handle, _ptr(w_gate), _ptr(s_gate), _ptr(w_up), _ptr(s_up),
+                                               inter, K, G, _ptr(W_out), _ptr(scale_out), _stream(stream)),
+                    "w8a8_pack_gate_up")
+
+    def shim_int8_dequant_gemm_fp16(self, W, scale, group_size, act_scale, smooth_inv, X, Y, M_out, N_tok, K,
+                                    stream=None):
+        """Drives the C++ entry point with the reference's own signature and argument order."""
+        buf = C.create_string_buffer(512)
+        rc = self.lib.fish_shim_int8_dequant_gemm_fp16(_ptr(W), _ptr(scale), group_size, _ptr(act_scale),
+                                                       _ptr(smooth_inv), _ptr(X), _ptr(Y), M_out, N_tok, K,
+                                                       _stream(stream), buf, 512)
+        if rc:
+            raise RuntimeError(buf.value.decode())

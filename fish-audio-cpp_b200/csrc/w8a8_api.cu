@@ -1,0 +1,302 @@
+// C ABI of libw8a8 (see include/w8a8.h): argument checks, kernel choice, scratch layout.
+#include <cstdarg>
+#include <cstdio>
+#include <new>
+
+#include "w8a8_internal.h"
+
+struct w8a8_ctx {
+    int device = 0;
+    unsigned char* workspace = nullptr;
+    size_t workspace_bytes = 0;
+    int* device_status = nullptr;  // set by kernels whose bounded waits run out
+};
+
+namespace w8a8 {
+
+static thread_local char g_error[512] = "";
+
+int fail(int status, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof g_error, fmt, ap);
+    va_end(ap);
+    return status;
+}
+
+int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+    return W8A8_OK;
+}
+
+static inline size_t align256(size_t x) { return (x + 255) & ~size_t(255); }
+
+static size_t quant_scratch_bytes(int M, int K, int group_size) {
+    return align256(static_cast<size_t>(M) * K) + align256(static_cast<size_t>(M) * num_groups(K, group_size) * 4);
+}
+
+#if !defined(W8A8_HAVE_GEMM_SM100)
+bool gemm_supports(const LinearArgs&) { return false; }
+int launch_linear_gemm(const LinearArgs&, int*, cudaStream_t) {
+    return fail(W8A8_ERR_UNSUPPORTED, "tcgen05 GEMM not built into this library");
+}
+#endif
+
+static int check_linear_common(const w8a8_ctx* ctx, const void* W, const void* w_scale, const void* Y,
+                               int M, int N, int K, const w8a8_linear_opts* o) {
+    if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
+    if (M < 0 || N <= 0 || K <= 0) return fail(W8A8_ERR_INVALID_ARG, "bad shape M=%d N=%d K=%d", M, N, K);
+    if (!W || !w_scale || (!Y && M > 0)) return fail(W8A8_ERR_INVALID_ARG, "null W, w_scale or Y");
+    if (o) {
+        if (o->epilogue < W8A8_EPI_NONE || o->epilogue > W8A8_EPI_SWIGLU)
+            return fail(W8A8_ERR_INVALID_ARG, "unknown epilogue %d", o->epilogue);
+        if (o->epilogue == W8A8_EPI_RESIDUAL && !o->residual)
+            return fail(W8A8_ERR_INVALID_ARG, "W8A8_EPI_RESIDUAL needs opts->residual");
+        if (o->epilogue == W8A8_EPI_SWIGLU && N % 16 != 0)
+            return fail(W8A8_ERR_INVALID_ARG, "W8A8_EPI_SWIGLU needs N %% 16 == 0 (got %d)", N);
+        if (o->act_mode != W8A8_ACT_PER_TOKEN_GROUP && o->act_mode != W8A8_ACT_PER_TOKEN)
+            return fail(W8A8_ERR_INVALID_ARG, "unknown act_mode %d", o->act_mode);
+        if (o->kernel < W8A8_KERNEL_AUTO || o->kernel > W8A8_KERNEL_GEMM)
+            return fail(W8A8_ERR_INVALID_ARG, "unknown kernel %d", o->kernel);
+    }
+    return W8A8_OK;
+}
+
+static LinearArgs make_args(const void* W, const void* w_scale, int group_size, void* Y, int M, int N, int K,
+                            const w8a8_linear_opts* o) {
+    LinearArgs a = {};
+    a.W = static_cast<const int8_t*>(W);
+    a.w_scale = static_cast<const __half*>(w_scale);
+    a.Y = static_cast<__half*>(Y);
+    a.M = M;
+    a.N = N;
+    a.K = K;
+    a.g = norm_group(K, group_size);
+    a.G = num_groups(K, group_size);
+    a.epilogue = o ? o->epilogue : W8A8_EPI_NONE;
+    a.residual = o ? static_cast<const __half*>(o->residual) : nullptr;
+    a.dump = o ? o->dump_group_sums : nullptr;
+    a.split_k = o ? o->split_k : 0;
+    return a;
+}
+
+// Runs a linear whose codes and scales exist.
+static int dispatch_q(w8a8_ctx* ctx, const LinearArgs& a, int kernel, cudaStream_t s) {
+    if (a.M == 0) return W8A8_OK;
+    switch (kernel) {
+        case W8A8_KERNEL_GENERIC: return launch_linear_generic(a, s);
+        case W8A8_KERNEL_GEMV: return launch_linear_gemv(a, s);
+        case W8A8_KERNEL_GEMM: return launch_linear_gemm(a, ctx->device_status, s);
+        default: break;
+    }
+    if (a.M <= 32 && gemv_supports(a)) return launch_linear_gemv(a, s);
+    if (gemm_supports(a)) return launch_linear_gemm(a, ctx->device_status, s);
+    return launch_linear_generic(a, s);
+}
+
+}  // namespace w8a8
+
+using namespace w8a8;
+
+extern "C" {
+
+const char* w8a8_status_string(int status) {
+    switch (status) {
+        case W8A8_OK: return "ok";
+        case W8A8_ERR_INVALID_ARG: return "invalid argument";
+        case W8A8_ERR_UNSUPPORTED: return "unsupported shape";
+        case W8A8_ERR_CUDA: return "CUDA error";
+        case W8A8_ERR_TIMEOUT: return "device-side wait timed out";
+        case W8A8_ERR_WORKSPACE: return "context workspace too small";
+    }
+    return "unknown status";
+}
+
+const char* w8a8_last_error(void) { return g_error; }
+
+int w8a8_create(w8a8_ctx** out, int device, size_t workspace_bytes) {
+    if (!out) return fail(W8A8_ERR_INVALID_ARG, "null out");
+    *out = nullptr;
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) {
+        cudaGetLastError();
+        return fail(W8A8_ERR_CUDA, "no CUDA device: %s", cudaGetErrorString(e));
+    }
+    if (device < 0 || device >= count) return fail(W8A8_ERR_INVALID_ARG, "device %d of %d", device, count);
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, device);
+    if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    if (prop.major != 10)
+        return fail(W8A8_ERR_UNSUPPORTED, "built for sm_100a only; device %d is sm_%d%d", device, prop.major,
+                    prop.minor);
+    int prev = 0;
+    cudaGetDevice(&prev);
+    if ((e = cudaSetDevice(device)) != cudaSuccess)
+        return fail(W8A8_ERR_CUDA, "cudaSetDevice: %s", cudaGetErrorString(e));
+    w8a8_ctx* c = new (std::nothrow) w8a8_ctx;
+    if (!c) return fail(W8A8_ERR_CUDA, "out of host memory");
+    c->device = device;
+    if (workspace_bytes == 0) workspace_bytes = quant_scratch_bytes(8192, 9728, 64);
+    c->workspace_bytes = align256(workspace_bytes);
+    e = cudaMalloc(&c->workspace, c->workspace_bytes);
+    if (e == cudaSuccess) e = cudaMalloc(&c->device_status, sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(c->device_status, 0, sizeof(int));
+    cudaSetDevice(prev);
+    if (e != cudaSuccess) {
+        cudaFree(c->workspace);
+        cudaFree(c->device_status);
+        delete c;
+        return fail(W8A8_ERR_CUDA, "context allocation: %s", cudaGetErrorString(e));
+    }
+    *out = c;
+    return W8A8_OK;
+}
+
+int w8a8_destroy(w8a8_ctx* ctx) {
+    if (!ctx) return W8A8_OK;
+    cudaFree(ctx->workspace);
+    cudaFree(ctx->device_status);
+    delete ctx;
+    return W8A8_OK;
+}
+
+size_t w8a8_workspace_bytes(int M, int N, int K, int group_size) {
+    (void)N;
+    if (M <= 0 || K <= 0) return 0;
+    return quant_scratch_bytes(M, K, group_size);
+}
+
+size_t w8a8_ctx_workspace_bytes(const w8a8_ctx* ctx) { return ctx ? ctx->workspace_bytes : 0; }
+
+int w8a8_check_device_status(w8a8_ctx* ctx, void* stream) {
+    if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int host = 0;
+    cudaError_t e = cudaMemcpyAsync(&host, ctx->device_status, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "status read: %s", cudaGetErrorString(e));
+    if (host != 0) {
+        cudaMemsetAsync(ctx->device_status, 0, sizeof(int), s);
+        return fail(W8A8_ERR_TIMEOUT, "a kernel gave up a bounded wait (code %d)", host);
+    }
+    return W8A8_OK;
+}
+
+int w8a8_quantize(w8a8_ctx* ctx, const void* X, const void* smooth_inv, const void* act_scale, int M, int K,
+                  int group_size, int act_mode, void* Xq, void* Xs, void* stream) {
+    if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
+    if (M < 0 || K <= 0) return fail(W8A8_ERR_INVALID_ARG, "bad shape M=%d K=%d", M, K);
+    if (M > 0 && (!X || !Xq || !Xs)) return fail(W8A8_ERR_INVALID_ARG, "null X, Xq or Xs");
+    if (act_mode != W8A8_ACT_PER_TOKEN_GROUP && act_mode != W8A8_ACT_PER_TOKEN)
+        return fail(W8A8_ERR_INVALID_ARG, "unknown act_mode %d", act_mode);
+    return launch_rowquant(static_cast<const __half*>(X), nullptr, nullptr, nullptr, 0.0f,
+                           static_cast<const __half*>(smooth_inv), static_cast<const __half*>(act_scale), M, K,
+                           group_size, act_mode, nullptr, static_cast<int8_t*>(Xq), static_cast<float*>(Xs),
+                           static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_rms_norm(w8a8_ctx* ctx, const void* x, const void* weight, void* out, int tokens, int dim, float eps,
+                  void* stream) {
+    if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
+    if (tokens < 0 || dim <= 0) return fail(W8A8_ERR_INVALID_ARG, "bad shape tokens=%d dim=%d", tokens, dim);
+    if (tokens > 0 && (!x || !weight || !out)) return fail(W8A8_ERR_INVALID_ARG, "null x, weight or out");
+    return launch_rowquant(static_cast<const __half*>(x), nullptr, nullptr, static_cast<const __half*>(weight), eps,
+                           nullptr, nullptr, tokens, dim, dim, W8A8_ACT_PER_TOKEN_GROUP, static_cast<__half*>(out),
+                           nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_rmsnorm_quantize(w8a8_ctx* ctx, void* x, const void* residual, const void* weight, float eps,
+                          const void* smooth_inv, const void* act_scale, int M, int K, int group_size,
+                          int act_mode, void* normed_out, void* Xq, void* Xs, void* stream) {
+    if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
+    if (M < 0 || K <= 0) return fail(W8A8_ERR_INVALID_ARG, "bad shape M=%d K=%d", M, K);
+    if (M > 0 && (!x || !weight || !Xq || !Xs)) return fail(W8A8_ERR_INVALID_ARG, "null x, weight, Xq or Xs");
+    if (act_mode != W8A8_ACT_PER_TOKEN_GROUP && act_mode != W8A8_ACT_PER_TOKEN)
+        return fail(W8A8_ERR_INVALID_ARG, "unknown act_mode %d", act_mode);
+    return launch_rowquant(static_cast<const __half*>(x), static_cast<__half*>(x),
+                           static_cast<const __half*>(residual), static_cast<const __half*>(weight), eps,
+                           static_cast<const __half*>(smooth_inv), static_cast<const __half*>(act_scale), M, K,
+                           group_size, act_mode, static_cast<__half*>(normed_out), static_cast<int8_t*>(Xq),
+                           static_cast<float*>(Xs), static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_silu(w8a8_ctx* ctx, void* a, long n, void* stream) {
+    if (!ctx || (n > 0 && !a) || n < 0) return fail(W8A8_ERR_INVALID_ARG, "silu: bad arguments");
+    return launch_silu(static_cast<__half*>(a), n, static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_mul(w8a8_ctx* ctx, void* a, const void* b, long n, void* stream) {
+    if (!ctx || (n > 0 && (!a || !b)) || n < 0) return fail(W8A8_ERR_INVALID_ARG, "mul: bad arguments");
+    return launch_mul(static_cast<__half*>(a), static_cast<const __half*>(b), n, static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_residual_add(w8a8_ctx* ctx, void* a, const void* b, long n, void* stream) {
+    if (!ctx || (n > 0 && (!a || !b)) || n < 0) return fail(W8A8_ERR_INVALID_ARG, "residual_add: bad arguments");
+    return launch_residual_add(static_cast<__half*>(a), static_cast<const __half*>(b), n,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_linear_q(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size, const void* Xq,
+                  const void* Xs, void* Y, int M, int N, int K, const w8a8_linear_opts* opts, void* stream) {
+    int rc = check_linear_common(ctx, W, w_scale, Y, M, N, K, opts);
+    if (rc) return rc;
+    if (M > 0 && (!Xq || !Xs)) return fail(W8A8_ERR_INVALID_ARG, "null Xq or Xs");
+    LinearArgs a = make_args(W, w_scale, group_size, Y, M, N, K, opts);
+    a.Xq = static_cast<const int8_t*>(Xq);
+    a.Xs = static_cast<const float*>(Xs);
+    return dispatch_q(ctx, a, opts ? opts->kernel : W8A8_KERNEL_AUTO, static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_linear(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size, const void* act_scale,
+                const void* smooth_inv, const void* X, void* Y, int M, int N, int K,
+                const w8a8_linear_opts* opts, void* stream) {
+    int rc = check_linear_common(ctx, W, w_scale, Y, M, N, K, opts);
+    if (rc) return rc;
+    if (M > 0 && !X) return fail(W8A8_ERR_INVALID_ARG, "null X");
+    if (M == 0) return W8A8_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    LinearArgs a = make_args(W, w_scale, group_size, Y, M, N, K, opts);
+    const int act_mode = opts ? opts->act_mode : W8A8_ACT_PER_TOKEN_GROUP;
+    const int kernel = opts ? opts->kernel : W8A8_KERNEL_AUTO;
+
+    // Small M: one launch, the GEMV quantises its own K-slice.
+    if ((kernel == W8A8_KERNEL_AUTO || kernel == W8A8_KERNEL_GEMV) && M <= 32 &&
+        act_mode == W8A8_ACT_PER_TOKEN_GROUP) {
+        LinearArgs f = a;
+        f.X = static_cast<const __half*>(X);
+        f.smooth_inv = static_cast<const __half*>(smooth_inv);
+        f.act_scale = static_cast<const __half*>(act_scale);
+        if (gemv_supports(f)) return launch_linear_gemv(f, s);
+    }
+
+    // Otherwise: codes and scales into the context's scratch, then the integer kernel.
+    const size_t need = quant_scratch_bytes(M, K, group_size);
+    if (need > ctx->workspace_bytes)
+        return fail(W8A8_ERR_WORKSPACE, "need %zu bytes of scratch, context has %zu", need, ctx->workspace_bytes);
+    int8_t* Xq = reinterpret_cast<int8_t*>(ctx->workspace);
+    float* Xs = reinterpret_cast<float*>(ctx->workspace + align256(static_cast<size_t>(M) * K));
+    rc = launch_rowquant(static_cast<const __half*>(X), nullptr, nullptr, nullptr, 0.0f,
+                         static_cast<const __half*>(smooth_inv), static_cast<const __half*>(act_scale), M, K,
+                         group_size, act_mode, nullptr, Xq, Xs, s);
+    if (rc) return rc;
+    a.Xq = Xq;
+    a.Xs = Xs;
+    return dispatch_q(ctx, a, kernel, s);
+}
+
+int w8a8_pack_gate_up(w8a8_ctx* ctx, const void* w_gate, const void* s_gate, const void* w_up, const void* s_up,
+                      int inter, int K, int G, void* W_out, void* scale_out, void* stream) {
+    if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
+    if (inter < 0 || inter % 8 != 0 || K <= 0 || G <= 0)
+        return fail(W8A8_ERR_INVALID_ARG, "pack_gate_up: inter=%d (must be a multiple of 8) K=%d G=%d", inter, K, G);
+    if (inter > 0 && (!w_gate || !s_gate || !w_up || !s_up || !W_out || !scale_out))
+        return fail(W8A8_ERR_INVALID_ARG, "pack_gate_up: null pointer");
+    return launch_pack_gate_up(static_cast<const int8_t*>(w_gate), static_cast<const __half*>(s_gate),
+                               static_cast<const int8_t*>(w_up), static_cast<const __half*>(s_up), inter, K, G,
+                               static_cast<int8_t*>(W_out), static_cast<__half*>(scale_out),
+                               static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,63 @@
+// Internal declarations shared by the .cu files of libw8a8. Not installed.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstddef>
+#include <cstdint>
+
+#include "../../include/w8a8.h"
+
+namespace w8a8 {
+
+// Records a message for w8a8_last_error() and returns `status`.
+int fail(int status, const char* fmt, ...);
+// cudaGetLastError() after a launch -> status.
+int check_launch(const char* what);
+
+inline int norm_group(int K, int group_size) {
+    return (group_size <= 0 || group_size > K) ? K : group_size;
+}
+inline int num_groups(int K, int group_size) {
+    int g = norm_group(K, group_size);
+    return (K + g - 1) / g;
+}
+
+struct LinearArgs {
+    const int8_t* W;
+    const __half* w_scale;  // [N, G]
+    const int8_t* Xq;       // [M, K]   (null when X is given and the kernel quantises itself)
+    const float* Xs;        // [M, G]
+    const __half* X;        // [M, K]   fp16 source for kernels that quantise in their prologue
+    const __half* smooth_inv;
+    const __half* act_scale;
+    __half* Y;
+    const __half* residual;
+    int32_t* dump;          // [M, N, G] or null
+    int M, N, K, g, G;
+    int epilogue;
+    int split_k;
+};
+
+// w8a8_quant.cu
+int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
+                    const __half* norm_weight, float eps, const __half* smooth_inv,
+                    const __half* act_scale, int M, int K, int g, int act_mode, __half* normed_out,
+                    int8_t* Xq, float* Xs, cudaStream_t stream);
+// w8a8_elementwise.cu
+int launch_silu(__half* a, long n, cudaStream_t s);
+int launch_mul(__half* a, const __half* b, long n, cudaStream_t s);
+int launch_residual_add(__half* a, const __half* b, long n, cudaStream_t s);
+int launch_pack_gate_up(const int8_t* wg, const __half* sg, const int8_t* wu, const __half* su,
+                        int inter, int K, int G, int8_t* Wo, __half* So, cudaStream_t s);
+// w8a8_generic.cu : any shape, sequential group order.
+int launch_linear_generic(const LinearArgs& a, cudaStream_t s);
+// w8a8_gemv.cu : M <= 32.
+bool gemv_supports(const LinearArgs& a);
+int launch_linear_gemv(const LinearArgs& a, cudaStream_t s);
+// w8a8_gemm_sm100.cu : tcgen05 + TMA.
+bool gemm_supports(const LinearArgs& a);
+int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t s);
+
+}  // namespace w8a8

@@ -1,0 +1,231 @@
+// Row kernels: residual add -> RMSNorm -> activation quantiser, any subset, one launch.
+//
+// One CTA owns one token row and keeps it in shared memory from the first load
+// to the last store, so the chain
+//     residual_add (ffn_activations.cu:41-45) -> rms_norm (rms_norm.cu:10-58)
+//     -> quantize_activation_groups_kernel (int8_gemm.cu:147-211)
+// costs one read of the row instead of three round trips through HBM. Every
+// value that the reference would have rounded to fp16 on its way through global
+// memory is rounded to fp16 here too, so the int8 codes and the fp32 scales are
+// bit-identical to those of the unfused reference chain.
+#include "w8a8_internal.h"
+
+namespace w8a8 {
+namespace {
+
+constexpr int kWarp = 32;
+
+struct RowQuantParams {
+    const __half* x_in;
+    __half* x_out;            // where x_in + residual goes (null: not stored)
+    const __half* residual;   // null: no add
+    const __half* norm_weight;  // null: no norm
+    float eps;
+    const __half* smooth_inv;
+    const __half* act_scale;  // static scales [G] or null
+    __half* normed_out;       // null: not stored
+    int8_t* Xq;               // null: no quantisation (plain rms_norm)
+    float* Xs;
+    int K, g, G;
+    int per_token;
+    int vec_ok;               // K % 8 == 0 and all fp16 pointers 16-byte aligned
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = kWarp / 2; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+__global__ void __launch_bounds__(1024) rowquant_kernel(const RowQuantParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __half* row = reinterpret_cast<__half*>(smem_raw);
+    float* gscale = reinterpret_cast<float*>(smem_raw + ((static_cast<size_t>(p.K) * 2 + 15) & ~size_t(15)));
+    __shared__ float s_red[kWarp];
+
+    const int tid = threadIdx.x;
+    const int T = blockDim.x;
+    const int K = p.K;
+    const size_t base = static_cast<size_t>(blockIdx.x) * K;
+
+    // ---- stage the row (+ residual add, rounded to fp16 like residual_add_kernel) ----
+    if (p.vec_ok) {
+        const uint4* src = reinterpret_cast<const uint4*>(p.x_in + base);
+        const uint4* res = p.residual ? reinterpret_cast<const uint4*>(p.residual + base) : nullptr;
+        uint4* dst = p.x_out ? reinterpret_cast<uint4*>(p.x_out + base) : nullptr;
+        for (int v = tid; v < K / 8; v += T) {
+            uint4 u = src[v];
+            if (res) {
+                uint4 r = res[v];
+                __half2* uh = reinterpret_cast<__half2*>(&u);
+                const __half2* rh = reinterpret_cast<const __half2*>(&r);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    float2 a = __half22float2(uh[i]), b = __half22float2(rh[i]);
+                    uh[i] = __halves2half2(__float2half(a.x + b.x), __float2half(a.y + b.y));
+                }
+                if (dst) dst[v] = u;
+            }
+            reinterpret_cast<uint4*>(row)[v] = u;
+        }
+    } else {
+        for (int i = tid; i < K; i += T) {
+            __half h = p.x_in[base + i];
+            if (p.residual) {
+                h = __float2half(__half2float(h) + __half2float(p.residual[base + i]));
+                if (p.x_out) p.x_out[base + i] = h;
+            }
+            row[i] = h;
+        }
+    }
+    __syncthreads();
+
+    // ---- RMSNorm, with the reference's summation order (rms_norm.cu:23-49): thread t sums
+    // elements t, t+T, ...; shuffle-down tree inside each warp; shuffle-down tree over warps. ----
+    if (p.norm_weight) {
+        float local_sum = 0.0f;
+        for (int i = tid; i < K; i += T) {
+            float val = __half2float(row[i]);
+            local_sum += val * val;
+        }
+        for (int offset = kWarp / 2; offset > 0; offset /= 2)
+            local_sum += __shfl_down_sync(0xffffffffu, local_sum, offset);
+        if ((tid & (kWarp - 1)) == 0) s_red[tid / kWarp] = local_sum;
+        __syncthreads();
+        float total_sum = 0.0f;
+        int num_warps = (T + kWarp - 1) / kWarp;
+        if (tid < num_warps) total_sum = s_red[tid];
+        for (int offset = kWarp / 2; offset > 0; offset /= 2)
+            total_sum += __shfl_down_sync(0xffffffffu, total_sum, offset);
+        __syncthreads();
+        if (tid == 0) s_red[0] = rsqrtf(total_sum / K + p.eps);
+        __syncthreads();
+        const float rms = s_red[0];
+        for (int i = tid; i < K; i += T) {
+            float val = __half2float(row[i]) * rms;
+            __half o = __float2half(val * __half2float(p.norm_weight[i]));
+            row[i] = o;
+            if (p.normed_out) p.normed_out[base + i] = o;
+        }
+        __syncthreads();
+    }
+    if (!p.Xq) return;
+
+    // ---- scales: one warp per group; absmax is order-free (int8_gemm.cu:177-199) ----
+    const int lane = tid & (kWarp - 1), warp = tid / kWarp, nwarps = T / kWarp;
+    const int g = p.g, G = p.G;
+    if (p.act_scale) {
+        for (int j = tid; j < G; j += T) {
+            float s = __half2float(p.act_scale[j]);
+            gscale[j] = s < 1e-8f ? 1e-8f : s;
+        }
+    } else {
+        for (int j = warp; j < G; j += nwarps) {
+            int start = j * g, end = min(start + g, K);
+            float m = 0.0f;
+            for (int k = start + lane; k < end; k += kWarp) {
+                float v = __half2float(row[k]);
+                if (p.smooth_inv) v *= __half2float(p.smooth_inv[k]);
+                m = fmaxf(m, fabsf(v));
+            }
+            m = warp_max(m);
+            if (lane == 0) gscale[j] = m;  // absmax for now
+        }
+        __syncthreads();
+        if (p.per_token) {
+            float m = 0.0f;
+            for (int j = tid; j < G; j += T) m = fmaxf(m, gscale[j]);
+            m = warp_max(m);
+            if (lane == 0) s_red[warp] = m;
+            __syncthreads();
+            m = 0.0f;
+            for (int w = 0; w < nwarps; ++w) m = fmaxf(m, s_red[w]);
+            __syncthreads();
+            for (int j = tid; j < G; j += T) gscale[j] = m;
+            __syncthreads();
+        }
+        for (int j = tid; j < G; j += T) {
+            float s = gscale[j] / 127.0f;
+            gscale[j] = s < 1e-8f ? 1e-8f : s;
+        }
+    }
+    __syncthreads();
+    for (int j = tid; j < G; j += T) p.Xs[static_cast<size_t>(blockIdx.x) * G + j] = gscale[j];
+
+    // ---- codes (int8_gemm.cu:201-210) ----
+    int8_t* q_row = p.Xq + base;
+    if ((K & 3) == 0 && (g & 3) == 0) {
+        for (int w4 = tid; w4 < K / 4; w4 += T) {
+            const int k0 = w4 * 4;
+            const float inv_scale = 1.0f / gscale[k0 / g];
+            uint32_t packed = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                float v = __half2float(row[k0 + i]);
+                if (p.smooth_inv) v *= __half2float(p.smooth_inv[k0 + i]);
+                int q = __float2int_rn(v * inv_scale);
+                q = max(-127, min(127, q));
+                packed |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
+            }
+            reinterpret_cast<uint32_t*>(q_row)[w4] = packed;
+        }
+    } else {
+        for (int k = tid; k < K; k += T) {
+            const float inv_scale = 1.0f / gscale[k / g];
+            float v = __half2float(row[k]);
+            if (p.smooth_inv) v *= __half2float(p.smooth_inv[k]);
+            int q = __float2int_rn(v * inv_scale);
+            q = max(-127, min(127, q));
+            q_row[k] = static_cast<int8_t>(q);
+        }
+    }
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
+                    const __half* norm_weight, float eps, const __half* smooth_inv,
+                    const __half* act_scale, int M, int K, int g, int act_mode, __half* normed_out,
+                    int8_t* Xq, float* Xs, cudaStream_t stream) {
+    if (M == 0) return W8A8_OK;
+    RowQuantParams p;
+    p.x_in = x_in;
+    p.x_out = x_out;
+    p.residual = residual;
+    p.norm_weight = norm_weight;
+    p.eps = eps;
+    p.smooth_inv = smooth_inv;
+    p.act_scale = act_scale;
+    p.normed_out = normed_out;
+    p.Xq = Xq;
+    p.Xs = Xs;
+    p.K = K;
+    p.g = norm_group(K, g);
+    p.G = num_groups(K, g);
+    p.per_token = act_mode == W8A8_ACT_PER_TOKEN;
+    p.vec_ok = (K % 8 == 0) && aligned16(x_in) && (!residual || aligned16(residual)) &&
+               (!x_out || aligned16(x_out));
+    // The norm must run with the reference's block size to reproduce its summation order:
+    // min(1024, next_pow2(dim)), rms_norm.cu:69-70.
+    int threads = 256;
+    if (norm_weight) {
+        threads = 1;
+        while (threads < K && threads < 1024) threads <<= 1;
+        if (threads < 32) threads = 32;  // shuffles need whole warps; lanes past K add 0.0f
+    } else if (K >= 4096) {
+        threads = 512;
+    }
+    size_t smem = ((static_cast<size_t>(K) * 2 + 15) & ~size_t(15)) + static_cast<size_t>(p.G) * 4;
+    if (smem > 200 * 1024) return fail(W8A8_ERR_UNSUPPORTED, "row of K=%d does not fit shared memory", K);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(rowquant_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    }
+    rowquant_kernel<<<M, threads, smem, stream>>>(p);
+    return check_launch("rowquant_kernel");
+}
+
+}  // namespace w8a8

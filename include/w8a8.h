@@ -1,0 +1,156 @@
+/*
+ * w8a8.h — C ABI of the B200 (sm_100a) INT8 W8A8 linear-layer library.
+ *
+ * Drop-in for the kernel-layer boundary of KBlackMeow/fish-audio-cpp: every
+ * entry point names the reference interface it replaces (path:line inside
+ * that project). All pointers are DEVICE pointers owned by the caller unless
+ * said otherwise; `stream` is a cudaStream_t passed as void*. Every call is
+ * asynchronous on `stream`, never allocates, never synchronises, and returns a
+ * status code (no C++ exception crosses this boundary).
+ *
+ * Naming: M = tokens, N = output features (weight rows), K = input features,
+ * group_size = quantisation group along K (<= 0 or > K means one group of K),
+ * G = ceil(K / group_size). The reference's own signature calls the weight
+ * rows "M" and the tokens "N"; the C++ shim (fish_kernels_shim.h) keeps that
+ * order, this header does not.
+ *
+ * Layouts (all row-major, identical to the reference's):
+ *   W        int8   [N, K]
+ *   w_scale  fp16   [N] when G == 1, else [N, G]
+ *   X, Y     fp16   [M, K], [M, N]
+ *   Xq       int8   [M, K]      activation codes, never -128
+ *   Xs       fp32   [M, G]      activation scales
+ *   smooth_inv fp16 [K]  (optional)   act_scale fp16 [G] (optional, static scales)
+ */
+#ifndef W8A8_H
+#define W8A8_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define W8A8_API __attribute__((visibility("default")))
+#else
+#define W8A8_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status -------------------------------------------------------------- */
+enum {
+    W8A8_OK = 0,
+    W8A8_ERR_INVALID_ARG = 1, /* null pointer, negative size, misaligned pointer */
+    W8A8_ERR_UNSUPPORTED = 2, /* shape outside what any kernel here handles */
+    W8A8_ERR_CUDA = 3,        /* a CUDA call failed; see w8a8_last_error() */
+    W8A8_ERR_TIMEOUT = 4,     /* a bounded device-side wait ran out */
+    W8A8_ERR_WORKSPACE = 5    /* the context's scratch is too small for this call */
+};
+W8A8_API const char* w8a8_status_string(int status);
+/* Message of the last failing call on this host thread (thread-local, never NULL).
+ * Replaces the std::runtime_error text of CUDA_CHECK, src/utils/cuda_utils.h:9-16. */
+W8A8_API const char* w8a8_last_error(void);
+
+/* ---- context ------------------------------------------------------------- */
+/* Owns the scratch that the reference keeps in a thread_local Workspace that
+ * grows by cudaFree+cudaMalloc inside the call (src/kernels/int8_gemm.cu:31-44,
+ * :97-102, :405-413). Here it is sized once, so calls are capturable and never
+ * block. One context per stream: calls sharing a context must not overlap. */
+typedef struct w8a8_ctx w8a8_ctx;
+
+W8A8_API int w8a8_create(w8a8_ctx** out, int device, size_t workspace_bytes);
+W8A8_API int w8a8_destroy(w8a8_ctx* ctx);
+/* Scratch a w8a8_linear call of this shape needs (codes + scales for M > 32; 0 below). */
+W8A8_API size_t w8a8_workspace_bytes(int M, int N, int K, int group_size);
+W8A8_API size_t w8a8_ctx_workspace_bytes(const w8a8_ctx* ctx);
+/* Polls the context's device error word (set by a kernel whose bounded wait ran
+ * out). Synchronises `stream`. Returns W8A8_OK or W8A8_ERR_TIMEOUT and clears it. */
+W8A8_API int w8a8_check_device_status(w8a8_ctx* ctx, void* stream);
+
+/* ---- options ------------------------------------------------------------- */
+enum { /* how activation scales are formed */
+    W8A8_ACT_PER_TOKEN_GROUP = 0, /* one scale per (token, K-group): what the reference does,
+                                     int8_gemm.cu:147-211 with grid (tokens, groups) */
+    W8A8_ACT_PER_TOKEN = 1        /* one scale per token over all of K (no reference counterpart) */
+};
+enum { /* what happens to the fp32 accumulator after the last group */
+    W8A8_EPI_NONE = 0,     /* Y = half(acc)                         int8_gemm.cu:236-243 */
+    W8A8_EPI_RESIDUAL = 1, /* Y = half(float(half(acc)) + float(R)) + ffn_activations.cu:41-45 */
+    W8A8_EPI_SWIGLU = 2    /* W holds gate and up rows interleaved in blocks of 16 rows
+                              (8 gate rows, then the 8 up rows of the same channels; see
+                              w8a8_pack_gate_up). Y is [M, N/2]:
+                              half(float(half(silu(float(half(g))))) * float(half(u))),
+                              i.e. the GEMM, silu, GEMM, mul chain of
+                              src/engine/dual_ar_engine.cc:640-644 with every fp16 rounding kept. */
+};
+enum { /* forces a kernel family; default picks by shape */
+    W8A8_KERNEL_AUTO = 0,
+    W8A8_KERNEL_GENERIC = 1, /* scalar-order SIMT kernel, any shape */
+    W8A8_KERNEL_GEMV = 2,    /* M <= 32: warp-MMA weight-streaming kernel */
+    W8A8_KERNEL_GEMM = 3     /* tcgen05 + TMA kernel */
+};
+
+typedef struct w8a8_linear_opts {
+    int act_mode;             /* W8A8_ACT_* (ignored by w8a8_linear_q) */
+    int epilogue;             /* W8A8_EPI_* */
+    const void* residual;     /* fp16 [M, N], W8A8_EPI_RESIDUAL only; may alias Y */
+    int32_t* dump_group_sums; /* optional int32 [M, N, G]: the exact per-group integer sums
+                                 (what int8_gemm.cu:470-490 leaves in `partial`), for parity tests */
+    int kernel;               /* W8A8_KERNEL_* */
+    int split_k;              /* GEMV only: 0 = choose, else 1/2/4/8 K-slices per row tile */
+} w8a8_linear_opts;
+
+/* ---- the path ------------------------------------------------------------ */
+
+/* Replaces quantize_activation_groups_kernel, src/kernels/int8_gemm.cu:147-211. */
+W8A8_API int w8a8_quantize(w8a8_ctx* ctx, const void* X, const void* smooth_inv, const void* act_scale,
+                  int M, int K, int group_size, int act_mode, void* Xq, void* Xs, void* stream);
+
+/* Replaces fish::kernels::rms_norm, src/kernels/kernels.h:10-19 (src/kernels/rms_norm.cu:10-76).
+ * Same summation order as the reference kernel, so results are bit-identical to it. */
+W8A8_API int w8a8_rms_norm(w8a8_ctx* ctx, const void* x, const void* weight, void* out, int tokens,
+                  int dim, float eps, void* stream);
+
+/* Fuses, per token row: [x += residual (ffn_activations.cu:41-45)] -> rms_norm
+ * (rms_norm.cu:10-58) -> quantiser (int8_gemm.cu:147-211). The normed value is rounded to
+ * fp16 in registers before it is quantised, so codes equal those of the unfused chain.
+ * residual may be NULL; when it is not, x is updated in place. normed_out may be NULL. */
+W8A8_API int w8a8_rmsnorm_quantize(w8a8_ctx* ctx, void* x, const void* residual, const void* weight,
+                          float eps, const void* smooth_inv, const void* act_scale, int M, int K,
+                          int group_size, int act_mode, void* normed_out, void* Xq, void* Xs,
+                          void* stream);
+
+/* Replace silu_forward / mul_forward / residual_add, src/kernels/kernels.h:111-141
+ * (src/kernels/ffn_activations.cu:12-17, :35-45). In place on a. */
+W8A8_API int w8a8_silu(w8a8_ctx* ctx, void* a, long n, void* stream);
+W8A8_API int w8a8_mul(w8a8_ctx* ctx, void* a, const void* b, long n, void* stream);
+W8A8_API int w8a8_residual_add(w8a8_ctx* ctx, void* a, const void* b, long n, void* stream);
+
+/* Replaces fish::kernels::int8_dequant_gemm_fp16, src/kernels/kernels.h:242-259
+ * (src/kernels/int8_gemm.cu:384-511): quantise X, integer GEMM per K-group, fp32 promote with
+ * both scales, fp16 out. opts may be NULL (reference behaviour). */
+W8A8_API int w8a8_linear(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size,
+                const void* act_scale, const void* smooth_inv, const void* X, void* Y, int M,
+                int N, int K, const w8a8_linear_opts* opts, void* stream);
+
+/* The same from codes and scales already formed (by w8a8_quantize or
+ * w8a8_rmsnorm_quantize): int8_gemm.cu:423-505 without its first stage. */
+W8A8_API int w8a8_linear_q(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size,
+                  const void* Xq, const void* Xs, void* Y, int M, int N, int K,
+                  const w8a8_linear_opts* opts, void* stream);
+
+/* ---- loader side --------------------------------------------------------- */
+/* Pre-pack for W8A8_EPI_SWIGLU: interleaves w1 (gate) and w3 (up), both int8 [inter, K] with
+ * fp16 scales [inter, G], into W_out int8 [2*inter, K] / scale_out fp16 [2*inter, G] in blocks
+ * of 16 rows = 8 gate rows then the 8 up rows of the same channels. inter % 8 == 0. The
+ * reference keeps w1 and w3 apart and runs two GEMMs (src/engine/dual_ar_engine.cc:640-643);
+ * this is what its loader loop (dual_ar_engine.cc:231-278) would call once per layer. */
+W8A8_API int w8a8_pack_gate_up(w8a8_ctx* ctx, const void* w_gate, const void* s_gate, const void* w_up,
+                      const void* s_up, int inter, int K, int G, void* W_out, void* scale_out,
+                      void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* W8A8_H */
