@@ -36,6 +36,7 @@ def lib() -> C.CDLL:
         _lib.fishref_int8_dequant_gemm_fp16.argtypes = [P, P, I, P, P, P, P, I, I, I, P]
         _lib.fishref_workspace_ptr.restype = P
         _lib.fishref_workspace_ptr.argtypes = [I]
+        _lib.fishref_copy_workspace.argtypes = [I, P, C.c_size_t]
         _lib.fishref_rms_norm.argtypes = [P, P, P, I, I, C.c_float, P]
         _lib.fishref_silu.argtypes = [P, I, P]
         _lib.fishref_mul.argtypes = [P, P, I, P]
@@ -56,6 +57,11 @@ def int8_dequant_gemm_fp16(W, scale, group_size, act_scale, smooth_inv, X, Y, M_
 def workspace_ptr(which: int) -> int:
     """0 codes [N_tok,K] int8 · 1 scales [N_tok,G] fp32 · 2 last group's int32 sums [N_tok][M_out] · 3 fp32 accum."""
     return lib().fishref_workspace_ptr(which)
+
+
+def copy_workspace(which: int, dst: int, nbytes: int):
+    """Device-to-device copy of workspace `which` (see workspace_ptr) into dst."""
+    _check(lib().fishref_copy_workspace(which, dst, nbytes))
 
 
 def rms_norm(x, w, out, n_tokens, dim, eps, stream=None):

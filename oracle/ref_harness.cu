@@ -70,6 +70,15 @@ void* fishref_workspace_ptr(int which) {
     return nullptr;
 }
 
+// Copies `bytes` of workspace `which` (see above) into the device buffer dst.
+int fishref_copy_workspace(int which, void* dst, size_t bytes) {
+    void* src = fishref_workspace_ptr(which);
+    if (!src) { snprintf(g_err, sizeof g_err, "workspace %d is empty", which); return 1; }
+    cudaError_t e = cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToDevice);
+    if (e != cudaSuccess) { snprintf(g_err, sizeof g_err, "CUDA: %s", cudaGetErrorString(e)); return 3; }
+    return 0;
+}
+
 int fishref_rms_norm(const void* x, const void* w, void* out, int n_tokens, int dim, float eps,
                      void* stream) {
     return guarded([&] {

@@ -1,0 +1,388 @@
+"""GPU parity: every entry point of the C ABI against the CPU oracle on identical seeded inputs,
+and against the reference's own CUDA kernels when that harness was built.
+
+Bars: int8 codes, fp32 activation scales and per-group int32 sums bit-exact; fp16 outputs
+within 2 fp16 ulp of the fp32-accumulated oracle (or relative error <= 2e-3).
+"""
+import numpy as np
+import pytest
+import torch
+
+from fish_audio_cpp_b200 import synth
+from oracle import fishref
+
+pytestmark = pytest.mark.gpu
+
+ULP_BAR = 2
+REL_BAR = 2e-3
+# A third way to pass, for outputs that are small only because large terms cancel: the difference is
+# no more than a re-ordering of the same fp32 sum can produce, 4 * 2^-24 * sum_j |P_j * ws_j * xs_j|.
+# (The reference's own M <= 4 kernels sum per-thread partials in a tree and differ from its M > 4
+# path by the same kind of amount.)
+REORDER_EPS = 4 * 2.0 ** -24
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+def guarded(shape, dtype, fill):
+    """A device tensor with 64 sentinel elements before and after the payload."""
+    n = int(np.prod(shape))
+    buf = torch.full((n + 128,), fill, dtype=dtype, device="cuda")
+    return buf, buf[64:64 + n].view(*shape)
+
+
+def guards_intact(buf, fill):
+    return bool((buf[:64] == fill).all() and (buf[-64:] == fill).all())
+
+
+def abs_term_sum(P, ws, Xs):
+    """sum_j |P[m,n,j] * ws[n,j] * xs[m,j]| in float64: the scale of the fp32 summation error."""
+    M, N, G = P.shape
+    return (np.abs(P).astype(np.float64) * ws.reshape(N, G).astype(np.float64)[None] *
+            Xs.astype(np.float64)[:, None, :]).sum(-1)
+
+
+def assert_close_fp16(oracle, got, want, what="", abs_terms=None):
+    ulp = oracle.ulp_distance_fp16(got, want)
+    g32, w32 = got.astype(np.float32), want.astype(np.float32)
+    diff = np.abs(g32 - w32)
+    rel = diff / np.maximum(np.abs(w32), 1e-30)
+    bad = (ulp > ULP_BAR) & (rel > REL_BAR)
+    if abs_terms is not None:
+        # half an fp16 ulp of slack on each side for the final roundings of got and want
+        slack = REORDER_EPS * abs_terms + np.spacing(np.abs(want).astype(np.float16)).astype(np.float64)
+        bad &= diff > slack
+    assert not bad.any(), f"{what}: {bad.sum()} elements off; max ulp {ulp[bad].max()}, max rel {rel[bad].max():.3g}"
+
+
+# ---------------------------------------------------------------- quantiser (A1)
+QUANT_CASES = [(1, 2560, 256), (16, 2560, 256), (4, 4096, 64), (16, 9728, 64), (3, 9728, 256), (2, 100, 32),
+               (5, 52, 20), (7, 72, 0), (33, 640, 128), (1, 64, 64), (2, 2560, 2560)]
+
+
+@pytest.mark.parametrize("M,K,g", QUANT_CASES)
+@pytest.mark.parametrize("mode", [0, 1])
+def test_quantize_bit_exact(ctx, oracle, M, K, g, mode):
+    rng = np.random.default_rng(100 + M + K)
+    X = synth.activations(rng, M, K)
+    G = oracle.num_groups(K, g)
+    qbuf, dq = guarded((M, K), torch.int8, 55)
+    sbuf, ds = guarded((M, G), torch.float32, -7.0)
+    ctx.quantize(dev(X), M, K, g, dq, ds, act_mode=mode)
+    torch.cuda.synchronize()
+    wq, wsc = oracle.quantize(X, g, act_mode=mode)
+    assert np.array_equal(dq.cpu().numpy(), wq)
+    assert np.array_equal(ds.cpu().numpy(), wsc)
+    assert guards_intact(qbuf, 55) and guards_intact(sbuf, -7.0)
+
+
+def test_quantize_smooth_static_zero_group(ctx, oracle):
+    rng = np.random.default_rng(3)
+    M, K, g = 5, 512, 64
+    X = synth.activations(rng, M, K)
+    X[1, 64:128] = 0
+    smooth = rng.uniform(0.25, 4.0, K).astype(np.float16)
+    static = rng.uniform(0.01, 0.5, K // g).astype(np.float16)
+    static[2] = 0  # floors at 1e-8, codes saturate
+    for kw, okw in [({"smooth_inv": dev(smooth)}, {"smooth_inv": smooth}),
+                    ({"act_scale": dev(static)}, {"act_scale": static}),
+                    ({"smooth_inv": dev(smooth), "act_scale": dev(static)}, {"smooth_inv": smooth, "act_scale": static})]:
+        dq = torch.empty((M, K), dtype=torch.int8, device="cuda")
+        ds = torch.empty((M, K // g), dtype=torch.float32, device="cuda")
+        ctx.quantize(dev(X), M, K, g, dq, ds, **kw)
+        wq, wsc = oracle.quantize(X, g, **okw)
+        assert np.array_equal(dq.cpu().numpy(), wq) and np.array_equal(ds.cpu().numpy(), wsc)
+        assert dq.min().item() >= -127
+
+
+@pytest.mark.skipif(not fishref.available(), reason="reference harness not built")
+@pytest.mark.parametrize("M,K,g", [(1, 2560, 256), (16, 2560, 64), (6, 4096, 256), (8, 9728, 64), (3, 100, 32)])
+def test_quantize_matches_reference_kernel(ctx, oracle, M, K, g):
+    """Codes and scales against what the reference leaves in its workspace (int8_gemm.cu:415-421)."""
+    rng = np.random.default_rng(M * 7 + K)
+    X = synth.activations(rng, M, K)
+    N = 8
+    W, ws = synth.weights(rng, N, K), synth.weight_scales(rng, N, oracle.num_groups(K, g))
+    dX, dW, dS = dev(X), dev(W), dev(ws)
+    dY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    fishref.int8_dequant_gemm_fp16(dW.data_ptr(), dS.data_ptr(), g, None, None, dX.data_ptr(), dY.data_ptr(), N, M, K)
+    torch.cuda.synchronize()
+    G = oracle.num_groups(K, g)
+    rq = torch.empty((M, K), dtype=torch.int8, device="cuda")
+    rs = torch.empty((M, G), dtype=torch.float32, device="cuda")
+    fishref.copy_workspace(0, rq.data_ptr(), M * K)
+    fishref.copy_workspace(1, rs.data_ptr(), M * G * 4)
+    dq = torch.empty_like(rq)
+    ds = torch.empty_like(rs)
+    ctx.quantize(dX, M, K, g, dq, ds)
+    torch.cuda.synchronize()
+    assert torch.equal(dq, rq) and torch.equal(ds, rs)
+    wq, wsc = oracle.quantize(X, g)  # and the oracle agrees with the reference: this pins the oracle
+    assert np.array_equal(rq.cpu().numpy(), wq) and np.array_equal(rs.cpu().numpy(), wsc)
+
+
+# ---------------------------------------------------------------- RMSNorm (A2) and the fused row kernel
+@pytest.mark.parametrize("T,D", [(4, 8), (3, 16), (16, 2560), (1, 2560), (40, 128), (5, 4096), (2, 100)])
+def test_rms_norm(ctx, oracle, T, D):
+    rng = np.random.default_rng(T + D)
+    x = rng.standard_normal((T, D)).astype(np.float16)
+    w = rng.uniform(0.5, 1.5, D).astype(np.float16)
+    obuf, do = guarded((T, D), torch.float16, 77.0)
+    dx, dw = dev(x), dev(w)
+    ctx.rms_norm(dx, dw, do, T, D, 1e-6)
+    torch.cuda.synchronize()
+    got = do.cpu().numpy()
+    assert oracle.ulp_distance_fp16(got, oracle.rms_norm(x, w, 1e-6)).max() <= 1
+    assert guards_intact(obuf, 77.0)
+    if fishref.available() and D >= 32:
+        ro = torch.empty((T, D), dtype=torch.float16, device="cuda")
+        fishref.rms_norm(dx.data_ptr(), dw.data_ptr(), ro.data_ptr(), T, D, 1e-6)
+        torch.cuda.synchronize()
+        assert torch.equal(ro, do), "same summation order as rms_norm.cu must give the same bits"
+
+
+def test_rms_norm_reference_known_answers(ctx):
+    """tests/test_kernels.cu:121-247 of the reference, same inputs and tolerances."""
+    def run(x, w, eps):
+        o = torch.empty_like(x)
+        ctx.rms_norm(x, w, o, x.shape[0], x.shape[1], eps)
+        torch.cuda.synchronize()
+        return o.float()
+    h = dict(dtype=torch.float16, device="cuda")
+    assert (run(torch.ones(4, 8, **h), torch.ones(8, **h), 1e-6) - 1).abs().max() < 1e-3
+    assert torch.isfinite(run(torch.zeros(2, 4, **h), torch.ones(4, **h), 1e-5)).all()
+    x = torch.tensor([[1., 3., 1., 3.]], **h)
+    want = x.float() / (5 + 1e-6) ** 0.5 * 2
+    assert (run(x, torch.full((4,), 2.0, **h), 1e-6) - want).abs().max() < 1e-2
+    x = torch.from_numpy(np.random.default_rng(42).standard_normal((3, 16)).astype(np.float16)).cuda()
+    out = run(x, torch.ones(16, **h), 1e-6)
+    assert ((out ** 2).mean(dim=1).sqrt() - 1).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("M,K,g", [(1, 2560, 256), (8, 2560, 64), (16, 2560, 256), (3, 4096, 64), (2, 128, 64)])
+@pytest.mark.parametrize("with_residual", [False, True])
+def test_rmsnorm_quantize_equals_unfused_chain(ctx, oracle, M, K, g, with_residual):
+    rng = np.random.default_rng(K + M)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    r = rng.standard_normal((M, K)).astype(np.float16)
+    w = rng.uniform(0.5, 1.5, K).astype(np.float16)
+    G = oracle.num_groups(K, g)
+    dx, dr, dw = dev(x), dev(r), dev(w)
+    dn = torch.empty((M, K), dtype=torch.float16, device="cuda")
+    dq = torch.empty((M, K), dtype=torch.int8, device="cuda")
+    ds = torch.empty((M, G), dtype=torch.float32, device="cuda")
+    ctx.rmsnorm_quantize(dx, dw, 1e-6, M, K, g, dq, ds, residual=dr if with_residual else None, normed_out=dn)
+    torch.cuda.synchronize()
+    # the chain, step by step through the separate entry points
+    cx = dev(x)
+    if with_residual:
+        ctx.residual_add(cx, dr, M * K)
+        assert torch.equal(cx, dx), "x must be updated in place with the rounded sum"
+        assert np.array_equal(dx.cpu().numpy(), oracle.residual_add(x, r))
+    cn = torch.empty_like(dn)
+    ctx.rms_norm(cx, dw, cn, M, K, 1e-6)
+    assert torch.equal(cn, dn)
+    wq, wsc = oracle.quantize(dn.cpu().numpy(), g)  # oracle quantiser on the device's normed values
+    assert np.array_equal(dq.cpu().numpy(), wq) and np.array_equal(ds.cpu().numpy(), wsc)
+
+
+# ---------------------------------------------------------------- elementwise (A10)
+@pytest.mark.parametrize("n", [16, 1024, 8 * 9728 + 3])
+def test_elementwise(ctx, oracle, n):
+    rng = np.random.default_rng(n)
+    a = (rng.standard_normal(n) * 2).astype(np.float16)
+    b = rng.standard_normal(n).astype(np.float16)
+    da = dev(a); ctx.silu(da, n)
+    assert oracle.ulp_distance_fp16(da.cpu().numpy(), oracle.silu(a)).max() <= 1
+    dm = dev(a); ctx.mul(dm, dev(b), n)
+    assert np.array_equal(dm.cpu().numpy(), oracle.mul(a, b))
+    dr = dev(a); ctx.residual_add(dr, dev(b), n)
+    assert np.array_equal(dr.cpu().numpy(), oracle.residual_add(a, b))
+    if fishref.available():
+        db = dev(b)
+        ra = dev(a); fishref.silu(ra.data_ptr(), n); torch.cuda.synchronize()
+        assert torch.equal(ra, da)
+        ra = dev(a); fishref.mul(ra.data_ptr(), db.data_ptr(), n); torch.cuda.synchronize()
+        assert torch.equal(ra, dm)
+        ra = dev(a); fishref.residual_add(ra.data_ptr(), db.data_ptr(), n); torch.cuda.synchronize()
+        assert torch.equal(ra, dr)
+
+
+# ---------------------------------------------------------------- linear (A3-A8)
+def run_linear(ctx, oracle, M, N, K, g, seed=0, fused_quant=True, **kw):
+    X, W, ws = synth.linear_case(seed, M, N, K, g)
+    G = oracle.num_groups(K, g)
+    dX, dW, dS = dev(X), dev(W), dev(ws)
+    ybuf, dY = guarded((M, N), torch.float16, 99.0)
+    dP = torch.full((M, N, G), -1, dtype=torch.int32, device="cuda")
+    if fused_quant:
+        ctx.linear(dW, dS, g, dX, dY, M, N, K, dump=dP, **kw)
+    else:
+        dq = torch.empty((M, K), dtype=torch.int8, device="cuda")
+        ds = torch.empty((M, G), dtype=torch.float32, device="cuda")
+        ctx.quantize(dX, M, K, g, dq, ds)
+        ctx.linear_q(dW, dS, g, dq, ds, dY, M, N, K, dump=dP, **kw)
+    torch.cuda.synchronize()
+    assert guards_intact(ybuf, 99.0)
+    Xq, Xs = oracle.quantize(X, g)
+    return (X, W, ws, Xq, Xs), dY.cpu().numpy(), dP.cpu().numpy()
+
+
+SMALL_SHAPES = [(1, 128, 256, 64), (4, 200, 512, 128), (8, 64, 2560, 256), (9, 192, 1024, 256), (16, 256, 2560, 2560),
+                (17, 96, 640, 64), (32, 128, 768, 256), (3, 72, 512, 512)]
+
+
+@pytest.mark.parametrize("M,N,K,g", SMALL_SHAPES)
+@pytest.mark.parametrize("fused_quant", [True, False])
+def test_gemv_small_shapes(ctx, oracle, pkg, M, N, K, g, fused_quant):
+    (X, W, ws, Xq, Xs), Y, P = run_linear(ctx, oracle, M, N, K, g, seed=M + N, fused_quant=fused_quant,
+                                          kernel=pkg.KERNEL_GEMV)
+    assert np.array_equal(P, oracle.group_sums(W, Xq, g)), "per-group int32 sums must be bit-exact"
+    assert_close_fp16(oracle, Y, oracle.linear_q(W, ws, Xq, Xs, g), "gemv")
+
+
+@pytest.mark.parametrize("split_k", [1, 2, 3, 4, 5, 8])
+def test_gemv_split_k_is_deterministic_and_correct(ctx, oracle, pkg, split_k):
+    M, N, K, g = 16, 320, 2560, 256
+    (X, W, ws, Xq, Xs), Y, P = run_linear(ctx, oracle, M, N, K, g, seed=1, kernel=pkg.KERNEL_GEMV, split_k=split_k)
+    assert np.array_equal(P, oracle.group_sums(W, Xq, g))
+    assert_close_fp16(oracle, Y, oracle.linear_q(W, ws, Xq, Xs, g), f"split_k={split_k}")
+    _, Y2, _ = run_linear(ctx, oracle, M, N, K, g, seed=1, kernel=pkg.KERNEL_GEMV, split_k=split_k)
+    assert np.array_equal(Y.view(np.uint16), Y2.view(np.uint16)), "two runs must agree bit for bit"
+    if split_k == 1:  # one slice = ascending groups = the oracle's order exactly
+        assert np.array_equal(Y.view(np.uint16), oracle.linear_q(W, ws, Xq, Xs, g).view(np.uint16))
+
+
+GENERIC_SHAPES = [(1, 8, 64, 64), (3, 24, 256, 64), (2, 7, 100, 32), (5, 9, 72, 0), (2, 5, 52, 20), (40, 33, 200, 64),
+                  (3, 10, 50, 16)]
+
+
+@pytest.mark.parametrize("M,N,K,g", GENERIC_SHAPES)
+def test_generic_kernel_is_bit_exact(ctx, oracle, pkg, M, N, K, g):
+    """Ragged last groups, odd K: the generic kernel follows the oracle's order, so fp16 bits match."""
+    (X, W, ws, Xq, Xs), Y, P = run_linear(ctx, oracle, M, N, K, g, seed=K, kernel=pkg.KERNEL_GENERIC)
+    assert np.array_equal(P, oracle.group_sums(W, Xq, g))
+    assert np.array_equal(Y.view(np.uint16), oracle.linear_q(W, ws, Xq, Xs, g).view(np.uint16))
+
+
+def test_auto_dispatch_covers_awkward_shapes(ctx, oracle):
+    for (M, N, K, g) in [(2, 7, 100, 32), (1, 64, 2560, 256), (40, 33, 200, 64), (0, 8, 64, 64)]:
+        X, W, ws = synth.linear_case(2, M, N, K, g)
+        dY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        ctx.linear(dev(W), dev(ws), g, dev(X), dY, M, N, K)
+        torch.cuda.synchronize()
+        if M:
+            assert_close_fp16(oracle, dY.cpu().numpy(), oracle.linear(W, ws, g, X), f"auto {M,N,K,g}")
+
+
+@pytest.mark.parametrize("kernel_name", ["KERNEL_GEMV", "KERNEL_GENERIC"])
+def test_epilogues_equal_the_unfused_chain(ctx, oracle, pkg, kernel_name):
+    kernel = getattr(pkg, kernel_name)
+    M, inter, K, g = 8, 192, 512, 256
+    rng = np.random.default_rng(9)
+    X = synth.activations(rng, M, K)
+    wg, wu = synth.weights(rng, inter, K), synth.weights(rng, inter, K)
+    G = K // g
+    sg, su = synth.weight_scales(rng, inter, G), synth.weight_scales(rng, inter, G)
+    # loader-side pack on the device vs its numpy restatement
+    dWp = torch.empty((2 * inter, K), dtype=torch.int8, device="cuda")
+    dSp = torch.empty((2 * inter, G), dtype=torch.float16, device="cuda")
+    ctx.pack_gate_up(dev(wg), dev(sg), dev(wu), dev(su), inter, K, G, dWp, dSp)
+    Wp, Sp = oracle.pack_gate_up(wg, sg, wu, su)
+    assert np.array_equal(dWp.cpu().numpy(), Wp) and np.array_equal(dSp.cpu().numpy().reshape(Sp.shape), Sp)
+    # SwiGLU epilogue == GEMM, silu, GEMM, mul through the separate entry points (bitwise, on the device)
+    dX = dev(X)
+    dA = torch.empty((M, inter), dtype=torch.float16, device="cuda")
+    ctx.linear(dWp, dSp, g, dX, dA, M, 2 * inter, K, epilogue=pkg.EPI_SWIGLU, kernel=kernel)
+    dG = torch.empty((M, inter), dtype=torch.float16, device="cuda")
+    dU = torch.empty((M, inter), dtype=torch.float16, device="cuda")
+    ctx.linear(dev(wg), dev(sg), g, dX, dG, M, inter, K, kernel=kernel)
+    ctx.linear(dev(wu), dev(su), g, dX, dU, M, inter, K, kernel=kernel)
+    ctx.silu(dG, M * inter)
+    ctx.mul(dG, dU, M * inter)
+    torch.cuda.synchronize()
+    assert torch.equal(dA, dG)
+    assert oracle.ulp_distance_fp16(dA.cpu().numpy(), oracle.linear(Wp, Sp, g, X, epilogue=oracle.EPI_SWIGLU)).max() <= 2
+    # residual epilogue == GEMM then residual_add; in place on the residual stream
+    R = rng.standard_normal((M, inter)).astype(np.float16)
+    dR = dev(R)
+    ctx.linear(dev(wg), dev(sg), g, dX, dR, M, inter, K, epilogue=pkg.EPI_RESIDUAL, residual=dR, kernel=kernel)
+    dT = torch.empty((M, inter), dtype=torch.float16, device="cuda")
+    ctx.linear(dev(wg), dev(sg), g, dX, dT, M, inter, K, kernel=kernel)
+    dR2 = dev(R)
+    ctx.residual_add(dR2, dT, M * inter)
+    torch.cuda.synchronize()
+    assert torch.equal(dR, dR2)
+
+
+def test_per_token_mode_and_static_scales_through_linear(ctx, oracle, pkg):
+    M, N, K, g = 8, 128, 1024, 256
+    X, W, ws = synth.linear_case(4, M, N, K, g)
+    static = np.random.default_rng(1).uniform(0.05, 0.3, K // g).astype(np.float16)
+    smooth = np.random.default_rng(2).uniform(0.5, 2.0, K).astype(np.float16)
+    for kw, okw in [({"act_mode": pkg.ACT_PER_TOKEN}, {"act_mode": oracle.ACT_PER_TOKEN}),
+                    ({"act_scale": dev(static)}, {"act_scale": static}),
+                    ({"smooth_inv": dev(smooth)}, {"smooth_inv": smooth})]:
+        dY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        ctx.linear(dev(W), dev(ws), g, dev(X), dY, M, N, K, **kw)
+        torch.cuda.synchronize()
+        assert_close_fp16(oracle, dY.cpu().numpy(), oracle.linear(W, ws, g, X, **okw), str(list(kw)))
+
+
+def test_shim_has_reference_semantics(ctx, oracle):
+    """The C++ entry point with the reference's letters: M = weight rows, N = tokens."""
+    tokens, out, K, g = 4, 96, 512, 64
+    X, W, ws = synth.linear_case(8, tokens, out, K, g)
+    dY = torch.empty((tokens, out), dtype=torch.float16, device="cuda")
+    ctx.shim_int8_dequant_gemm_fp16(dev(W), dev(ws), g, None, None, dev(X), dY, out, tokens, K)
+    torch.cuda.synchronize()
+    assert_close_fp16(oracle, dY.cpu().numpy(), oracle.linear(W, ws, g, X), "shim")
+    # group_size <= 0 or > K means one group of K, scale shape [M] (int8_gemm.cu:396-397)
+    ws1 = synth.weight_scales(np.random.default_rng(0), out, 1)
+    for gs in (0, -5, K + 1):
+        ctx.shim_int8_dequant_gemm_fp16(dev(W), dev(ws1), gs, None, None, dev(X), dY, out, tokens, K)
+        torch.cuda.synchronize()
+        assert_close_fp16(oracle, dY.cpu().numpy(), oracle.linear(W, ws1, gs, X), f"group_size={gs}")
+
+
+@pytest.mark.skipif(not fishref.available(), reason="reference harness not built")
+@pytest.mark.parametrize("M,N,K,g", [(1, 256, 2560, 256), (3, 128, 4096, 64), (8, 256, 2560, 256), (16, 192, 1024, 64),
+                                     (32, 64, 512, 256)])
+def test_linear_against_reference_kernel(ctx, oracle, M, N, K, g):
+    """Same seeded inputs through the reference's stock entry point and ours."""
+    X, W, ws = synth.linear_case(M + K, M, N, K, g)
+    dX, dW, dS = dev(X), dev(W), dev(ws)
+    rY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    fishref.int8_dequant_gemm_fp16(dW.data_ptr(), dS.data_ptr(), g, None, None, dX.data_ptr(), rY.data_ptr(), N, M, K)
+    dY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    ctx.linear(dW, dS, g, dX, dY, M, N, K)
+    torch.cuda.synchronize()
+    assert_close_fp16(oracle, dY.cpu().numpy(), rY.cpu().numpy(), "ours vs reference kernel")
+    want = oracle.linear(W, ws, g, X)
+    assert_close_fp16(oracle, rY.cpu().numpy(), want, "reference kernel vs oracle")
+    if M > 4:  # the reference's M>4 path accumulates groups in ascending order like the oracle
+        exact = np.array_equal(rY.cpu().numpy().view(np.uint16), want.view(np.uint16))
+        alt = oracle.linear(W, ws, g, X, promote=oracle.PROMOTE_MUL_ADD)
+        exact_alt = np.array_equal(rY.cpu().numpy().view(np.uint16), alt.view(np.uint16))
+        assert exact or exact_alt, "oracle promote order matches neither fma nor mul+add of the reference"
+
+
+# ---------------------------------------------------------------- headline shapes at full size
+@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
+@pytest.mark.parametrize("g", [256, 64])
+@pytest.mark.parametrize("M", [1, 4, 16])
+def test_decode_shapes_full_size(ctx, oracle, name, g, M):
+    K, N = synth.PROJECTIONS[name]
+    X, W, ws = synth.linear_case(1000 + M, M, N, K, g)
+    G = oracle.num_groups(K, g)
+    dP = torch.empty((M, N, G), dtype=torch.int32, device="cuda")
+    dY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    ctx.linear(dev(W), dev(ws), g, dev(X), dY, M, N, K, dump=dP)
+    torch.cuda.synchronize()
+    Xq, Xs = oracle.quantize(X, g)
+    P = oracle.group_sums(W, Xq, g)
+    assert np.array_equal(dP.cpu().numpy(), P)
+    assert_close_fp16(oracle, dY.cpu().numpy(), oracle.linear_q(W, ws, Xq, Xs, g), f"{name} M={M} g={g}",
+                      abs_terms=abs_term_sum(P, ws, Xs))
