@@ -18,6 +18,8 @@ from .capi import (  # noqa: F401
     Context,
     W8A8Error,
     library_path,
+    linear_static_scratch,
     load_library,
     num_groups,
+    static_scratch_bytes,
 )

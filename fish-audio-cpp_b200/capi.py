@@ -59,6 +59,8 @@ def load_library() -> C.CDLL:
         "w8a8_linear": (I, [P, P, P, I, P, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_linear_q": (I, [P, P, P, I, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_pack_gate_up": (I, [P, P, P, P, P, I, I, I, P, P, P]),
+        "w8a8_static_scratch_bytes": (Z, []),
+        "w8a8_linear_static_scratch": (I, [P, P, I, P, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "fish_shim_int8_dequant_gemm_fp16": (I, [P, P, I, P, P, P, P, I, I, I, P, C.c_char_p, I]),
     }
     for name, (res, args) in sigs.items():
@@ -72,7 +74,7 @@ EXPORTS = [
     "w8a8_status_string", "w8a8_last_error", "w8a8_create", "w8a8_destroy", "w8a8_workspace_bytes",
     "w8a8_ctx_workspace_bytes", "w8a8_check_device_status", "w8a8_quantize", "w8a8_rms_norm",
     "w8a8_rmsnorm_quantize", "w8a8_silu", "w8a8_mul", "w8a8_residual_add", "w8a8_linear", "w8a8_linear_q",
-    "w8a8_pack_gate_up",
+    "w8a8_pack_gate_up", "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch",
 ]
 
 
@@ -95,6 +97,24 @@ def _stream(stream) -> int | None:
 
         return torch.cuda.current_stream().cuda_stream or None
     return stream or None
+
+
+def static_scratch_bytes() -> int:
+    return load_library().w8a8_static_scratch_bytes()
+
+
+def linear_static_scratch(W, w_scale, group_size, X, Y, M, N, K, act_scale=None, smooth_inv=None,
+                          act_mode=ACT_PER_TOKEN_GROUP, epilogue=EPI_NONE, residual=None, dump=None,
+                          kernel=KERNEL_AUTO, split_k=0, stream=None):
+    """w8a8_linear for callers that may not allocate: no context, scratch built into the library
+    (one 8 MiB array per GPU, shared by all callers — do not overlap calls)."""
+    lib = load_library()
+    rc = lib.w8a8_linear_static_scratch(_ptr(W), _ptr(w_scale), group_size, _ptr(act_scale), _ptr(smooth_inv),
+                                        _ptr(X), _ptr(Y), M, N, K,
+                                        Context._opts(act_mode, epilogue, residual, dump, kernel, split_k),
+                                        _stream(stream))
+    if rc != 0:
+        raise W8A8Error(rc, "w8a8_linear_static_scratch", lib.w8a8_last_error().decode())
 
 
 class Context:

@@ -82,17 +82,21 @@ static LinearArgs make_args(const void* W, const void* w_scale, int group_size, 
 }
 
 // Runs a linear whose codes and scales exist.
-static int dispatch_q(w8a8_ctx* ctx, const LinearArgs& a, int kernel, cudaStream_t s) {
+int dispatch_linear_q(const LinearArgs& a, int kernel, int* device_status, cudaStream_t s) {
     if (a.M == 0) return W8A8_OK;
     switch (kernel) {
         case W8A8_KERNEL_GENERIC: return launch_linear_generic(a, s);
         case W8A8_KERNEL_GEMV: return launch_linear_gemv(a, s);
-        case W8A8_KERNEL_GEMM: return launch_linear_gemm(a, ctx->device_status, s);
+        case W8A8_KERNEL_GEMM: return launch_linear_gemm(a, device_status, s);
         default: break;
     }
     if (a.M <= 32 && gemv_supports(a)) return launch_linear_gemv(a, s);
-    if (gemm_supports(a)) return launch_linear_gemm(a, ctx->device_status, s);
+    if (gemm_supports(a)) return launch_linear_gemm(a, device_status, s);
     return launch_linear_generic(a, s);
+}
+
+static int dispatch_q(w8a8_ctx* ctx, const LinearArgs& a, int kernel, cudaStream_t s) {
+    return dispatch_linear_q(a, kernel, ctx->device_status, s);
 }
 
 }  // namespace w8a8

@@ -40,6 +40,8 @@ struct LinearArgs {
     int split_k;
 };
 
+// w8a8_api.cu : picks the kernel for a linear whose codes and scales exist.
+int dispatch_linear_q(const LinearArgs& a, int kernel, int* device_status, cudaStream_t s);
 // w8a8_quant.cu
 int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
                     const __half* norm_weight, float eps, const __half* smooth_inv,

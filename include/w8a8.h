@@ -140,6 +140,24 @@ W8A8_API int w8a8_linear_q(w8a8_ctx* ctx, const void* W, const void* w_scale, in
                   const void* Xq, const void* Xs, void* Y, int M, int N, int K,
                   const w8a8_linear_opts* opts, void* stream);
 
+/* No counterpart in the reference. The same computation as w8a8_linear for callers that may not
+ * allocate device memory and therefore cannot create a context (w8a8_create allocates): a plugin
+ * inside a host process that owns the whole device-memory budget, or a real-time audio thread that
+ * cannot afford the device-wide synchronisation cudaMalloc/cudaFree imply. The activation codes and
+ * scales live in an array built into the library image: w8a8_static_scratch_bytes() (8 MiB) on
+ * every GPU that loads the library, until the process exits. The call needs
+ * round_up(M*K, 256) + round_up(4*M*G, 256) bytes of it and returns W8A8_ERR_WORKSPACE, launching
+ * nothing, when that is more than the array holds. One array per GPU is shared by all streams and
+ * threads and keeps the last call's contents: calls that can overlap on the GPU race, so order
+ * them; nothing needs clearing between calls (every byte read was written by the same call). The
+ * first call on a device resolves the array's address on that device and should be made before any
+ * stream capture begins. Calls no cudaMalloc, cudaFree or other allocating routine. */
+W8A8_API size_t w8a8_static_scratch_bytes(void);
+W8A8_API int w8a8_linear_static_scratch(const void* W, const void* w_scale, int group_size,
+                               const void* act_scale, const void* smooth_inv, const void* X,
+                               void* Y, int M, int N, int K, const w8a8_linear_opts* opts,
+                               void* stream);
+
 /* ---- loader side --------------------------------------------------------- */
 /* Pre-pack for W8A8_EPI_SWIGLU: interleaves w1 (gate) and w3 (up), both int8 [inter, K] with
  * fp16 scales [inter, G], into W_out int8 [2*inter, K] / scale_out fp16 [2*inter, G] in blocks
