@@ -144,12 +144,13 @@ class DecodeSweep:
             self.host_y.append(torch.empty((c["M"], c["N"]), dtype=torch.float16).pin_memory())
         self.bytes_per_step = sum(algorithmic_bytes(c["M"], c["N"], c["K"], c["g"]) for c in self.cases)
         self.ops_per_step = sum(2 * c["M"] * c["N"] * c["K"] for c in self.cases)
-        self.launches_per_step = len(self.cases) if not reference else sum(
+        self.launches_per_step = 2 * len(self.cases) if not reference else sum(
             2 if c["M"] <= 4 else 2 * ((c["K"] + c["g"] - 1) // c["g"]) + 3 for c in self.cases)
         self.h2d = sum(h.numel() * 2 for h in self.host_x)
         self.d2h = sum(h.numel() * 2 for h in self.host_y)
         self.step_no = 0
         self.eager = False
+        self.split_k = 0
         self.graphs = {}
         if reference:
             from oracle import fishref
@@ -165,7 +166,7 @@ class DecodeSweep:
                                                 self.dev_x[i].data_ptr(), self.dev_y[i].data_ptr(), c["N"], c["M"],
                                                 c["K"], s)
         else:
-            self.ctx.linear(W, S, c["g"], self.dev_x[i], self.dev_y[i], c["M"], c["N"], c["K"])
+            self.ctx.linear(W, S, c["g"], self.dev_x[i], self.dev_y[i], c["M"], c["N"], c["K"], split_k=self.split_k)
 
     def one_pass(self, parity, e2e):
         for i, c in enumerate(self.cases):
@@ -262,6 +263,7 @@ def main():
     ap.add_argument("--only", default=None, metavar="NAME:M:G",
                     help="restrict the sweep to one case, e.g. gate_up:16:256 (for profiling)")
     ap.add_argument("--no-detail", action="store_true", help="skip the per-case timings")
+    ap.add_argument("--split-k", type=int, default=0, help="force the GEMV's K-slice count (tuning aid)")
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -303,6 +305,7 @@ def main():
         wl = DecodeSweep(torch, ctx)
 
     wl.eager = args.eager
+    wl.split_k = args.split_k
 
     def barrier():
         if dist is not None:

@@ -1,6 +1,7 @@
 // C ABI of libw8a8 (see include/w8a8.h): argument checks, kernel choice, scratch layout.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <new>
 
 #include "w8a8_internal.h"
@@ -10,7 +11,12 @@ struct w8a8_ctx {
     unsigned char* workspace = nullptr;
     size_t workspace_bytes = 0;
     int* device_status = nullptr;  // set by kernels whose bounded waits run out
+    void* splitk_partials = nullptr;  // per-warp fp32 partial tiles of the stream-K GEMV
+    int* splitk_counters = nullptr;   // one arrival counter per 16-row tile, zero between launches
 };
+
+static constexpr size_t kSplitkPartialBytes = size_t(16) << 20;
+static constexpr size_t kSplitkCounters = size_t(1) << 18;
 
 namespace w8a8 {
 
@@ -22,6 +28,14 @@ int fail(int status, const char* fmt, ...) {
     vsnprintf(g_error, sizeof g_error, fmt, ap);
     va_end(ap);
     return status;
+}
+
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* v = std::getenv("W8A8_NO_PDL");
+        return !(v && *v && *v != '0');
+    }();
+    return on;
 }
 
 int check_launch(const char* what) {
@@ -57,7 +71,7 @@ static int check_linear_common(const w8a8_ctx* ctx, const void* W, const void* w
             return fail(W8A8_ERR_INVALID_ARG, "W8A8_EPI_SWIGLU needs N %% 16 == 0 (got %d)", N);
         if (o->act_mode != W8A8_ACT_PER_TOKEN_GROUP && o->act_mode != W8A8_ACT_PER_TOKEN)
             return fail(W8A8_ERR_INVALID_ARG, "unknown act_mode %d", o->act_mode);
-        if (o->kernel < W8A8_KERNEL_AUTO || o->kernel > W8A8_KERNEL_GEMM)
+        if (o->kernel < W8A8_KERNEL_AUTO || o->kernel > W8A8_KERNEL_GEMV_TMA)
             return fail(W8A8_ERR_INVALID_ARG, "unknown kernel %d", o->kernel);
     }
     return W8A8_OK;
@@ -88,14 +102,21 @@ int dispatch_linear_q(const LinearArgs& a, int kernel, int* device_status, cudaS
         case W8A8_KERNEL_GENERIC: return launch_linear_generic(a, s);
         case W8A8_KERNEL_GEMV: return launch_linear_gemv(a, s);
         case W8A8_KERNEL_GEMM: return launch_linear_gemm(a, device_status, s);
+        case W8A8_KERNEL_GEMV_TMA: return launch_linear_gemv_tma(a, device_status, s);
         default: break;
     }
+    if (a.M <= 32 && gemv_tma_supports(a)) return launch_linear_gemv_tma(a, device_status, s);
     if (a.M <= 32 && gemv_supports(a)) return launch_linear_gemv(a, s);
     if (gemm_supports(a)) return launch_linear_gemm(a, device_status, s);
     return launch_linear_generic(a, s);
 }
 
-static int dispatch_q(w8a8_ctx* ctx, const LinearArgs& a, int kernel, cudaStream_t s) {
+static int dispatch_q(w8a8_ctx* ctx, const LinearArgs& args, int kernel, cudaStream_t s) {
+    LinearArgs a = args;
+    a.splitk_partials = ctx->splitk_partials;
+    a.splitk_partial_bytes = kSplitkPartialBytes;
+    a.splitk_counters = ctx->splitk_counters;
+    a.splitk_counter_count = kSplitkCounters;
     return dispatch_linear_q(a, kernel, ctx->device_status, s);
 }
 
@@ -147,10 +168,15 @@ int w8a8_create(w8a8_ctx** out, int device, size_t workspace_bytes) {
     e = cudaMalloc(&c->workspace, c->workspace_bytes);
     if (e == cudaSuccess) e = cudaMalloc(&c->device_status, sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->device_status, 0, sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&c->splitk_partials, kSplitkPartialBytes);
+    if (e == cudaSuccess) e = cudaMalloc(&c->splitk_counters, kSplitkCounters * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(c->splitk_counters, 0, kSplitkCounters * sizeof(int));
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
         cudaFree(c->workspace);
         cudaFree(c->device_status);
+        cudaFree(c->splitk_partials);
+        cudaFree(c->splitk_counters);
         delete c;
         return fail(W8A8_ERR_CUDA, "context allocation: %s", cudaGetErrorString(e));
     }
@@ -162,6 +188,8 @@ int w8a8_destroy(w8a8_ctx* ctx) {
     if (!ctx) return W8A8_OK;
     cudaFree(ctx->workspace);
     cudaFree(ctx->device_status);
+    cudaFree(ctx->splitk_partials);
+    cudaFree(ctx->splitk_counters);
     delete ctx;
     return W8A8_OK;
 }
@@ -265,17 +293,8 @@ int w8a8_linear(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_siz
     const int act_mode = opts ? opts->act_mode : W8A8_ACT_PER_TOKEN_GROUP;
     const int kernel = opts ? opts->kernel : W8A8_KERNEL_AUTO;
 
-    // Small M: one launch, the GEMV quantises its own K-slice.
-    if ((kernel == W8A8_KERNEL_AUTO || kernel == W8A8_KERNEL_GEMV) && M <= 32 &&
-        act_mode == W8A8_ACT_PER_TOKEN_GROUP) {
-        LinearArgs f = a;
-        f.X = static_cast<const __half*>(X);
-        f.smooth_inv = static_cast<const __half*>(smooth_inv);
-        f.act_scale = static_cast<const __half*>(act_scale);
-        if (gemv_supports(f)) return launch_linear_gemv(f, s);
-    }
-
-    // Otherwise: codes and scales into the context's scratch, then the integer kernel.
+    // Codes and scales into the context's scratch (row kernel), then the integer kernel; the two are
+    // chained with programmatic dependent launch, so the second starts streaming weights early.
     const size_t need = quant_scratch_bytes(M, K, group_size);
     if (need > ctx->workspace_bytes)
         return fail(W8A8_ERR_WORKSPACE, "need %zu bytes of scratch, context has %zu", need, ctx->workspace_bytes);

@@ -1,7 +1,8 @@
 // Small-M (decode) W8A8 linear: a weight-streaming kernel bound by HBM bandwidth.
 //
 // Replaces int8_matvec_dequant_kernel / int8_smallbatch_dequant_kernel and, for
-// 4 < tokens <= 32, the per-group cuBLAS loop of int8_gemm.cu:245-505.
+// 4 < tokens <= 32, the per-group cuBLAS loop of int8_gemm.cu:245-505. Input is the
+// activation codes and scales (int8_gemm.cu:147-211 is the row kernel in w8a8_quant.cu).
 //
 // Work split: grid = (row tiles of 64 weight rows) x (S slices of K); the S CTAs
 // that share a row tile form one thread-block cluster and add their fp32 partial
@@ -13,13 +14,15 @@
 // feed mma.sync.m16n8k32.s8 as the A operand with the tokens as the 8-wide B
 // operand. Integer dot products do not care in which order K is visited, so the
 // kernel lets "MMA k index" be a permutation of the real k that makes every
-// load 128-bit and contiguous; activations are read with the same permutation.
-// The int32 sums of one K-group are exact and complete inside one warp; they are
-// promoted with acc = fma(float(P) * ws, xs, acc) in ascending group order.
+// load 128-bit and contiguous; activation codes are read with the same
+// permutation, straight from global memory: they are a few KB shared by every
+// CTA, so after first touch they are L1 hits. The int32 sums of one K-group are
+// exact and complete inside one warp; they are promoted with
+// acc = fma(float(P) * ws, xs, acc) in ascending group order.
 //
-// The activation slice comes either as int8 codes + fp32 scales, or as fp16
-// that the CTA quantises for itself in its prologue (per (token, K-group) scales
-// only — every group lies wholly inside one slice, so no exchange is needed).
+// Launched with programmatic dependent launch: the first weight block is
+// requested before griddepcontrol.wait, i.e. while the kernel that produces the
+// activations is still running. Weights must not be written by that kernel.
 #include <cooperative_groups.h>
 
 #include "w8a8_internal.h"
@@ -37,11 +40,8 @@ constexpr int kNumSMs = 148;
 
 struct GemvParams {
     LinearArgs a;
-    int S;           // K-slices per row tile = cluster size along y
-    int bpg;         // 256-byte blocks per group when g >= 256
-    int xq_pitch;    // bytes per token row of the staged codes
-    int xs_pitch;    // floats per token row of the staged scales
-    int max_slice_groups;
+    int S;    // K-slices per row tile = cluster size along y
+    int bpg;  // 256-byte blocks per group when g >= 256
 };
 
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -52,8 +52,13 @@ __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, ui
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+// Weights are read once: stream them past L1.
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
-    return __ldcs(reinterpret_cast<const uint4*>(p));
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+                 : "l"(p));
+    return v;
 }
 
 struct WBlock {  // one lane's share of 4 K-chunks of its two rows, plus the scales they need
@@ -63,13 +68,12 @@ struct WBlock {  // one lane's share of 4 K-chunks of its two rows, plus the sca
 
 // CPG: 64-byte chunks per group when that is 1, 2 or 4 (g = 64, 128, 256); 0 means
 // g is a multiple of 256 larger than 256 and p.bpg counts 256-byte blocks per group.
-template <int MT, int CPG, bool FUSED>
+template <int MT, int CPG>
 __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
-    extern __shared__ __align__(16) unsigned char smem[];
+    __shared__ float part_s[MT * 8 * kPartPitch];
     const LinearArgs& a = p.a;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int gq = lane >> 2, c = lane & 3;
-    constexpr int TOK = MT * 8;
 
     // ---- this CTA's share: rows [n0, n0+64), groups [j0, j0+nj) ----
     const int S = p.S, s = blockIdx.y;
@@ -78,14 +82,9 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
     const int nj = base + (s < rem ? 1 : 0);
     const int g = a.g;
     const int k0 = j0 * g;
-    const int slice_bytes = nj * g;
-    const int total_chunks = slice_bytes / 64;
+    const int total_chunks = nj * (g / 64);
     const int n0 = blockIdx.x * kTileRows;
     constexpr int GPB = CPG == 0 ? 1 : 4 / CPG;  // group boundaries that can fall inside one block
-
-    unsigned char* xq_s = smem;
-    float* xs_s = reinterpret_cast<float*>(smem + static_cast<size_t>(TOK) * p.xq_pitch);
-    float* part_s = xs_s + TOK * p.xs_pitch;
 
     const int rowA_raw = n0 + warp * 16 + gq;
     const int rowA = min(rowA_raw, a.N - 1), rowB = min(rowA_raw + 8, a.N - 1);
@@ -116,84 +115,19 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
     // Weights do not depend on the kernel before this one: start streaming them at once.
     WBlock w0, w1;
     load_block(0, w0);
+    load_block(1, w1);
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
-    // ---- stage the activation slice ----
-    if (FUSED) {
-        // Quantise X[:, k0:k0+slice) here: int8_gemm.cu:147-211 per (token, group).
-        const int vpg = g / 8;  // 16-byte vectors per group
-        int lpp = 32;           // lanes per (token, group) pair: largest power of two <= min(32, vpg)
-        while (lpp > vpg) lpp >>= 1;
-        const int ppw = 32 / lpp, sub = lane % lpp, which = lane / lpp;
-        const int pairs = a.M * nj;
-        for (int pr0 = warp * ppw; pr0 < pairs; pr0 += kWarps * ppw) {
-            const int pr = pr0 + which;
-            const bool live = pr < pairs;
-            const int m = live ? pr / nj : 0, jl = live ? pr % nj : 0;
-            const __half* xg = a.X + static_cast<size_t>(m) * a.K + k0 + jl * g;
-            const __half* sm = a.smooth_inv ? a.smooth_inv + k0 + jl * g : nullptr;
-            float amax = 0.0f;
-            if (live && !a.act_scale) {
-                for (int v = sub; v < vpg; v += lpp) {
-                    uint4 u = *reinterpret_cast<const uint4*>(xg + v * 8);
-                    const __half* h = reinterpret_cast<const __half*>(&u);
+    // Token rows past M read the last real row; their results are never stored.
+    const int8_t* xq[MT];
+    const float* xsp[MT][2];
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        float f = __half2float(h[e]);
-                        if (sm) f *= __half2float(sm[v * 8 + e]);
-                        amax = fmaxf(amax, fabsf(f));
-                    }
-                }
-            }
-            for (int o = lpp / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-            float scale = a.act_scale ? __half2float(a.act_scale[j0 + jl]) : amax / 127.0f;
-            if (scale < 1e-8f) scale = 1e-8f;
-            const float inv_scale = 1.0f / scale;
-            if (live) {
-                if (sub == 0) xs_s[m * p.xs_pitch + jl] = scale;
-                for (int v = sub; v < vpg; v += lpp) {
-                    uint4 u = *reinterpret_cast<const uint4*>(xg + v * 8);
-                    const __half* h = reinterpret_cast<const __half*>(&u);
-                    uint32_t lo = 0, hi = 0;
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) {
-                        float f = __half2float(h[e]);
-                        if (sm) f *= __half2float(sm[v * 8 + e]);
-                        int q = __float2int_rn(f * inv_scale);
-                        q = max(-127, min(127, q));
-                        if (e < 4) lo |= (static_cast<uint32_t>(q) & 0xffu) << (8 * e);
-                        else hi |= (static_cast<uint32_t>(q) & 0xffu) << (8 * (e - 4));
-                    }
-                    *reinterpret_cast<uint2*>(xq_s + static_cast<size_t>(m) * p.xq_pitch + jl * g + v * 8) =
-                        make_uint2(lo, hi);
-                }
-            }
-        }
-    } else {
-        const int vec_per_row = slice_bytes / 16;
-        for (int i = tid; i < a.M * vec_per_row; i += kThreads) {
-            const int m = i / vec_per_row, v = i % vec_per_row;
-            *reinterpret_cast<uint4*>(xq_s + static_cast<size_t>(m) * p.xq_pitch + v * 16) =
-                *reinterpret_cast<const uint4*>(a.Xq + static_cast<size_t>(m) * a.K + k0 + v * 16);
-        }
-        for (int i = tid; i < a.M * nj; i += kThreads) {
-            const int m = i / nj, jl = i % nj;
-            xs_s[m * p.xs_pitch + jl] = a.Xs[static_cast<size_t>(m) * a.G + j0 + jl];
-        }
+    for (int nt = 0; nt < MT; ++nt) {
+        xq[nt] = a.Xq + static_cast<size_t>(min(nt * 8 + gq, a.M - 1)) * a.K + k0 + c * 16;
+        xsp[nt][0] = a.Xs + static_cast<size_t>(min(nt * 8 + 2 * c, a.M - 1)) * a.G + j0;
+        xsp[nt][1] = a.Xs + static_cast<size_t>(min(nt * 8 + 2 * c + 1, a.M - 1)) * a.G + j0;
     }
-    // Token rows past M take part in the MMA as zeros.
-    {
-        const int vec_per_row = slice_bytes / 16;
-        for (int i = tid; i < (TOK - a.M) * vec_per_row; i += kThreads) {
-            const int m = a.M + i / vec_per_row, v = i % vec_per_row;
-            *reinterpret_cast<uint4*>(xq_s + static_cast<size_t>(m) * p.xq_pitch + v * 16) = make_uint4(0, 0, 0, 0);
-        }
-        for (int i = tid; i < (TOK - a.M) * nj; i += kThreads)
-            xs_s[(a.M + i / nj) * p.xs_pitch + i % nj] = 0.0f;
-    }
-    __syncthreads();
 
-    // ---- main loop ----
     int P[MT][4];
     float acc[MT][4];
 #pragma unroll
@@ -205,10 +139,9 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
         const float fa = __half2float(hsa), fb = __half2float(hsb);
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt) {
-            const int t0 = nt * 8 + 2 * c;
-            const float x0 = xs_s[t0 * p.xs_pitch + jl], x1 = xs_s[(t0 + 1) * p.xs_pitch + jl];
+            const float x0 = __ldg(xsp[nt][0] + jl), x1 = __ldg(xsp[nt][1] + jl);
             if (a.dump) {
-                const int j = j0 + jl;
+                const int t0 = nt * 8 + 2 * c, j = j0 + jl;
                 const size_t NG = static_cast<size_t>(a.N) * a.G;
                 if (rowA_raw < a.N) {
                     if (t0 < a.M) a.dump[t0 * NG + static_cast<size_t>(rowA_raw) * a.G + j] = P[nt][0];
@@ -228,24 +161,36 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
     };
 
     auto process = [&](int blk, const WBlock& w) {
+        // Activation codes come from L1; request a whole block's worth up front (two chunks at a
+        // time when 32 tokens make that too many registers).
+        constexpr int XB = MT <= 2 ? 4 : 2;
+        uint4 xv[XB][MT];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int t = blk * 4 + i;
-            if (t < total_chunks) {
+        for (int i0 = 0; i0 < 4; i0 += XB) {
 #pragma unroll
-                for (int nt = 0; nt < MT; ++nt) {
-                    const uint4 xv = *reinterpret_cast<const uint4*>(
-                        xq_s + static_cast<size_t>(nt * 8 + gq) * p.xq_pitch + t * 64 + c * 16);
-                    mma_s8(P[nt], w.a[i].x, w.b[i].x, w.a[i].y, w.b[i].y, xv.x, xv.y);
-                    mma_s8(P[nt], w.a[i].z, w.b[i].z, w.a[i].w, w.b[i].w, xv.z, xv.w);
-                }
-                if (CPG != 0) {
-                    if ((i + 1) % (CPG == 0 ? 1 : CPG) == 0) {
-                        const int q = i / (CPG == 0 ? 1 : CPG);
-                        promote(blk * GPB + q, w.sa[q], w.sb[q]);
+            for (int i = 0; i < XB; ++i)
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt)
+                    if (blk * 4 + i0 + i < total_chunks)
+                        xv[i][nt] = __ldg(reinterpret_cast<const uint4*>(xq[nt] + (blk * 4 + i0 + i) * 64));
+#pragma unroll
+            for (int ii = 0; ii < XB; ++ii) {
+                const int i = i0 + ii;
+                const int t = blk * 4 + i;
+                if (t < total_chunks) {
+#pragma unroll
+                    for (int nt = 0; nt < MT; ++nt) {
+                        mma_s8(P[nt], w.a[i].x, w.b[i].x, w.a[i].y, w.b[i].y, xv[ii][nt].x, xv[ii][nt].y);
+                        mma_s8(P[nt], w.a[i].z, w.b[i].z, w.a[i].w, w.b[i].w, xv[ii][nt].z, xv[ii][nt].w);
                     }
-                } else if (i == 3 && (blk + 1) % p.bpg == 0) {
-                    promote(blk / p.bpg, w.sa[0], w.sb[0]);
+                    if (CPG != 0) {
+                        if ((i + 1) % (CPG == 0 ? 1 : CPG) == 0) {
+                            const int q = i / (CPG == 0 ? 1 : CPG);
+                            promote(blk * GPB + q, w.sa[q], w.sb[q]);
+                        }
+                    } else if (i == 3 && (blk + 1) % p.bpg == 0) {
+                        promote(blk / p.bpg, w.sa[0], w.sb[0]);
+                    }
                 }
             }
         }
@@ -253,10 +198,10 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
 
     const int nblk = (total_chunks + 3) / 4;
     for (int blk = 0; blk < nblk; blk += 2) {
-        load_block(blk + 1, w1);
         process(blk, w0);
         load_block(blk + 2, w0);
         process(blk + 1, w1);
+        load_block(blk + 3, w1);
     }
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
@@ -314,20 +259,15 @@ __global__ void __launch_bounds__(kThreads) gemv_kernel(const GemvParams p) {
 }
 
 struct Plan {
-    int MT, CPG, S, bpg, xq_pitch, xs_pitch, max_slice_groups;
-    size_t smem;
+    int MT, CPG, S, bpg;
 };
 
 bool make_plan(const LinearArgs& a, Plan& pl) {
-    if (a.M < 1 || a.M > 32) return false;
+    if (a.M < 1 || a.M > 32 || !a.Xq || !a.Xs) return false;
     if (a.K % 64 != 0 || a.g % 64 != 0 || a.K % a.g != 0) return false;
     if (a.g > 256 && a.g % 256 != 0) return false;
     if (a.g == 192) return false;
-    const bool fused = a.Xq == nullptr;
-    uintptr_t al = reinterpret_cast<uintptr_t>(a.W);
-    if (fused) al |= reinterpret_cast<uintptr_t>(a.X);
-    else al |= reinterpret_cast<uintptr_t>(a.Xq);
-    if (al & 15u) return false;
+    if ((reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.Xq)) & 15u) return false;
     if (a.epilogue == W8A8_EPI_SWIGLU && a.N % 16 != 0) return false;
     pl.MT = a.M <= 8 ? 1 : (a.M <= 16 ? 2 : 4);
     pl.CPG = a.g == 64 ? 1 : a.g == 128 ? 2 : a.g == 256 ? 4 : 0;
@@ -348,58 +288,37 @@ bool make_plan(const LinearArgs& a, Plan& pl) {
     }
     if (S > 8 || S > a.G || S < 1) return false;
     pl.S = S;
-    pl.max_slice_groups = (a.G + S - 1) / S;
-    const int slice_bytes = pl.max_slice_groups * a.g;
-    pl.xq_pitch = (slice_bytes % 128 == 0) ? slice_bytes + 64 : slice_bytes;  // == 64 mod 128
-    pl.xs_pitch = pl.max_slice_groups | 1;
-    const int TOK = pl.MT * 8;
-    pl.smem = static_cast<size_t>(TOK) * pl.xq_pitch + sizeof(float) * TOK * pl.xs_pitch +
-              sizeof(float) * TOK * kPartPitch;
-    pl.smem = (pl.smem + 15) & ~size_t(15);
-    return pl.smem <= 200 * 1024;
+    return true;
 }
 
-template <int MT, int CPG, bool FUSED>
+template <int MT, int CPG>
 int launch_variant(const GemvParams& p, const Plan& pl, cudaStream_t stream) {
-    auto kern = gemv_kernel<MT, CPG, FUSED>;
-    if (pl.smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(pl.smem));
-        if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((p.a.N + kTileRows - 1) / kTileRows, pl.S, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = pl.smem;
+    cfg.dynamicSmemBytes = 0;
     cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 1;
     attr[0].val.clusterDim.y = pl.S;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_kernel<MT, CPG>, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "gemv launch: %s", cudaGetErrorString(e));
     return W8A8_OK;
 }
 
-template <int MT, bool FUSED>
+template <int MT>
 int launch_cpg(const GemvParams& p, const Plan& pl, cudaStream_t s) {
     switch (pl.CPG) {
-        case 1: return launch_variant<MT, 1, FUSED>(p, pl, s);
-        case 2: return launch_variant<MT, 2, FUSED>(p, pl, s);
-        case 4: return launch_variant<MT, 4, FUSED>(p, pl, s);
-        default: return launch_variant<MT, 0, FUSED>(p, pl, s);
-    }
-}
-
-template <bool FUSED>
-int launch_mt(const GemvParams& p, const Plan& pl, cudaStream_t s) {
-    switch (pl.MT) {
-        case 1: return launch_cpg<1, FUSED>(p, pl, s);
-        case 2: return launch_cpg<2, FUSED>(p, pl, s);
-        default: return launch_cpg<4, FUSED>(p, pl, s);
+        case 1: return launch_variant<MT, 1>(p, pl, s);
+        case 2: return launch_variant<MT, 2>(p, pl, s);
+        case 4: return launch_variant<MT, 4>(p, pl, s);
+        default: return launch_variant<MT, 0>(p, pl, s);
     }
 }
 
@@ -417,10 +336,11 @@ int launch_linear_gemv(const LinearArgs& a, cudaStream_t s) {
     p.a = a;
     p.S = pl.S;
     p.bpg = pl.bpg;
-    p.xq_pitch = pl.xq_pitch;
-    p.xs_pitch = pl.xs_pitch;
-    p.max_slice_groups = pl.max_slice_groups;
-    return a.Xq ? launch_mt<false>(p, pl, s) : launch_mt<true>(p, pl, s);
+    switch (pl.MT) {
+        case 1: return launch_cpg<1>(p, pl, s);
+        case 2: return launch_cpg<2>(p, pl, s);
+        default: return launch_cpg<4>(p, pl, s);
+    }
 }
 
 }  // namespace w8a8

@@ -15,6 +15,8 @@ namespace w8a8 {
 int fail(int status, const char* fmt, ...);
 // cudaGetLastError() after a launch -> status.
 int check_launch(const char* what);
+// Programmatic dependent launch is on unless the environment says W8A8_NO_PDL=1 (debugging aid).
+bool pdl_enabled();
 
 inline int norm_group(int K, int group_size) {
     return (group_size <= 0 || group_size > K) ? K : group_size;
@@ -38,6 +40,11 @@ struct LinearArgs {
     int M, N, K, g, G;
     int epilogue;
     int split_k;
+    // scratch for kernels that cut K across CTAs (owned by the context; null: such kernels are not used)
+    void* splitk_partials;
+    size_t splitk_partial_bytes;
+    int* splitk_counters;        // zero between launches
+    size_t splitk_counter_count;
 };
 
 // w8a8_api.cu : picks the kernel for a linear whose codes and scales exist.
@@ -58,6 +65,9 @@ int launch_linear_generic(const LinearArgs& a, cudaStream_t s);
 // w8a8_gemv.cu : M <= 32.
 bool gemv_supports(const LinearArgs& a);
 int launch_linear_gemv(const LinearArgs& a, cudaStream_t s);
+// w8a8_gemv_tma.cu : M <= 32, TMA-fed persistent stream-K form.
+bool gemv_tma_supports(const LinearArgs& a);
+int launch_linear_gemv_tma(const LinearArgs& a, int* device_status, cudaStream_t s);
 // w8a8_gemm_sm100.cu : tcgen05 + TMA.
 bool gemm_supports(const LinearArgs& a);
 int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t s);

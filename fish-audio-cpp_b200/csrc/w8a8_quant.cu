@@ -47,6 +47,9 @@ __global__ void __launch_bounds__(1024) rowquant_kernel(const RowQuantParams p) 
     const int T = blockDim.x;
     const int K = p.K;
     const size_t base = static_cast<size_t>(blockIdx.x) * K;
+    // Let the next kernel in the stream start its own prologue; wait for the one before this.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     // ---- stage the row (+ residual add, rounded to fp16 like residual_add_kernel) ----
     if (p.vec_ok) {
@@ -183,6 +186,73 @@ __global__ void __launch_bounds__(1024) rowquant_kernel(const RowQuantParams p) 
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// The quantiser alone (int8_gemm.cu:147-211) for g in {64, 128, 256}: no shared memory, no block
+// barrier. A thread owns 8 consecutive activations (one 128-bit load), the g/8 threads of a group
+// find the absmax with shuffles, and each thread stores its 8 codes as one 64-bit word. At decode
+// sizes the whole activation matrix is a few KB, so what counts is the length of the dependency
+// chain (one load, log2(g/8) shuffles, one divide, one store), not bandwidth.
+template <int LANES>  // threads per group = g / 8
+__global__ void __launch_bounds__(128) groupquant_kernel(const __half* __restrict__ X,
+                                                         const __half* __restrict__ smooth_inv,
+                                                         const __half* __restrict__ act_scale,
+                                                         int8_t* __restrict__ Xq, float* __restrict__ Xs, int K,
+                                                         int G) {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const int m = blockIdx.y;
+    const int e = (blockIdx.x * 128 + threadIdx.x) * 8;
+    const bool live = e < K;
+    float v[8];
+    float amax = 0.0f;
+    if (live) {
+        const uint4 u = *reinterpret_cast<const uint4*>(X + static_cast<size_t>(m) * K + e);
+        const __half* h = reinterpret_cast<const __half*>(&u);
+        uint4 su = make_uint4(0, 0, 0, 0);
+        if (smooth_inv) su = *reinterpret_cast<const uint4*>(smooth_inv + e);
+        const __half* sh = reinterpret_cast<const __half*>(&su);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            v[i] = __half2float(h[i]);
+            if (smooth_inv) v[i] *= __half2float(sh[i]);
+            amax = fmaxf(amax, fabsf(v[i]));
+        }
+    }
+#pragma unroll
+    for (int o = LANES / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (!live) return;
+    const int j = e / (LANES * 8);
+    float scale = act_scale ? __half2float(act_scale[j]) : amax / 127.0f;
+    if (scale < 1e-8f) scale = 1e-8f;
+    if ((threadIdx.x & (LANES - 1)) == 0) Xs[static_cast<size_t>(m) * G + j] = scale;
+    const float inv_scale = 1.0f / scale;
+    uint32_t lo = 0, hi = 0;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        int q = __float2int_rn(v[i] * inv_scale);
+        q = max(-127, min(127, q));
+        if (i < 4) lo |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
+        else hi |= (static_cast<uint32_t>(q) & 0xffu) << (8 * (i - 4));
+    }
+    *reinterpret_cast<uint2*>(Xq + static_cast<size_t>(m) * K + e) = make_uint2(lo, hi);
+}
+
+template <int LANES>
+int launch_groupquant(const __half* X, const __half* smooth_inv, const __half* act_scale, int8_t* Xq, float* Xs,
+                      int M, int K, int G, cudaStream_t stream) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((K + 1023) / 1024, M, 1);
+    cfg.blockDim = dim3(128, 1, 1);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, groupquant_kernel<LANES>, X, smooth_inv, act_scale, Xq, Xs, K, G);
+    if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "groupquant launch: %s", cudaGetErrorString(e));
+    return W8A8_OK;
+}
+
 }  // namespace
 
 int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
@@ -190,6 +260,17 @@ int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
                     const __half* act_scale, int M, int K, int g, int act_mode, __half* normed_out,
                     int8_t* Xq, float* Xs, cudaStream_t stream) {
     if (M == 0) return W8A8_OK;
+    {   // the quantiser alone, common group sizes: the barrier-free kernel
+        const int gn = norm_group(K, g);
+        if (!residual && !norm_weight && !normed_out && Xq && act_mode == W8A8_ACT_PER_TOKEN_GROUP &&
+            (gn == 64 || gn == 128 || gn == 256) && K % gn == 0 && M <= 65535 && aligned16(x_in) &&
+            (reinterpret_cast<uintptr_t>(Xq) & 7u) == 0 && (!smooth_inv || aligned16(smooth_inv))) {
+            const int G = K / gn;
+            if (gn == 64) return launch_groupquant<8>(x_in, smooth_inv, act_scale, Xq, Xs, M, K, G, stream);
+            if (gn == 128) return launch_groupquant<16>(x_in, smooth_inv, act_scale, Xq, Xs, M, K, G, stream);
+            return launch_groupquant<32>(x_in, smooth_inv, act_scale, Xq, Xs, M, K, G, stream);
+        }
+    }
     RowQuantParams p;
     p.x_in = x_in;
     p.x_out = x_out;
@@ -224,8 +305,19 @@ int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
                                              static_cast<int>(smem));
         if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     }
-    rowquant_kernel<<<M, threads, smem, stream>>>(p);
-    return check_launch("rowquant_kernel");
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(M, 1, 1);
+    cfg.blockDim = dim3(threads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, rowquant_kernel, p);
+    if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "rowquant launch: %s", cudaGetErrorString(e));
+    return W8A8_OK;
 }
 
 }  // namespace w8a8

@@ -87,8 +87,9 @@ enum { /* what happens to the fp32 accumulator after the last group */
 enum { /* forces a kernel family; default picks by shape */
     W8A8_KERNEL_AUTO = 0,
     W8A8_KERNEL_GENERIC = 1, /* scalar-order SIMT kernel, any shape */
-    W8A8_KERNEL_GEMV = 2,    /* M <= 32: warp-MMA weight-streaming kernel */
-    W8A8_KERNEL_GEMM = 3     /* tcgen05 + TMA kernel */
+    W8A8_KERNEL_GEMV = 2,    /* M <= 32: warp-MMA weight-streaming kernel, cluster split-K */
+    W8A8_KERNEL_GEMM = 3,    /* tcgen05 + TMA kernel */
+    W8A8_KERNEL_GEMV_TMA = 4 /* M <= 32: TMA-fed persistent stream-K kernel (the default when it fits) */
 };
 
 typedef struct w8a8_linear_opts {

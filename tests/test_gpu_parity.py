@@ -243,6 +243,45 @@ def test_gemv_small_shapes(ctx, oracle, pkg, M, N, K, g, fused_quant):
     assert_close_fp16(oracle, Y, oracle.linear_q(W, ws, Xq, Xs, g), "gemv")
 
 
+TMA_SHAPES = [(1, 128, 256, 64), (4, 200, 512, 128), (8, 64, 2560, 256), (9, 192, 1024, 256), (16, 256, 2560, 2560),
+              (17, 96, 768, 64), (32, 128, 768, 256), (3, 72, 512, 512), (5, 8, 256, 256), (16, 1000, 1280, 64),
+              (2, 48, 1024, 1024), (7, 40, 9728, 256)]
+
+
+@pytest.mark.parametrize("M,N,K,g", TMA_SHAPES)
+def test_gemv_tma_small_shapes(ctx, oracle, pkg, M, N, K, g):
+    """The stream-K TMA kernel: tiles cut by warp-range boundaries, N not a multiple of 16, every
+    group-size branch; two runs must agree bit for bit (the partial sums are added in a fixed order)."""
+    (X, W, ws, Xq, Xs), Y, P = run_linear(ctx, oracle, M, N, K, g, seed=M + N, kernel=pkg.KERNEL_GEMV_TMA)
+    Pw = oracle.group_sums(W, Xq, g)
+    assert np.array_equal(P, Pw), "per-group int32 sums must be bit-exact"
+    assert_close_fp16(oracle, Y, oracle.linear_q(W, ws, Xq, Xs, g), "gemv_tma", abs_terms=abs_term_sum(Pw, ws, Xs))
+    _, Y2, _ = run_linear(ctx, oracle, M, N, K, g, seed=M + N, kernel=pkg.KERNEL_GEMV_TMA)
+    assert np.array_equal(Y.view(np.uint16), Y2.view(np.uint16))
+    ctx.check_device_status()
+
+
+def test_gemv_tma_epilogues(ctx, oracle, pkg):
+    M, inter, K, g = 8, 192, 512, 256
+    rng = np.random.default_rng(19)
+    X = synth.activations(rng, M, K)
+    wg, wu = synth.weights(rng, inter, K), synth.weights(rng, inter, K)
+    sg, su = synth.weight_scales(rng, inter, K // g), synth.weight_scales(rng, inter, K // g)
+    Wp, Sp = oracle.pack_gate_up(wg, sg, wu, su)
+    dX = dev(X)
+    dA = torch.empty((M, inter), dtype=torch.float16, device="cuda")
+    ctx.linear(dev(Wp), dev(Sp), g, dX, dA, M, 2 * inter, K, epilogue=pkg.EPI_SWIGLU, kernel=pkg.KERNEL_GEMV_TMA)
+    torch.cuda.synchronize()
+    assert oracle.ulp_distance_fp16(dA.cpu().numpy(), oracle.linear(Wp, Sp, g, X, epilogue=oracle.EPI_SWIGLU)).max() <= 2
+    R = rng.standard_normal((M, inter)).astype(np.float16)
+    dR = dev(R)
+    ctx.linear(dev(wg), dev(sg), g, dX, dR, M, inter, K, epilogue=pkg.EPI_RESIDUAL, residual=dR,
+               kernel=pkg.KERNEL_GEMV_TMA)
+    torch.cuda.synchronize()
+    want = oracle.linear(wg, sg, g, X, epilogue=oracle.EPI_RESIDUAL, residual=R)
+    assert oracle.ulp_distance_fp16(dR.cpu().numpy(), want).max() <= 2
+
+
 @pytest.mark.parametrize("split_k", [1, 2, 3, 4, 5, 8])
 def test_gemv_split_k_is_deterministic_and_correct(ctx, oracle, pkg, split_k):
     M, N, K, g = 16, 320, 2560, 256
