@@ -117,7 +117,7 @@ class DecodeSweep:
 
     ROTATION_BYTES = 320e6
 
-    def __init__(self, torch, ctx, seed=1234, reference=False):
+    def __init__(self, torch, ctx, seed=1234, reference=False, pack=True):
         from fish_audio_cpp_b200 import synth
 
         self.torch, self.ctx, self.reference = torch, ctx, reference
@@ -134,6 +134,14 @@ class DecodeSweep:
                     (torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda", generator=gen),
                      torch.empty((N, G), dtype=torch.float32, device="cuda").uniform_(1e-3, 5e-3, generator=gen).half())
                     for _ in range(copies)]
+                if not reference and pack:
+                    # what a loader does once per weight: pack for the decode kernel and register the pair
+                    self.packed = getattr(self, "packed", [])
+                    for (W, S) in self.weights[(name, g)]:
+                        P = torch.empty((ctx.packed_weight_bytes(N, K, g),), dtype=torch.uint8, device="cuda")
+                        ctx.pack_weight(W, S, N, K, g, P)
+                        ctx.register_packed_weight(W, P)
+                        self.packed.append(P)
         self.host_x, self.dev_x, self.dev_y, self.host_y = [], [], [], []
         for c in self.cases:
             x = synth.activations(rng, c["M"], c["K"])
@@ -264,6 +272,7 @@ def main():
                     help="restrict the sweep to one case, e.g. gate_up:16:256 (for profiling)")
     ap.add_argument("--no-detail", action="store_true", help="skip the per-case timings")
     ap.add_argument("--split-k", type=int, default=0, help="force the GEMV's K-slice count (tuning aid)")
+    ap.add_argument("--no-pack", action="store_true", help="leave weights row-major (skip the loader-side pack)")
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a graph")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -302,7 +311,7 @@ def main():
         wl = DecodeSweep(torch, None, reference=True)
     else:
         ctx = pkg.Context(local_rank, 0)
-        wl = DecodeSweep(torch, ctx)
+        wl = DecodeSweep(torch, ctx, pack=not args.no_pack)
 
     wl.eager = args.eager
     wl.split_k = args.split_k

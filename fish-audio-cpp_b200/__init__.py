@@ -14,6 +14,7 @@ from .capi import (  # noqa: F401
     KERNEL_AUTO,
     KERNEL_GEMM,
     KERNEL_GEMV,
+    KERNEL_GEMV_PACKED,
     KERNEL_GEMV_TMA,
     KERNEL_GENERIC,
     Context,

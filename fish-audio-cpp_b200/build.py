@@ -45,8 +45,6 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) 
     LIB.parent.mkdir(exist_ok=True)
     hdr = _newest_header()
     defines = []
-    if (CSRC / "w8a8_gemm_sm100.cu").exists():
-        defines.append("-DW8A8_HAVE_GEMM_SM100")
     jobs = []
     for src in sources():
         obj = OBJ / (src.stem + ".o")

@@ -6,7 +6,7 @@ from pathlib import Path
 
 ACT_PER_TOKEN_GROUP, ACT_PER_TOKEN = 0, 1
 EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
-KERNEL_AUTO, KERNEL_GENERIC, KERNEL_GEMV, KERNEL_GEMM, KERNEL_GEMV_TMA = 0, 1, 2, 3, 4
+KERNEL_AUTO, KERNEL_GENERIC, KERNEL_GEMV, KERNEL_GEMM, KERNEL_GEMV_TMA, KERNEL_GEMV_PACKED = 0, 1, 2, 3, 4, 5
 
 _LIB = None
 
@@ -59,6 +59,9 @@ def load_library() -> C.CDLL:
         "w8a8_linear": (I, [P, P, P, I, P, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_linear_q": (I, [P, P, P, I, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_pack_gate_up": (I, [P, P, P, P, P, I, I, I, P, P, P]),
+        "w8a8_packed_weight_bytes": (Z, [I, I, I]),
+        "w8a8_pack_weight": (I, [P, P, P, I, I, I, P, P]),
+        "w8a8_register_packed_weight": (I, [P, P, P]),
         "w8a8_static_scratch_bytes": (Z, []),
         "w8a8_linear_static_scratch": (I, [P, P, I, P, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "fish_shim_int8_dequant_gemm_fp16": (I, [P, P, I, P, P, P, P, I, I, I, P, C.c_char_p, I]),
@@ -74,7 +77,8 @@ EXPORTS = [
     "w8a8_status_string", "w8a8_last_error", "w8a8_create", "w8a8_destroy", "w8a8_workspace_bytes",
     "w8a8_ctx_workspace_bytes", "w8a8_check_device_status", "w8a8_quantize", "w8a8_rms_norm",
     "w8a8_rmsnorm_quantize", "w8a8_silu", "w8a8_mul", "w8a8_residual_add", "w8a8_linear", "w8a8_linear_q",
-    "w8a8_pack_gate_up", "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch",
+    "w8a8_pack_gate_up", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
+    "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch",
 ]
 
 
@@ -200,6 +204,17 @@ class Context:
         self._check(self.lib.w8a8_pack_gate_up(self.handle, _ptr(w_gate), _ptr(s_gate), _ptr(w_up), _ptr(s_up),
                                                inter, K, G, _ptr(W_out), _ptr(scale_out), _stream(stream)),
                     "w8a8_pack_gate_up")
+
+    def packed_weight_bytes(self, N, K, group_size) -> int:
+        return self.lib.w8a8_packed_weight_bytes(N, K, group_size)
+
+    def pack_weight(self, W, w_scale, N, K, group_size, packed_out, stream=None):
+        self._check(self.lib.w8a8_pack_weight(self.handle, _ptr(W), _ptr(w_scale), N, K, group_size,
+                                              _ptr(packed_out), _stream(stream)), "w8a8_pack_weight")
+
+    def register_packed_weight(self, W, packed):
+        self._check(self.lib.w8a8_register_packed_weight(self.handle, _ptr(W), _ptr(packed)),
+                    "w8a8_register_packed_weight")
 
     def shim_int8_dequant_gemm_fp16(self, W, scale, group_size, act_scale, smooth_inv, X, Y, M_out, N_tok, K,
                                     stream=None):

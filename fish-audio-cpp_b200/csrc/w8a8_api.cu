@@ -2,7 +2,9 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
+#include <mutex>
 #include <new>
+#include <unordered_map>
 
 #include "w8a8_internal.h"
 
@@ -13,6 +15,10 @@ struct w8a8_ctx {
     int* device_status = nullptr;  // set by kernels whose bounded waits run out
     void* splitk_partials = nullptr;  // per-warp fp32 partial tiles of the stream-K GEMV
     int* splitk_counters = nullptr;   // one arrival counter per 16-row tile, zero between launches
+    // raw weight pointer -> its packed image; filled by the loader (w8a8_register_packed_weight), the
+    // same pointer-keyed lookup as DualAREngine::weight_quant_meta_ (src/engine/dual_ar_engine.h:105)
+    std::unordered_map<const void*, const void*> packed;
+    std::mutex packed_mu;
 };
 
 static constexpr size_t kSplitkPartialBytes = size_t(16) << 20;
@@ -50,12 +56,6 @@ static size_t quant_scratch_bytes(int M, int K, int group_size) {
     return align256(static_cast<size_t>(M) * K) + align256(static_cast<size_t>(M) * num_groups(K, group_size) * 4);
 }
 
-#if !defined(W8A8_HAVE_GEMM_SM100)
-bool gemm_supports(const LinearArgs&) { return false; }
-int launch_linear_gemm(const LinearArgs&, int*, cudaStream_t) {
-    return fail(W8A8_ERR_UNSUPPORTED, "tcgen05 GEMM not built into this library");
-}
-#endif
 
 static int check_linear_common(const w8a8_ctx* ctx, const void* W, const void* w_scale, const void* Y,
                                int M, int N, int K, const w8a8_linear_opts* o) {
@@ -71,7 +71,7 @@ static int check_linear_common(const w8a8_ctx* ctx, const void* W, const void* w
             return fail(W8A8_ERR_INVALID_ARG, "W8A8_EPI_SWIGLU needs N %% 16 == 0 (got %d)", N);
         if (o->act_mode != W8A8_ACT_PER_TOKEN_GROUP && o->act_mode != W8A8_ACT_PER_TOKEN)
             return fail(W8A8_ERR_INVALID_ARG, "unknown act_mode %d", o->act_mode);
-        if (o->kernel < W8A8_KERNEL_AUTO || o->kernel > W8A8_KERNEL_GEMV_TMA)
+        if (o->kernel < W8A8_KERNEL_AUTO || o->kernel > W8A8_KERNEL_GEMV_PACKED)
             return fail(W8A8_ERR_INVALID_ARG, "unknown kernel %d", o->kernel);
     }
     return W8A8_OK;
@@ -103,8 +103,10 @@ int dispatch_linear_q(const LinearArgs& a, int kernel, int* device_status, cudaS
         case W8A8_KERNEL_GEMV: return launch_linear_gemv(a, s);
         case W8A8_KERNEL_GEMM: return launch_linear_gemm(a, device_status, s);
         case W8A8_KERNEL_GEMV_TMA: return launch_linear_gemv_tma(a, device_status, s);
+        case W8A8_KERNEL_GEMV_PACKED: return launch_linear_gemv_packed(a, device_status, s);
         default: break;
     }
+    if (a.M <= 32 && gemv_packed_supports(a)) return launch_linear_gemv_packed(a, device_status, s);
     if (a.M <= 32 && gemv_tma_supports(a)) return launch_linear_gemv_tma(a, device_status, s);
     if (a.M <= 32 && gemv_supports(a)) return launch_linear_gemv(a, s);
     if (gemm_supports(a)) return launch_linear_gemm(a, device_status, s);
@@ -117,6 +119,11 @@ static int dispatch_q(w8a8_ctx* ctx, const LinearArgs& args, int kernel, cudaStr
     a.splitk_partial_bytes = kSplitkPartialBytes;
     a.splitk_counters = ctx->splitk_counters;
     a.splitk_counter_count = kSplitkCounters;
+    if (a.M <= 32 && !ctx->packed.empty()) {
+        std::lock_guard<std::mutex> lock(ctx->packed_mu);
+        auto it = ctx->packed.find(a.W);
+        if (it != ctx->packed.end()) a.packed = it->second;
+    }
     return dispatch_linear_q(a, kernel, ctx->device_status, s);
 }
 
@@ -307,6 +314,24 @@ int w8a8_linear(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_siz
     a.Xq = Xq;
     a.Xs = Xs;
     return dispatch_q(ctx, a, kernel, s);
+}
+
+size_t w8a8_packed_weight_bytes(int N, int K, int group_size) { return packed_weight_bytes(N, K, group_size); }
+
+int w8a8_pack_weight(w8a8_ctx* ctx, const void* W, const void* w_scale, int N, int K, int group_size,
+                     void* packed_out, void* stream) {
+    if (!ctx || !W || !w_scale || !packed_out) return fail(W8A8_ERR_INVALID_ARG, "pack_weight: null argument");
+    if (N <= 0 || K <= 0) return fail(W8A8_ERR_INVALID_ARG, "pack_weight: bad shape N=%d K=%d", N, K);
+    return launch_pack_weight(static_cast<const int8_t*>(W), static_cast<const __half*>(w_scale), N, K, group_size,
+                              packed_out, static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_register_packed_weight(w8a8_ctx* ctx, const void* W, const void* packed) {
+    if (!ctx || !W) return fail(W8A8_ERR_INVALID_ARG, "register_packed_weight: null argument");
+    std::lock_guard<std::mutex> lock(ctx->packed_mu);
+    if (packed) ctx->packed[W] = packed;
+    else ctx->packed.erase(W);
+    return W8A8_OK;
 }
 
 int w8a8_pack_gate_up(w8a8_ctx* ctx, const void* w_gate, const void* s_gate, const void* w_up, const void* s_up,

@@ -1,0 +1,340 @@
+// Large-M (prefill) W8A8 linear on the 5th-generation tensor cores: TMA -> shared memory ->
+// tcgen05.mma kind::i8 -> int32 accumulators in tensor memory -> fp32 promote per K-group.
+//
+// Replaces, for tokens > 32, the reference's loop of one cuBLAS int8 GEMM per K-group plus an
+// accumulate pass over the whole [tokens, rows] matrix per group and a cast pass
+// (int8_gemm.cu:423-505): here a K-group's exact int32 sums never leave the SM.
+//
+// One CTA computes a 128-token x 128-row output tile with three kinds of warps:
+//   warp 0      producer: one lane issues TMA loads of 128 x 128-byte boxes of the activation codes
+//               and of the weights (both are row-major with K contiguous, i.e. already the K-major
+//               operand; the 128-byte swizzle is applied by TMA) into a ring of kStages stages;
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (M=128, N=128, K=32 per instruction), four per
+//               128-byte stage. Each K-group accumulates into its own 128-column slice of tensor
+//               memory (4 slices = all 512 columns), starting with "overwrite"; a tcgen05.commit
+//               hands the slice to the epilogue and another frees the shared-memory stage;
+//   warps 2..5  epilogue: thread <-> token row (tensor-memory lane). For every K-group they read the
+//               int32 sums with tcgen05.ld, and promote  acc = fma(float(P) * ws[n,j], xs[m,j], acc)
+//               in ascending group order into 128 fp32 registers per thread — the arithmetic and
+//               order of accumulate_group_kernel (int8_gemm.cu:213-234) — while the MMA warp already
+//               fills the next slice. Weight scales of the group are staged in shared memory once
+//               per CTA; the final fp16 store applies the optional residual / SwiGLU epilogue.
+// Every mbarrier wait is bounded; a wait that runs out records an error word, and the CTA still
+// frees its tensor memory before it returns.
+#include "sm100_ptx.cuh"
+#include "w8a8_internal.h"
+
+namespace w8a8 {
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 128;  // BK in bytes = int8 elements
+constexpr int kStages = 5;
+constexpr int kAccStages = 4;  // 4 x 128 columns = the whole tensor memory
+constexpr int kStageBytes = (BM + BN) * BK;
+constexpr int kThreads = 192;
+constexpr uint32_t kSpin = 1u << 21;
+
+struct GemmParams {
+    LinearArgs a;
+    int* status;
+    int mmas_per_group;  // g / 32
+    int num_kblocks;     // K / 128
+};
+
+// ---- tcgen05 wrappers ----
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(ptx::smem_u32(smem_dst)),
+                 "r"(cols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     ptx::smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t"
+        "}\n" ::"r"(tmem_d),
+        "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory operand descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
+    return static_cast<uint64_t>((saddr & 0x3ffffu) >> 4) | (1ull << 16) /* leading offset (unused) */ |
+           (static_cast<uint64_t>(1024 >> 4) << 32) /* stride between 8-row groups */ | (1ull << 46) /* version */ |
+           (2ull << 61) /* SWIZZLE_128B */;
+}
+// Instruction descriptor: int8 x int8 -> int32, both operands K-major, M = 128, N = BN.
+constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
+                            (static_cast<uint32_t>(BM >> 4) << 24);
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               const GemmParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages];
+    __shared__ __align__(8) uint64_t acc_full[kAccStages], acc_empty[kAccStages];
+    __shared__ uint32_t tmem_base_s;
+    __shared__ int failed_s;
+    __shared__ __align__(16) float ws_s[2][BN];
+
+    const LinearArgs& a = p.a;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const uint32_t tiles = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int G = a.G;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full_bar[s], 1); ptx::mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < kAccStages; ++s) { ptx::mbar_init(&acc_full[s], 1); ptx::mbar_init(&acc_empty[s], 4); }
+        failed_s = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc(&tmem_base_s, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_base_s;
+    // The activation codes come from the kernel before this one (the row quantiser).
+    ptx::pdl_wait();
+
+    if (warp == 0) {
+        // ---------------- producer ----------------
+        if (lane == 0) {
+            for (int kb = 0; kb < p.num_kblocks; ++kb) {
+                const int s = kb % kStages;
+                if (kb >= kStages && !ptx::mbar_wait_bounded(&empty_bar[s], ((kb / kStages) - 1) & 1, kSpin)) {
+                    atomicExch(p.status, 200 + s);
+                    atomicExch(&failed_s, 1);
+                    break;
+                }
+                ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
+                const uint32_t dst = tiles + s * kStageBytes;
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                    ::"r"(dst), "l"(&map_x), "r"(ptx::smem_u32(&full_bar[s])), "r"(kb * BK), "r"(m0) : "memory");
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                    ::"r"(dst + BM * BK), "l"(&map_w), "r"(ptx::smem_u32(&full_bar[s])), "r"(kb * BK), "r"(n0) : "memory");
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (lane == 0) {
+            const int total_mmas = p.num_kblocks * 4;
+            int q_in_group = 0, group = 0;
+            bool ok = true;
+            for (int q = 0; q < total_mmas && ok; ++q) {
+                const int kb = q >> 2, sub = q & 3, s = kb % kStages, as = group % kAccStages;
+                if (sub == 0) {
+                    if (!ptx::mbar_wait_bounded(&full_bar[s], (kb / kStages) & 1, kSpin)) {
+                        atomicExch(p.status, 300 + s); atomicExch(&failed_s, 1); ok = false; break;
+                    }
+                    tc_fence_after();
+                }
+                if (q_in_group == 0 && group >= kAccStages) {
+                    if (!ptx::mbar_wait_bounded(&acc_empty[as], ((group / kAccStages) - 1) & 1, kSpin)) {
+                        atomicExch(p.status, 400 + as); atomicExch(&failed_s, 1); ok = false; break;
+                    }
+                    tc_fence_after();
+                }
+                const uint32_t sa = tiles + s * kStageBytes + sub * 32;
+                mma_i8(tmem_base + as * BN, smem_desc(sa), smem_desc(sa + BM * BK), kIdesc, q_in_group != 0);
+                if (sub == 3) tc_commit(&empty_bar[s]);       // the stage may be refilled once these MMAs retire
+                if (++q_in_group == p.mmas_per_group) {
+                    tc_commit(&acc_full[as]);                 // the K-group's sums are complete
+                    q_in_group = 0;
+                    ++group;
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---------------- epilogue: 4 warps, thread <-> token row ----------------
+        const int quad = warp & 3;               // the tensor-memory lane quadrant this warp may read
+        const int row = quad * 32 + lane;        // row inside the tile
+        const int m = m0 + row;
+        const int et = (warp - 2) * 32 + lane;   // 0..127: which weight row's scale this thread stages
+        const bool m_ok = m < a.M;
+        const float* xs_row = a.Xs + static_cast<size_t>(m_ok ? m : 0) * G;
+        const int ncol = min(n0 + et, a.N - 1);
+        float acc[BN];
+#pragma unroll
+        for (int c = 0; c < BN; ++c) acc[c] = 0.0f;
+        ws_s[0][et] = __half2float(a.w_scale[static_cast<size_t>(ncol) * G]);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        bool ok = true;
+        for (int j = 0; j < G && ok; ++j) {
+            const int as = j % kAccStages, cur = j & 1;
+            const float xs = xs_row[j];
+            float ws_next = 0.0f;
+            if (j + 1 < G) ws_next = __half2float(a.w_scale[static_cast<size_t>(ncol) * G + j + 1]);
+            if (!ptx::mbar_wait_bounded(&acc_full[as], (j / kAccStages) & 1, kSpin)) {
+                atomicExch(p.status, 500 + as); atomicExch(&failed_s, 1); ok = false; break;
+            }
+            tc_fence_after();
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * BN;
+#pragma unroll
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                tmem_ld32(taddr + c0, r);
+                tmem_ld_wait();
+#pragma unroll
+                for (int c = 0; c < 32; c += 4) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(&ws_s[cur][c0 + c]);
+                    acc[c0 + c + 0] = __fmaf_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[c + 0])), w4.x), xs, acc[c0 + c + 0]);
+                    acc[c0 + c + 1] = __fmaf_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[c + 1])), w4.y), xs, acc[c0 + c + 1]);
+                    acc[c0 + c + 2] = __fmaf_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[c + 2])), w4.z), xs, acc[c0 + c + 2]);
+                    acc[c0 + c + 3] = __fmaf_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[c + 3])), w4.w), xs, acc[c0 + c + 3]);
+                }
+                if (a.dump && m_ok) {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c)
+                        if (n0 + c0 + c < a.N)
+                            a.dump[(static_cast<size_t>(m) * a.N + n0 + c0 + c) * G + j] = static_cast<int>(r[c]);
+                }
+            }
+            // this slice of tensor memory may be overwritten by group j + kAccStages
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
+            ws_s[cur ^ 1][et] = ws_next;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+        }
+        // ---- final store: fp16, optional residual add or SwiGLU, 16 bytes at a time ----
+        if (ok && m_ok) {
+            if (a.epilogue == W8A8_EPI_SWIGLU) {
+                __half* yrow = a.Y + static_cast<size_t>(m) * (a.N / 2) + n0 / 2;
+#pragma unroll
+                for (int b = 0; b < BN / 16; ++b) {
+                    if (n0 + b * 16 + 16 > a.N) break;
+                    __align__(16) __half o[8];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float g16 = __half2float(__float2half(acc[b * 16 + i]));
+                        const __half s16 = __float2half(g16 / (1.0f + expf(-g16)));
+                        const float u16 = __half2float(__float2half(acc[b * 16 + 8 + i]));
+                        o[i] = __float2half(__half2float(s16) * u16);
+                    }
+                    *reinterpret_cast<uint4*>(yrow + b * 8) = *reinterpret_cast<const uint4*>(o);
+                }
+            } else {
+                __half* yrow = a.Y + static_cast<size_t>(m) * a.N + n0;
+                const __half* rrow = a.residual ? a.residual + static_cast<size_t>(m) * a.N + n0 : nullptr;
+                const bool vec = (a.N % 8) == 0;
+#pragma unroll
+                for (int b = 0; b < BN / 8; ++b) {
+                    if (n0 + b * 8 >= a.N) break;
+                    __align__(16) __half o[8];
+                    __align__(16) __half rr[8];
+                    const bool full = vec && n0 + b * 8 + 8 <= a.N;
+                    if (a.epilogue == W8A8_EPI_RESIDUAL) {
+                        if (full) *reinterpret_cast<uint4*>(rr) = *reinterpret_cast<const uint4*>(rrow + b * 8);
+                        else
+                            for (int i = 0; i < 8; ++i) rr[i] = n0 + b * 8 + i < a.N ? rrow[b * 8 + i] : __float2half(0.f);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        __half y = __float2half(acc[b * 8 + i]);
+                        if (a.epilogue == W8A8_EPI_RESIDUAL) y = __float2half(__half2float(y) + __half2float(rr[i]));
+                        o[i] = y;
+                    }
+                    if (full) *reinterpret_cast<uint4*>(yrow + b * 8) = *reinterpret_cast<const uint4*>(o);
+                    else
+                        for (int i = 0; i < 8; ++i)
+                            if (n0 + b * 8 + i < a.N) yrow[b * 8 + i] = o[i];
+                }
+            }
+        }
+    }
+    // ---- teardown: everyone meets, then the allocating warp frees the tensor memory ----
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace
+
+bool gemm_supports(const LinearArgs& a) {
+    if (a.M < 1 || !a.Xq || !a.Xs) return false;
+    if (a.K % BK != 0 || a.g % 32 != 0 || a.K % a.g != 0) return false;
+    if ((reinterpret_cast<uintptr_t>(a.W) | reinterpret_cast<uintptr_t>(a.Xq)) & 15u) return false;
+    if (a.epilogue == W8A8_EPI_SWIGLU && (a.N % 16 != 0 || (reinterpret_cast<uintptr_t>(a.Y) & 15u))) return false;
+    if (a.epilogue != W8A8_EPI_SWIGLU && a.N % 8 == 0 && (reinterpret_cast<uintptr_t>(a.Y) & 15u)) return false;
+    if (a.residual && a.N % 8 == 0 && (reinterpret_cast<uintptr_t>(a.residual) & 15u)) return false;
+    return true;
+}
+
+int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t stream) {
+    if (!gemm_supports(a)) return fail(W8A8_ERR_UNSUPPORTED, "tcgen05 GEMM does not take this shape");
+    CUtensorMap map_x, map_w;
+    int rc = make_tensor_map_2d_u8(&map_x, a.Xq, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M),
+                                   static_cast<uint64_t>(a.K), BK, BM, 1);
+    if (rc) return rc;
+    rc = make_tensor_map_2d_u8(&map_w, a.W, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N),
+                               static_cast<uint64_t>(a.K), BK, BN, 1);
+    if (rc) return rc;
+    GemmParams p;
+    p.a = a;
+    p.status = device_status;
+    p.mmas_per_group = a.g / 32;
+    p.num_kblocks = a.K / BK;
+    const size_t smem = static_cast<size_t>(kStages) * kStageBytes + 1024;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((a.N + BN - 1) / BN, (a.M + BM - 1) / BM, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_kernel, map_x, map_w, p);
+    if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
+    return W8A8_OK;
+}
+
+}  // namespace w8a8

@@ -1,0 +1,489 @@
+// Small-M (decode) W8A8 linear over PRE-PACKED weights: the HBM-roofline form.
+//
+// Same arithmetic as the other GEMV kernels (exact int32 sum per K-group from mma.sync.m16n8k32.s8
+// with the weights as the A operand, acc = fma(float(P) * ws, xs, acc) over ascending groups, fp32
+// partial tiles of a cut row tile added in ascending-K order). What changes is the weight layout.
+//
+// A row-major [N,K] matrix makes every 16-row tile 16 separate runs in DRAM, 256 bytes at a time per
+// run; measured, that streams at about half of what a linear copy reaches. The loader therefore
+// re-packs each weight once (w8a8_pack_weight) into the order in which this kernel consumes it:
+//
+//   block (rt, kb) = 16 rows x 256 bytes of K      rt = row tile, kb = 256-byte K block
+//     [4 chunks of 64 K-bytes][32 lanes][32 bytes]   a lane's two MMA A-fragment pieces, rows gq and gq+8
+//     [16 rows][groups per block] fp16              the block's weight scales (32, 64 or 128 bytes)
+//   blocks ordered rt-major, kb ascending, one after another with no gaps.
+//
+// The stream-K range of a warp (w*U/W .. (w+1)*U/W units) is then ONE contiguous byte range: the warp
+// pulls it through a private ring of shared-memory stages with 1-D bulk copies (cp.async.bulk, one
+// block per copy, completion on an mbarrier), reads its fragments back with conflict-free 128-bit
+// shared loads, and finds the scales in the same stage — no strided access, no separate scale
+// traffic, no tensor map. Rows past N are stored as zeros, so no tail handling is needed on loads.
+//
+// Launched with programmatic dependent launch: the first kStages blocks are requested before
+// griddepcontrol.wait. Every mbarrier wait is bounded; on expiry the warp records an error word.
+#include "sm100_ptx.cuh"
+#include "w8a8_internal.h"
+
+namespace w8a8 {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kThreads = kWarps * 32;
+constexpr int kStages = 4;
+constexpr int kBlockW = 16 * 256;        // weight bytes of a block
+constexpr int kStagePitch = kBlockW + 128;  // room for the largest scale tail, keeps stages 128-byte aligned
+constexpr int kRingBytes = kStages * kStagePitch;
+
+struct GemvPackedParams {
+    LinearArgs a;
+    const unsigned char* packed;
+    int block_bytes;  // kBlockW + 32 * groups per block
+    int upt;          // units per 16-row tile
+    int bpu;          // blocks per unit (1, or g / 256 when g > 256)
+    unsigned U;       // units in all
+    int NW;           // warps that take part
+    float* partials;
+    int* counters;
+    int* status;
+};
+
+__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                       uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint4 lds128(uint32_t addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ uint32_t lds16(uint32_t addr) {
+    uint16_t v;
+    asm volatile("ld.shared.u16 %0, [%1];\n" : "=h"(v) : "r"(addr));
+    return v;
+}
+
+__device__ __forceinline__ float ld_cg(const float* p) {
+    float v;
+    asm volatile("ld.global.cg.f32 %0, [%1];\n" : "=f"(v) : "l"(p));
+    return v;
+}
+
+// GM: 64 or 128 = the group size itself; 256 = any group size that is a multiple of 256 (a unit is then
+// one whole group = g/256 blocks).
+template <int MT, int GM>
+__global__ void __launch_bounds__(kThreads, 2)
+gemv_packed_kernel(const GemvPackedParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bars[kWarps][kStages];
+    const LinearArgs& a = p.a;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gq = lane >> 2, c = lane & 3;
+    constexpr int GPU = GM == 64 ? 4 : GM == 128 ? 2 : 1;  // groups per unit
+
+    // ---- this warp's contiguous range of units; consecutive ranges sit on different SMs ----
+    const unsigned gw = warp * gridDim.x + blockIdx.x;
+    const unsigned NW = p.NW, U = p.U;
+    const unsigned u0 = gw * U / NW, u1 = (gw + 1) * U / NW;
+    const int T = gw < NW ? static_cast<int>(u1 - u0) * p.bpu : 0;  // blocks
+
+    const uint32_t ring = ((ptx::smem_u32(smem_raw) + 127u) & ~127u) + warp * kRingBytes;
+    uint64_t* bar = bars[warp];
+    if (lane == 0) {
+        for (int s = 0; s < kStages; ++s) ptx::mbar_init(&bar[s], 1);
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
+    }
+    __syncwarp();
+
+    // producer (lane 0): the range is one contiguous run of blocks in the packed image
+    int pt = 0;
+    const unsigned char* src = p.packed + static_cast<size_t>(u0) * p.bpu * p.block_bytes;
+    auto issue = [&]() {  // lane 0 only
+        const int slot = pt % kStages;
+        ptx::mbar_arrive_expect_tx(&bar[slot], p.block_bytes);
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                     ::"r"(ring + slot * kStagePitch), "l"(src), "r"(p.block_bytes), "r"(ptx::smem_u32(&bar[slot]))
+                     : "memory");
+        src += p.block_bytes;
+        ++pt;
+    };
+    if (lane == 0) {
+        const int pre = T < kStages ? T : kStages;
+        for (int i = 0; i < pre; ++i) issue();
+    }
+    // Everything above touches only weights. Let the next launch begin its own prologue, then wait
+    // for the kernel before this one: it produces the activations.
+    ptx::pdl_launch_dependents();
+    ptx::pdl_wait();
+
+    const int8_t* xq[MT];
+    const float* xsp[MT][2];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt) {
+        xq[nt] = a.Xq + static_cast<size_t>(min(nt * 8 + gq, a.M - 1)) * a.K + c * 16;
+        xsp[nt][0] = a.Xs + static_cast<size_t>(min(nt * 8 + 2 * c, a.M - 1)) * a.G;
+        xsp[nt][1] = a.Xs + static_cast<size_t>(min(nt * 8 + 2 * c + 1, a.M - 1)) * a.G;
+    }
+
+    int P[MT][4];
+    float acc[MT][4];
+#pragma unroll
+    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) { P[nt][r] = 0; acc[nt][r] = 0.0f; }
+
+    // Stores a finished 16-row tile held in fragment layout: rows gq / gq+8, tokens 2c / 2c+1.
+    auto store_tile = [&](int rt, const float (&v)[MT][4]) {
+        const int rA = rt * 16 + gq;
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int tok = nt * 8 + 2 * c + e;
+                if (tok >= a.M) continue;
+                if (a.epilogue == W8A8_EPI_SWIGLU) {
+                    if (rA + 8 < a.N) {
+                        const float g16 = __half2float(__float2half(v[nt][e]));
+                        const __half s16 = __float2half(g16 / (1.0f + expf(-g16)));
+                        const float u16 = __half2float(__float2half(v[nt][2 + e]));
+                        a.Y[static_cast<size_t>(tok) * (a.N / 2) + rt * 8 + gq] = __float2half(__half2float(s16) * u16);
+                    }
+                } else {
+#pragma unroll
+                    for (int hrow = 0; hrow < 2; ++hrow) {
+                        const int row = rA + 8 * hrow;
+                        if (row >= a.N) continue;
+                        const size_t o = static_cast<size_t>(tok) * a.N + row;
+                        __half y = __float2half(v[nt][2 * hrow + e]);
+                        if (a.epilogue == W8A8_EPI_RESIDUAL)
+                            y = __float2half(__half2float(y) + __half2float(a.residual[o]));
+                        a.Y[o] = y;
+                    }
+                }
+            }
+        }
+    };
+
+    auto warp_of_unit = [&](unsigned u) -> unsigned {  // the warp whose range holds unit u
+        return ((u + 1) * NW - 1) / U;
+    };
+
+    // Called when the warp has added its last unit of row tile rt into acc.
+    auto finish_tile = [&](int rt) {
+        const unsigned t_lo = static_cast<unsigned>(rt) * p.upt, t_hi = t_lo + p.upt;  // [t_lo, t_hi)
+        if (u0 <= t_lo && t_hi <= u1) {
+            store_tile(rt, acc);
+        } else {
+            // This warp holds only part of the tile's K range: park the partial, and if every other
+            // contributor has parked too, add them up in ascending-K order and store.
+            const unsigned first = warp_of_unit(t_lo), last = warp_of_unit(t_hi - 1);
+            constexpr int kSlot = MT * 4 * 32;
+            const int my_slot = (static_cast<int>(u0 / p.upt) == rt) ? 0 : 1;
+            float* mine = p.partials + (static_cast<size_t>(gw) * 2 + my_slot) * kSlot;
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) mine[(nt * 4 + r) * 32 + lane] = acc[nt][r];
+            __threadfence();
+            __syncwarp();
+            unsigned old = 0;
+            if (lane == 0) old = atomicAdd(reinterpret_cast<unsigned*>(&p.counters[rt]), 1u);
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old == last - first) {
+                __threadfence();
+                float sum[MT][4];
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) sum[nt][r] = 0.0f;
+                // four contributors' loads are in flight at a time; the adds stay in ascending-K order
+                for (unsigned w = first; w <= last; w += 4) {
+                    float v[4][MT][4];
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const unsigned ww = w + q <= last ? w + q : last;
+                        const int slot = (static_cast<int>((ww * U / NW) / p.upt) == rt) ? 0 : 1;
+                        const float* src = p.partials + (static_cast<size_t>(ww) * 2 + slot) * kSlot;
+#pragma unroll
+                        for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                            for (int r = 0; r < 4; ++r) v[q][nt][r] = ld_cg(src + (nt * 4 + r) * 32 + lane);
+                    }
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+                        if (w + q <= last) {
+#pragma unroll
+                            for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                                for (int r = 0; r < 4; ++r) sum[nt][r] += v[q][nt][r];
+                        }
+                }
+                store_tile(rt, sum);
+                if (lane == 0) p.counters[rt] = 0;  // ready for the next launch
+            }
+        }
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) acc[nt][r] = 0.0f;
+    };
+
+    auto promote = [&](int rt, int j, __half hsa, __half hsb) {
+        const float fa = __half2float(hsa), fb = __half2float(hsb);
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt) {
+            const float x0 = __ldg(xsp[nt][0] + j), x1 = __ldg(xsp[nt][1] + j);
+            if (a.dump) {
+                const int t0 = nt * 8 + 2 * c, rA = rt * 16 + gq;
+                const size_t NG = static_cast<size_t>(a.N) * a.G;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int row = rA + 8 * (r >> 1), tok = t0 + (r & 1);
+                    if (row < a.N && tok < a.M) a.dump[tok * NG + static_cast<size_t>(row) * a.G + j] = P[nt][r];
+                }
+            }
+            acc[nt][0] = __fmaf_rn(__fmul_rn(static_cast<float>(P[nt][0]), fa), x0, acc[nt][0]);
+            acc[nt][1] = __fmaf_rn(__fmul_rn(static_cast<float>(P[nt][1]), fa), x1, acc[nt][1]);
+            acc[nt][2] = __fmaf_rn(__fmul_rn(static_cast<float>(P[nt][2]), fb), x0, acc[nt][2]);
+            acc[nt][3] = __fmaf_rn(__fmul_rn(static_cast<float>(P[nt][3]), fb), x1, acc[nt][3]);
+            P[nt][0] = P[nt][1] = P[nt][2] = P[nt][3] = 0;
+        }
+    };
+
+    // ---- consumer loop: one packed block (16 rows x 256 bytes of K, plus its scales) per step ----
+    int si = 0;
+    int ub = static_cast<int>(u0 % p.upt), rt = static_cast<int>(u0 / p.upt);
+    bool ok = true;
+    for (int t = 0; t < T; ++t) {
+        const int slot = t % kStages;
+        const int kbase = (ub * p.bpu + si) * 256;
+        // Activation codes of the block's first half, from L1, before blocking on the weights.
+        uint4 xv[2][MT];
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt)
+                xv[h][nt] = __ldg(reinterpret_cast<const uint4*>(xq[nt] + kbase + h * 64));
+
+        if (!ptx::mbar_wait_bounded(&bar[slot], (t / kStages) & 1)) {
+            if (lane == 0) atomicExch(p.status, 600 + slot);
+            ok = false;
+            break;
+        }
+        const uint32_t st = ring + slot * kStagePitch;
+        // this block's weight scales ride behind its weights: [16 rows][GPU] fp16
+        __half sa[GPU], sb[GPU];
+#pragma unroll
+        for (int q = 0; q < GPU; ++q) {
+            sa[q] = __ushort_as_half(static_cast<unsigned short>(lds16(st + kBlockW + (gq * GPU + q) * 2)));
+            sb[q] = __ushort_as_half(static_cast<unsigned short>(lds16(st + kBlockW + ((gq + 8) * GPU + q) * 2)));
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {  // 64-byte K chunks
+            if (ch == 2) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+#pragma unroll
+                    for (int nt = 0; nt < MT; ++nt)
+                        xv[h][nt] = __ldg(reinterpret_cast<const uint4*>(xq[nt] + kbase + 128 + h * 64));
+            }
+            const uint32_t fa = st + (ch * 32 + lane) * 32;
+            const uint4 wa = lds128(fa), wb = lds128(fa + 16);
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt) {
+                mma_s8(P[nt], wa.x, wb.x, wa.y, wb.y, xv[ch & 1][nt].x, xv[ch & 1][nt].y);
+                mma_s8(P[nt], wa.z, wb.z, wa.w, wb.w, xv[ch & 1][nt].z, xv[ch & 1][nt].w);
+            }
+            if (GM == 64) promote(rt, ub * 4 + ch, sa[ch % GPU], sb[ch % GPU]);
+            if (GM == 128 && (ch & 1)) promote(rt, ub * 2 + (ch >> 1), sa[(ch >> 1) % GPU], sb[(ch >> 1) % GPU]);
+        }
+        // The block's bytes are in registers: the slot may be refilled.
+        __syncwarp();
+        if (lane == 0 && pt < T) {
+            ptx::fence_proxy_async();
+            issue();
+        }
+        if (++si == p.bpu) {
+            si = 0;
+            if (GM == 256) promote(rt, ub, sa[0], sb[0]);
+            if (++ub == p.upt) {
+                finish_tile(rt);
+                ub = 0;
+                ++rt;
+            }
+        }
+    }
+    if (ok && T > 0 && ub != 0) finish_tile(rt);  // the range ended inside a tile
+    if (!ok) {
+        // Leave only once every requested block has landed (or a second bounded wait ran out): a TMA write
+        // must not arrive in shared memory that already belongs to another CTA.
+        pt = __shfl_sync(0xffffffffu, pt, 0);
+        for (int s = 0; s < kStages; ++s)
+            if (pt > s) ptx::mbar_wait_bounded(&bar[s], ((pt - 1 - s) / kStages) & 1, 1u << 16);
+    }
+}
+
+struct Plan {
+    int MT, GM, upt, bpu, block_bytes, tiles, ctas;
+    long long U;
+    size_t partial_bytes;
+};
+
+int num_sms() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+            v = 148;
+        return v;
+    }();
+    return n;
+}
+
+bool packable(int N, int K, int g) {
+    return N > 0 && K > 0 && K % 256 == 0 && K % g == 0 && (g == 64 || g == 128 || g % 256 == 0);
+}
+
+bool make_plan(const LinearArgs& a, Plan& pl) {
+    if (a.M < 1 || a.M > 32 || !a.Xq || !a.Xs || !a.packed) return false;
+    if (!packable(a.N, a.K, a.g)) return false;
+    if (reinterpret_cast<uintptr_t>(a.Xq) & 15u) return false;
+    if (a.epilogue == W8A8_EPI_SWIGLU && a.N % 16 != 0) return false;
+    if (!a.splitk_partials || !a.splitk_counters) return false;
+    pl.MT = a.M <= 8 ? 1 : (a.M <= 16 ? 2 : 4);
+    pl.GM = a.g == 64 ? 64 : a.g == 128 ? 128 : 256;
+    pl.bpu = a.g > 256 ? a.g / 256 : 1;
+    pl.upt = a.K / (256 * pl.bpu);
+    pl.block_bytes = kBlockW + 32 * (a.g >= 256 ? 1 : 256 / a.g);
+    pl.tiles = (a.N + 15) / 16;
+    pl.U = static_cast<long long>(pl.tiles) * pl.upt;
+    pl.ctas = num_sms();
+    if ((pl.U + 1) * static_cast<long long>(pl.ctas) * kWarps >= (1ll << 32)) return false;  // 32-bit range math
+    pl.partial_bytes = static_cast<size_t>(pl.ctas) * kWarps * 2 * pl.MT * 4 * 32 * sizeof(float);
+    if (pl.partial_bytes > a.splitk_partial_bytes) return false;
+    if (static_cast<size_t>(pl.tiles) > a.splitk_counter_count) return false;
+    return true;
+}
+
+template <int MT, int GM>
+int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_t stream) {
+    GemvPackedParams p;
+    p.a = a;
+    p.packed = static_cast<const unsigned char*>(a.packed);
+    p.block_bytes = pl.block_bytes;
+    p.upt = pl.upt;
+    p.bpu = pl.bpu;
+    p.U = static_cast<unsigned>(pl.U);
+    p.NW = static_cast<int>(pl.U < static_cast<long long>(pl.ctas) * kWarps ? pl.U : pl.ctas * kWarps);
+    p.partials = static_cast<float*>(a.splitk_partials);
+    p.counters = a.splitk_counters;
+    p.status = status;
+    auto kern = gemv_packed_kernel<MT, GM>;
+    const size_t smem = static_cast<size_t>(kWarps) * kRingBytes + 128;
+    static bool attr_set = false;  // per template instance
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(pl.ctas, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, p);
+    if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "gemv_packed launch: %s", cudaGetErrorString(e));
+    return W8A8_OK;
+}
+
+template <int MT>
+int launch_gm(const LinearArgs& a, const Plan& pl, int* status, cudaStream_t s) {
+    switch (pl.GM) {
+        case 64: return launch_variant<MT, 64>(a, pl, status, s);
+        case 128: return launch_variant<MT, 128>(a, pl, status, s);
+        default: return launch_variant<MT, 256>(a, pl, status, s);
+    }
+}
+
+// One thread per 16 bytes of the packed image.
+__global__ void __launch_bounds__(256) pack_weight_kernel(const int8_t* __restrict__ W, const __half* __restrict__ S,
+                                                          int N, int K, int g, int G, int block_bytes,
+                                                          unsigned char* __restrict__ out, size_t total16) {
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= total16) return;
+    const int per_block = block_bytes / 16;
+    const size_t blk = i / per_block;
+    const int r = static_cast<int>(i % per_block);
+    const int kblocks = K / 256;
+    const int rt = static_cast<int>(blk / kblocks), kb = static_cast<int>(blk % kblocks);
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (r < kBlockW / 16) {
+        // [chunk][lane][2]: 16 bytes of row (lane/4) + 8*half at K offset chunk*64 + (lane%4)*16
+        const int half = r & 1, lane = (r >> 1) & 31, ch = r >> 6;
+        const int row = rt * 16 + (lane >> 2) + 8 * half;
+        const int k = kb * 256 + ch * 64 + (lane & 3) * 16;
+        if (row < N) v = *reinterpret_cast<const uint4*>(W + static_cast<size_t>(row) * K + k);
+    } else {
+        // scales: [16 rows][gpb] fp16, 8 halves per 16-byte piece
+        const int gpb = g >= 256 ? 1 : 256 / g;
+        __align__(16) __half h[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            const int idx = (r - kBlockW / 16) * 8 + e;  // row * gpb + q
+            const int row = rt * 16 + idx / gpb, q = idx % gpb;
+            const int j = g >= 256 ? (kb * 256) / g : kb * gpb + q;
+            h[e] = row < N ? S[static_cast<size_t>(row) * G + j] : __float2half(0.0f);
+        }
+        v = *reinterpret_cast<const uint4*>(h);
+    }
+    reinterpret_cast<uint4*>(out)[i] = v;
+}
+
+}  // namespace
+
+size_t packed_weight_bytes(int N, int K, int g) {
+    g = norm_group(K, g);
+    if (!packable(N, K, g)) return 0;
+    const size_t block_bytes = kBlockW + 32 * (g >= 256 ? 1 : 256 / g);
+    return static_cast<size_t>((N + 15) / 16) * (K / 256) * block_bytes;
+}
+
+int launch_pack_weight(const int8_t* W, const __half* S, int N, int K, int g, void* out, cudaStream_t s) {
+    g = norm_group(K, g);
+    const size_t bytes = packed_weight_bytes(N, K, g);
+    if (bytes == 0) return fail(W8A8_ERR_UNSUPPORTED, "N=%d K=%d group=%d cannot be packed (K %% 256, group 64/128/k*256)", N, K, g);
+    if ((reinterpret_cast<uintptr_t>(W) | reinterpret_cast<uintptr_t>(out)) & 15u)
+        return fail(W8A8_ERR_INVALID_ARG, "pack_weight needs 16-byte aligned W and output");
+    const int block_bytes = kBlockW + 32 * (g >= 256 ? 1 : 256 / g);
+    const size_t total16 = bytes / 16;
+    pack_weight_kernel<<<static_cast<unsigned>((total16 + 255) / 256), 256, 0, s>>>(
+        W, S, N, K, g, num_groups(K, g), block_bytes, static_cast<unsigned char*>(out), total16);
+    return check_launch("pack_weight_kernel");
+}
+
+bool gemv_packed_supports(const LinearArgs& a) {
+    Plan pl;
+    return make_plan(a, pl);
+}
+
+int launch_linear_gemv_packed(const LinearArgs& a, int* device_status, cudaStream_t s) {
+    Plan pl;
+    if (!make_plan(a, pl)) return fail(W8A8_ERR_UNSUPPORTED, "packed gemv kernel does not take this shape");
+    switch (pl.MT) {
+        case 1: return launch_gm<1>(a, pl, device_status, s);
+        case 2: return launch_gm<2>(a, pl, device_status, s);
+        default: return launch_gm<4>(a, pl, device_status, s);
+    }
+}
+
+}  // namespace w8a8

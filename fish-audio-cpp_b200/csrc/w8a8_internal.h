@@ -40,6 +40,7 @@ struct LinearArgs {
     int M, N, K, g, G;
     int epilogue;
     int split_k;
+    const void* packed;     // the weight re-packed by launch_pack_weight (null: not packed)
     // scratch for kernels that cut K across CTAs (owned by the context; null: such kernels are not used)
     void* splitk_partials;
     size_t splitk_partial_bytes;
@@ -68,6 +69,11 @@ int launch_linear_gemv(const LinearArgs& a, cudaStream_t s);
 // w8a8_gemv_tma.cu : M <= 32, TMA-fed persistent stream-K form.
 bool gemv_tma_supports(const LinearArgs& a);
 int launch_linear_gemv_tma(const LinearArgs& a, int* device_status, cudaStream_t s);
+// w8a8_gemv_packed.cu : M <= 32 over pre-packed weights (linear byte stream, 1-D bulk copies).
+size_t packed_weight_bytes(int N, int K, int g);
+int launch_pack_weight(const int8_t* W, const __half* S, int N, int K, int g, void* out, cudaStream_t s);
+bool gemv_packed_supports(const LinearArgs& a);
+int launch_linear_gemv_packed(const LinearArgs& a, int* device_status, cudaStream_t s);
 // w8a8_gemm_sm100.cu : tcgen05 + TMA.
 bool gemm_supports(const LinearArgs& a);
 int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t s);

@@ -89,7 +89,9 @@ enum { /* forces a kernel family; default picks by shape */
     W8A8_KERNEL_GENERIC = 1, /* scalar-order SIMT kernel, any shape */
     W8A8_KERNEL_GEMV = 2,    /* M <= 32: warp-MMA weight-streaming kernel, cluster split-K */
     W8A8_KERNEL_GEMM = 3,    /* tcgen05 + TMA kernel */
-    W8A8_KERNEL_GEMV_TMA = 4 /* M <= 32: TMA-fed persistent stream-K kernel (the default when it fits) */
+    W8A8_KERNEL_GEMV_TMA = 4, /* M <= 32: TMA-fed persistent stream-K kernel over the row-major matrix */
+    W8A8_KERNEL_GEMV_PACKED = 5 /* M <= 32: the same over a weight packed by w8a8_pack_weight (the default
+                                   once the weight is registered) */
 };
 
 typedef struct w8a8_linear_opts {
@@ -160,6 +162,21 @@ W8A8_API int w8a8_linear_static_scratch(const void* W, const void* w_scale, int 
                                void* stream);
 
 /* ---- loader side --------------------------------------------------------- */
+/* Decode-time weight layout. The reference uploads each weight as it lies in the container
+ * (src/engine/dual_ar_engine.cc:231-278) and keys its quantisation metadata by the device pointer
+ * (:275). A loader built on this library does one more step per weight: it packs the row-major
+ * matrix and its scales into one linear stream in the order the M <= 32 kernel consumes it
+ * (blocks of 16 rows x 256 K-bytes, each followed by its scales), and registers the pair. From
+ * then on w8a8_linear / w8a8_linear_q with that W pointer and M <= 32 stream the packed image;
+ * larger M keeps reading the row-major matrix (which TMA feeds to the tensor cores as it is).
+ * w8a8_packed_weight_bytes returns 0 for shapes that cannot be packed (needs K % 256 == 0 and a
+ * group size of 64, 128 or a multiple of 256); such weights simply stay unpacked. */
+W8A8_API size_t w8a8_packed_weight_bytes(int N, int K, int group_size);
+W8A8_API int w8a8_pack_weight(w8a8_ctx* ctx, const void* W, const void* w_scale, int N, int K,
+                     int group_size, void* packed_out, void* stream);
+/* packed == NULL removes the entry. */
+W8A8_API int w8a8_register_packed_weight(w8a8_ctx* ctx, const void* W, const void* packed);
+
 /* Pre-pack for W8A8_EPI_SWIGLU: interleaves w1 (gate) and w3 (up), both int8 [inter, K] with
  * fp16 scales [inter, G], into W_out int8 [2*inter, K] / scale_out fp16 [2*inter, G] in blocks
  * of 16 rows = 8 gate rows then the 8 up rows of the same channels. inter % 8 == 0. The

@@ -155,6 +155,35 @@ def pack_gate_up(w_gate, s_gate, w_up, s_up):
     return W, (S if G > 1 else S.reshape(-1))
 
 
+def pack_weight(W, S, g):
+    """numpy restatement of the decode-time weight stream (see include/w8a8.h, w8a8_pack_weight):
+    blocks of 16 rows x 256 K-bytes, rt-major then K; inside a block [4 chunks of 64 K-bytes][32 lanes]
+    [row lane//4 | row lane//4 + 8][16 bytes at K offset chunk*64 + (lane%4)*16], then [16 rows][groups
+    per block] fp16 scales. Rows past N are zeros."""
+    N, K = W.shape
+    g = K if g <= 0 or g > K else g
+    assert K % 256 == 0 and K % g == 0 and (g in (64, 128) or g % 256 == 0)
+    G = K // g
+    S = np.ascontiguousarray(S, dtype=np.float16).reshape(N, G)
+    gpb = 1 if g >= 256 else 256 // g
+    tiles, kblocks = (N + 15) // 16, K // 256
+    Wp = np.zeros((tiles * 16, K), np.int8)
+    Wp[:N] = W
+    Sp = np.zeros((tiles * 16, G), np.float16)
+    Sp[:N] = S
+    # [rt][r16][kb][ch][c][16] -> [rt][kb][ch][gq][c][half][16] with r16 = gq + 8*half, lane = gq*4 + c
+    w = Wp.reshape(tiles, 2, 8, kblocks, 4, 4, 16)          # rt, half, gq, kb, ch, c, byte
+    w = w.transpose(0, 3, 4, 2, 5, 1, 6).reshape(tiles, kblocks, 4096)
+    if g >= 256:
+        jidx = (np.arange(kblocks) * 256) // g               # group of each block
+        s = Sp.reshape(tiles, 16, G)[:, :, jidx]             # rt, row, kb
+        s = s.transpose(0, 2, 1).reshape(tiles, kblocks, 16, 1)
+    else:
+        s = Sp.reshape(tiles, 16, kblocks, gpb).transpose(0, 2, 1, 3)  # rt, kb, row, q
+    s = np.ascontiguousarray(s).view(np.uint8).reshape(tiles, kblocks, 32 * gpb)
+    return np.concatenate([w.view(np.uint8), s], axis=2).reshape(-1)
+
+
 def host_threads() -> int:
     return lib().w8a8o_host_threads()
 

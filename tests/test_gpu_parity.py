@@ -282,6 +282,112 @@ def test_gemv_tma_epilogues(ctx, oracle, pkg):
     assert oracle.ulp_distance_fp16(dR.cpu().numpy(), want).max() <= 2
 
 
+PACK_SHAPES = [(1, 128, 256, 64), (4, 200, 512, 128), (8, 64, 2560, 256), (16, 1000, 1280, 64), (3, 72, 512, 512),
+               (32, 128, 768, 256), (7, 40, 9728, 256), (2, 48, 1024, 1024), (16, 2560, 4096, 64)]
+
+
+@pytest.mark.parametrize("M,N,K,g", PACK_SHAPES)
+def test_packed_weight_stream(ctx, oracle, pkg, M, N, K, g):
+    """Loader-side pack against its numpy restatement, then the M <= 32 kernel over the packed stream:
+    per-group sums bit-exact, fp16 within the bars, two runs bitwise equal, and the registry routes a
+    plain w8a8_linear call with the raw W pointer to the packed kernel."""
+    X, W, ws = synth.linear_case(M + N + g, M, N, K, g)
+    G = K // g
+    dW, dS, dX = dev(W), dev(ws), dev(X)
+    nbytes = ctx.packed_weight_bytes(N, K, g)
+    want_pack = oracle.pack_weight(W, ws, g)
+    assert nbytes == want_pack.size
+    dP = torch.full((nbytes,), 0x5A, dtype=torch.uint8, device="cuda")
+    ctx.pack_weight(dW, dS, N, K, g, dP)
+    torch.cuda.synchronize()
+    assert np.array_equal(dP.cpu().numpy(), want_pack)
+    ctx.register_packed_weight(dW, dP)
+    try:
+        outs = []
+        for rep in range(2):
+            dY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+            dD = torch.full((M, N, G), -1, dtype=torch.int32, device="cuda")
+            ctx.linear(dW, dS, g, dX, dY, M, N, K, dump=dD, kernel=pkg.KERNEL_GEMV_PACKED if rep else pkg.KERNEL_AUTO)
+            torch.cuda.synchronize()
+            outs.append(dY.cpu().numpy())
+        ctx.check_device_status()
+        Xq, Xs = oracle.quantize(X, g)
+        Pw = oracle.group_sums(W, Xq, g)
+        assert np.array_equal(dD.cpu().numpy(), Pw)
+        assert_close_fp16(oracle, outs[0], oracle.linear_q(W, ws, Xq, Xs, g), "packed gemv", abs_terms=abs_term_sum(Pw, ws, Xs))
+        assert np.array_equal(outs[0].view(np.uint16), outs[1].view(np.uint16))
+    finally:
+        ctx.register_packed_weight(dW, None)
+    with pytest.raises(pkg.W8A8Error):  # forced, but nothing registered any more
+        ctx.linear(dW, dS, g, dX, dY, M, N, K, kernel=pkg.KERNEL_GEMV_PACKED)
+
+
+def test_unpackable_shapes_report_zero_bytes(ctx):
+    assert ctx.packed_weight_bytes(64, 640, 64) == 0      # K % 256 != 0
+    assert ctx.packed_weight_bytes(64, 768, 192) == 0     # group size
+    assert ctx.packed_weight_bytes(64, 512, 0) == (64 // 16) * 2 * (4096 + 32)  # one group of K = 512
+
+
+GEMM_SHAPES = [(33, 128, 128, 64), (128, 128, 256, 256), (129, 136, 512, 128), (200, 72, 384, 32), (300, 264, 2560, 256),
+               (64, 256, 1024, 64), (257, 128, 640, 640), (1, 128, 128, 128), (500, 16, 256, 64)]
+
+
+@pytest.mark.parametrize("M,N,K,g", GEMM_SHAPES)
+def test_gemm_tcgen05_small_shapes(ctx, oracle, pkg, M, N, K, g):
+    """The tcgen05 + TMA kernel: ragged token and row tails, every group size a multiple of 32 including
+    groups that straddle a 128-byte stage. Groups are added in ascending order exactly like the oracle,
+    so the fp16 output must agree bit for bit."""
+    (X, W, ws, Xq, Xs), Y, P = run_linear(ctx, oracle, M, N, K, g, seed=M + N + K, kernel=pkg.KERNEL_GEMM)
+    ctx.check_device_status()
+    assert np.array_equal(P, oracle.group_sums(W, Xq, g)), "per-group int32 sums must be bit-exact"
+    assert np.array_equal(Y.view(np.uint16), oracle.linear_q(W, ws, Xq, Xs, g).view(np.uint16))
+
+
+def test_gemm_tcgen05_epilogues(ctx, oracle, pkg):
+    M, inter, K, g = 150, 200, 512, 256
+    rng = np.random.default_rng(29)
+    X = synth.activations(rng, M, K)
+    wg, wu = synth.weights(rng, inter, K), synth.weights(rng, inter, K)
+    sg, su = synth.weight_scales(rng, inter, K // g), synth.weight_scales(rng, inter, K // g)
+    Wp, Sp = oracle.pack_gate_up(wg, sg, wu, su)
+    dX = dev(X)
+    dA = torch.empty((M, inter), dtype=torch.float16, device="cuda")
+    ctx.linear(dev(Wp), dev(Sp), g, dX, dA, M, 2 * inter, K, epilogue=pkg.EPI_SWIGLU, kernel=pkg.KERNEL_GEMM)
+    torch.cuda.synchronize()
+    assert oracle.ulp_distance_fp16(dA.cpu().numpy(), oracle.linear(Wp, Sp, g, X, epilogue=oracle.EPI_SWIGLU)).max() <= 1
+    R = rng.standard_normal((M, inter)).astype(np.float16)
+    dR = dev(R)
+    ctx.linear(dev(wg), dev(sg), g, dX, dR, M, inter, K, epilogue=pkg.EPI_RESIDUAL, residual=dR, kernel=pkg.KERNEL_GEMM)
+    torch.cuda.synchronize()
+    want = oracle.linear(wg, sg, g, X, epilogue=oracle.EPI_RESIDUAL, residual=R)
+    assert np.array_equal(dR.cpu().numpy().view(np.uint16), want.view(np.uint16))
+    ctx.check_device_status()
+
+
+@pytest.mark.parametrize("name,g", [("qkv", 256), ("o", 64), ("down", 256), ("gate_up", 64)])
+def test_prefill_shapes_full_size(ctx, oracle, name, g):
+    """configs[2] at M = 2048: the whole GEMM runs on the GPU; a random 48-token x 192-row sub-problem is
+    recomputed by the oracle (each output depends only on its own token row and weight row)."""
+    K, N = synth.PROJECTIONS[name]
+    M = 2048
+    rng = np.random.default_rng(7 + g)
+    X = synth.activations(rng, M, K)
+    gen = torch.Generator(device="cuda").manual_seed(g + K)
+    dW = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda", generator=gen)
+    G = K // g
+    dS = torch.empty((N, G), dtype=torch.float32, device="cuda").uniform_(1e-3, 5e-3, generator=gen).half()
+    dY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    ctx.linear(dW, dS, g, dev(X), dY, M, N, K)
+    torch.cuda.synchronize()
+    ctx.check_device_status()
+    ti = np.sort(rng.choice(M, 48, replace=False))
+    ri = np.sort(rng.choice(N, 192, replace=False))
+    tt, rr = torch.from_numpy(ti).cuda(), torch.from_numpy(ri).cuda()
+    want = oracle.linear(dW[rr].cpu().numpy(), dS[rr].cpu().numpy(), g, X[ti])
+    got = dY[tt][:, rr].cpu().numpy()
+    assert np.array_equal(got.view(np.uint16), want.view(np.uint16))
+
+
 @pytest.mark.parametrize("split_k", [1, 2, 3, 4, 5, 8])
 def test_gemv_split_k_is_deterministic_and_correct(ctx, oracle, pkg, split_k):
     M, N, K, g = 16, 320, 2560, 256
