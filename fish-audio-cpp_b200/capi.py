@@ -59,6 +59,8 @@ def load_library() -> C.CDLL:
         "w8a8_linear": (I, [P, P, P, I, P, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_linear_q": (I, [P, P, P, I, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_pack_gate_up": (I, [P, P, P, P, P, I, I, I, P, P, P]),
+        "w8a8_qknorm_rope_kvwrite": (I, [P, P, P, P, F, P, P, P, I, P, P, I, I, I, I, I, I, P, P]),
+        "w8a8_paged_attention_decode": (I, [P, P, P, P, P, P, P, I, I, I, I, F, I, I, I, I, P, P, I, P]),
         "w8a8_packed_weight_bytes": (Z, [I, I, I]),
         "w8a8_pack_weight": (I, [P, P, P, I, I, I, P, P]),
         "w8a8_register_packed_weight": (I, [P, P, P]),
@@ -77,7 +79,7 @@ EXPORTS = [
     "w8a8_status_string", "w8a8_last_error", "w8a8_create", "w8a8_destroy", "w8a8_workspace_bytes",
     "w8a8_ctx_workspace_bytes", "w8a8_check_device_status", "w8a8_quantize", "w8a8_rms_norm",
     "w8a8_rmsnorm_quantize", "w8a8_silu", "w8a8_mul", "w8a8_residual_add", "w8a8_linear", "w8a8_linear_q",
-    "w8a8_pack_gate_up", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
+    "w8a8_pack_gate_up", "w8a8_qknorm_rope_kvwrite", "w8a8_paged_attention_decode", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
     "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch",
 ]
 
@@ -204,6 +206,23 @@ class Context:
         self._check(self.lib.w8a8_pack_gate_up(self.handle, _ptr(w_gate), _ptr(s_gate), _ptr(w_up), _ptr(s_up),
                                                inter, K, G, _ptr(W_out), _ptr(scale_out), _stream(stream)),
                     "w8a8_pack_gate_up")
+
+    def qknorm_rope_kvwrite(self, qkv, q_norm_w, k_norm_w, eps, freqs, positions, block_table, max_blocks, k_cache,
+                            v_cache, layer, n_layers, batch, n_q, n_kv, head_dim, q_out, stream=None):
+        self._check(self.lib.w8a8_qknorm_rope_kvwrite(self.handle, _ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), eps,
+                                                      _ptr(freqs), _ptr(positions), _ptr(block_table), max_blocks,
+                                                      _ptr(k_cache), _ptr(v_cache), layer, n_layers, batch, n_q, n_kv,
+                                                      head_dim, _ptr(q_out), _stream(stream)),
+                    "w8a8_qknorm_rope_kvwrite")
+
+    def paged_attention_decode(self, q, k_cache, v_cache, block_table, seq_lens, out, batch, n_heads, head_dim,
+                               max_blocks, sm_scale, layer, n_layers, n_kv, quant_group_size=0, Xq=None, Xs=None,
+                               context_splits=0, stream=None):
+        self._check(self.lib.w8a8_paged_attention_decode(self.handle, _ptr(q), _ptr(k_cache), _ptr(v_cache),
+                                                         _ptr(block_table), _ptr(seq_lens), _ptr(out), batch, n_heads,
+                                                         head_dim, max_blocks, sm_scale, layer, n_layers, n_kv,
+                                                         quant_group_size, _ptr(Xq), _ptr(Xs), context_splits,
+                                                         _stream(stream)), "w8a8_paged_attention_decode")
 
     def packed_weight_bytes(self, N, K, group_size) -> int:
         return self.lib.w8a8_packed_weight_bytes(N, K, group_size)

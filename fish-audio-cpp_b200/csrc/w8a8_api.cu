@@ -316,6 +316,41 @@ int w8a8_linear(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_siz
     return dispatch_q(ctx, a, kernel, s);
 }
 
+int w8a8_qknorm_rope_kvwrite(w8a8_ctx* ctx, const void* qkv, const void* q_norm_w, const void* k_norm_w, float eps,
+                             const float* freqs, const int* positions, const int* block_table,
+                             int max_blocks_per_seq, void* k_cache, void* v_cache, int layer, int n_layers,
+                             int batch, int n_q_heads, int n_kv_heads, int head_dim, void* q_out, void* stream) {
+    if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
+    if (head_dim != 128) return fail(W8A8_ERR_UNSUPPORTED, "head_dim %d (only 128 is built)", head_dim);
+    if (batch < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || max_blocks_per_seq <= 0 || layer < 0 || layer >= n_layers)
+        return fail(W8A8_ERR_INVALID_ARG, "qknorm_rope_kvwrite: bad sizes");
+    if (batch > 0 && (!qkv || !freqs || !positions || !block_table || !k_cache || !v_cache || !q_out))
+        return fail(W8A8_ERR_INVALID_ARG, "qknorm_rope_kvwrite: null pointer");
+    return launch_qknorm_rope_kvwrite(static_cast<const __half*>(qkv), static_cast<const __half*>(q_norm_w),
+                                      static_cast<const __half*>(k_norm_w), eps, freqs, positions, block_table,
+                                      max_blocks_per_seq, static_cast<__half*>(k_cache), static_cast<__half*>(v_cache),
+                                      layer, n_layers, batch, n_q_heads, n_kv_heads, static_cast<__half*>(q_out),
+                                      static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_paged_attention_decode(w8a8_ctx* ctx, const void* q, const void* k_cache, const void* v_cache,
+                                const int* block_table, const int* seq_lens, void* out, int batch, int n_heads,
+                                int head_dim, int max_blocks_per_seq, float sm_scale, int layer, int n_layers,
+                                int n_kv_heads, int quant_group_size, void* Xq, void* Xs, int context_splits,
+                                void* stream) {
+    if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
+    if (head_dim != 128) return fail(W8A8_ERR_UNSUPPORTED, "head_dim %d (only 128 is built)", head_dim);
+    if (batch < 0 || n_heads <= 0 || n_kv_heads <= 0 || max_blocks_per_seq <= 0 || layer < 0 || layer >= n_layers)
+        return fail(W8A8_ERR_INVALID_ARG, "paged_attention_decode: bad sizes");
+    if (batch > 0 && (!q || !k_cache || !v_cache || !block_table || !seq_lens || (!out && !Xq) || (Xq && !Xs)))
+        return fail(W8A8_ERR_INVALID_ARG, "paged_attention_decode: null pointer");
+    return launch_paged_attention_decode(static_cast<const __half*>(q), static_cast<const __half*>(k_cache),
+                                         static_cast<const __half*>(v_cache), block_table, seq_lens, batch, n_heads,
+                                         n_kv_heads, max_blocks_per_seq, sm_scale, layer, n_layers,
+                                         static_cast<__half*>(out), quant_group_size, static_cast<int8_t*>(Xq),
+                                         static_cast<float*>(Xs), context_splits, static_cast<cudaStream_t>(stream));
+}
+
 size_t w8a8_packed_weight_bytes(int N, int K, int group_size) { return packed_weight_bytes(N, K, group_size); }
 
 int w8a8_pack_weight(w8a8_ctx* ctx, const void* W, const void* w_scale, int N, int K, int group_size,

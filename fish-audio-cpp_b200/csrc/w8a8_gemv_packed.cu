@@ -9,7 +9,8 @@
 // re-packs each weight once (w8a8_pack_weight) into the order in which this kernel consumes it:
 //
 //   block (rt, kb) = 16 rows x 256 bytes of K      rt = row tile, kb = 256-byte K block
-//     [4 chunks of 64 K-bytes][32 lanes][32 bytes]   a lane's two MMA A-fragment pieces, rows gq and gq+8
+//     [4 chunks of 64 K-bytes][2 halves][32 lanes][16 bytes]   a lane's MMA A-fragment pieces: half 0 =
+//                                                   row gq, half 1 = row gq+8 (gq = lane / 4)
 //     [16 rows][groups per block] fp16              the block's weight scales (32, 64 or 128 bytes)
 //   blocks ordered rt-major, kb ascending, one after another with no gaps.
 //
@@ -27,9 +28,9 @@
 namespace w8a8 {
 namespace {
 
-constexpr int kWarps = 4;
+constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kStages = 4;
+constexpr int kStages = 3;
 constexpr int kBlockW = 16 * 256;        // weight bytes of a block
 constexpr int kStagePitch = kBlockW + 128;  // room for the largest scale tail, keeps stages 128-byte aligned
 constexpr int kRingBytes = kStages * kStagePitch;
@@ -76,7 +77,7 @@ __device__ __forceinline__ float ld_cg(const float* p) {
 // GM: 64 or 128 = the group size itself; 256 = any group size that is a multiple of 256 (a unit is then
 // one whole group = g/256 blocks).
 template <int MT, int GM>
-__global__ void __launch_bounds__(kThreads, 2)
+__global__ void __launch_bounds__(kThreads, MT == 4 ? 1 : 2)
 gemv_packed_kernel(const GemvPackedParams p) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bars[kWarps][kStages];
@@ -130,12 +131,14 @@ gemv_packed_kernel(const GemvPackedParams p) {
         xsp[nt][1] = a.Xs + static_cast<size_t>(min(nt * 8 + 2 * c + 1, a.M - 1)) * a.G;
     }
 
-    int P[MT][4];
+    // Two integer accumulators per tile: consecutive MMAs alternate between them, so that one MMA does
+    // not wait for the previous one's result (with one warp per scheduler that latency is exposed).
+    int P[MT][4], Q[MT][4];
     float acc[MT][4];
 #pragma unroll
     for (int nt = 0; nt < MT; ++nt)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) { P[nt][r] = 0; acc[nt][r] = 0.0f; }
+        for (int r = 0; r < 4; ++r) { P[nt][r] = 0; Q[nt][r] = 0; acc[nt][r] = 0.0f; }
 
     // Stores a finished 16-row tile held in fragment layout: rows gq / gq+8, tokens 2c / 2c+1.
     auto store_tile = [&](int rt, const float (&v)[MT][4]) {
@@ -173,59 +176,34 @@ gemv_packed_kernel(const GemvPackedParams p) {
         return ((u + 1) * NW - 1) / U;
     };
 
+    // A tile cut by a range boundary: the warp parks its fp32 partial in scratch and bumps the tile's
+    // arrival counter with a release atomic WITHOUT waiting for the answer (a wait here would stall
+    // the warp's stream for two memory round trips in the middle of its range). The answer is looked
+    // at after the last block: whichever contributor arrived last adds all partials in ascending-K
+    // order and stores. A warp has at most two such tiles (the first and the last of its range).
+    constexpr int kSlot = MT * 4 * 32;
+    int pend_rt[2];
+    unsigned pend_old[2];
+    int npend = 0;
+
     // Called when the warp has added its last unit of row tile rt into acc.
     auto finish_tile = [&](int rt) {
         const unsigned t_lo = static_cast<unsigned>(rt) * p.upt, t_hi = t_lo + p.upt;  // [t_lo, t_hi)
         if (u0 <= t_lo && t_hi <= u1) {
             store_tile(rt, acc);
         } else {
-            // This warp holds only part of the tile's K range: park the partial, and if every other
-            // contributor has parked too, add them up in ascending-K order and store.
-            const unsigned first = warp_of_unit(t_lo), last = warp_of_unit(t_hi - 1);
-            constexpr int kSlot = MT * 4 * 32;
             const int my_slot = (static_cast<int>(u0 / p.upt) == rt) ? 0 : 1;
             float* mine = p.partials + (static_cast<size_t>(gw) * 2 + my_slot) * kSlot;
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt)
 #pragma unroll
                 for (int r = 0; r < 4; ++r) mine[(nt * 4 + r) * 32 + lane] = acc[nt][r];
-            __threadfence();
-            __syncwarp();
+            __syncwarp();  // orders the other lanes' stores before lane 0's release
             unsigned old = 0;
-            if (lane == 0) old = atomicAdd(reinterpret_cast<unsigned*>(&p.counters[rt]), 1u);
-            old = __shfl_sync(0xffffffffu, old, 0);
-            if (old == last - first) {
-                __threadfence();
-                float sum[MT][4];
-#pragma unroll
-                for (int nt = 0; nt < MT; ++nt)
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) sum[nt][r] = 0.0f;
-                // four contributors' loads are in flight at a time; the adds stay in ascending-K order
-                for (unsigned w = first; w <= last; w += 4) {
-                    float v[4][MT][4];
-#pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const unsigned ww = w + q <= last ? w + q : last;
-                        const int slot = (static_cast<int>((ww * U / NW) / p.upt) == rt) ? 0 : 1;
-                        const float* src = p.partials + (static_cast<size_t>(ww) * 2 + slot) * kSlot;
-#pragma unroll
-                        for (int nt = 0; nt < MT; ++nt)
-#pragma unroll
-                            for (int r = 0; r < 4; ++r) v[q][nt][r] = ld_cg(src + (nt * 4 + r) * 32 + lane);
-                    }
-#pragma unroll
-                    for (int q = 0; q < 4; ++q)
-                        if (w + q <= last) {
-#pragma unroll
-                            for (int nt = 0; nt < MT; ++nt)
-#pragma unroll
-                                for (int r = 0; r < 4; ++r) sum[nt][r] += v[q][nt][r];
-                        }
-                }
-                store_tile(rt, sum);
-                if (lane == 0) p.counters[rt] = 0;  // ready for the next launch
-            }
+            if (lane == 0)
+                asm volatile("atom.add.release.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + rt) : "memory");
+            if (npend == 0) { pend_rt[0] = rt; pend_old[0] = old; } else { pend_rt[1] = rt; pend_old[1] = old; }
+            ++npend;
         }
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt)
@@ -233,11 +211,50 @@ gemv_packed_kernel(const GemvPackedParams p) {
             for (int r = 0; r < 4; ++r) acc[nt][r] = 0.0f;
     };
 
-    auto promote = [&](int rt, int j, __half hsa, __half hsb) {
+    auto resolve_pending = [&](int rt, unsigned old_lane0) {
+        const unsigned t_lo = static_cast<unsigned>(rt) * p.upt, t_hi = t_lo + p.upt;
+        const unsigned first = warp_of_unit(t_lo), last = warp_of_unit(t_hi - 1);
+        const unsigned old = __shfl_sync(0xffffffffu, old_lane0, 0);
+        if (old != last - first) return;  // somebody else arrives later and does it
+        __threadfence();                  // acquire: the other contributors' partials
+        float sum[MT][4];
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) sum[nt][r] = 0.0f;
+        // four contributors' loads are in flight at a time; the adds stay in ascending-K order
+        for (unsigned w = first; w <= last; w += 4) {
+            float v[4][MT][4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const unsigned ww = w + q <= last ? w + q : last;
+                const int slot = (static_cast<int>((ww * U / NW) / p.upt) == rt) ? 0 : 1;
+                const float* src = p.partials + (static_cast<size_t>(ww) * 2 + slot) * kSlot;
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) v[q][nt][r] = ld_cg(src + (nt * 4 + r) * 32 + lane);
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+                if (w + q <= last) {
+#pragma unroll
+                    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) sum[nt][r] += v[q][nt][r];
+                }
+        }
+        store_tile(rt, sum);
+        if (lane == 0) p.counters[rt] = 0;  // ready for the next launch
+    };
+
+    auto promote = [&](int rt, int j, __half hsa, __half hsb, const float (&xsv)[MT][2]) {
         const float fa = __half2float(hsa), fb = __half2float(hsb);
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt) {
-            const float x0 = __ldg(xsp[nt][0] + j), x1 = __ldg(xsp[nt][1] + j);
+            const float x0 = xsv[nt][0], x1 = xsv[nt][1];
+#pragma unroll
+            for (int r = 0; r < 4; ++r) { P[nt][r] += Q[nt][r]; Q[nt][r] = 0; }
             if (a.dump) {
                 const int t0 = nt * 8 + 2 * c, rA = rt * 16 + gq;
                 const size_t NG = static_cast<size_t>(a.N) * a.G;
@@ -256,20 +273,43 @@ gemv_packed_kernel(const GemvPackedParams p) {
     };
 
     // ---- consumer loop: one packed block (16 rows x 256 bytes of K, plus its scales) per step ----
+    // Activation codes and scales are a few KB shared by the whole grid, but each warp touches a
+    // given piece only once, so these reads mostly miss L1 and cost an L2 round trip. They are
+    // requested one block ahead (registers xn / xsn) and never sit on the critical path.
     int si = 0;
     int ub = static_cast<int>(u0 % p.upt), rt = static_cast<int>(u0 / p.upt);
     bool ok = true;
-    for (int t = 0; t < T; ++t) {
-        const int slot = t % kStages;
-        const int kbase = (ub * p.bpu + si) * 256;
-        // Activation codes of the block's first half, from L1, before blocking on the weights.
-        uint4 xv[2][MT];
+    uint4 xc[4][MT], xn[4][MT];
+    float xsc[GPU][MT][2], xsn[GPU][MT][2];
+    auto load_x = [&](int kbase, uint4 (&dst)[4][MT]) {
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
+        for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt)
-                xv[h][nt] = __ldg(reinterpret_cast<const uint4*>(xq[nt] + kbase + h * 64));
-
+                dst[ch][nt] = __ldg(reinterpret_cast<const uint4*>(xq[nt] + kbase + ch * 64));
+    };
+    auto load_xs = [&](int unit_b, float (&dst)[GPU][MT][2]) {
+#pragma unroll
+        for (int q = 0; q < GPU; ++q)
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt) {
+                dst[q][nt][0] = __ldg(xsp[nt][0] + unit_b * GPU + q);
+                dst[q][nt][1] = __ldg(xsp[nt][1] + unit_b * GPU + q);
+            }
+    };
+    if (T > 0) {
+        load_x(ub * p.bpu * 256, xc);
+        load_xs(ub, xsc);
+    }
+    for (int t = 0; t < T; ++t) {
+        const int slot = t % kStages;
+        // position of the next block (the same row tile or the next one: K restarts at 0)
+        int nsi = si + 1, nub = ub;
+        if (nsi == p.bpu) { nsi = 0; if (++nub == p.upt) nub = 0; }
+        if (t + 1 < T) {
+            load_x((nub * p.bpu + nsi) * 256, xn);
+            if (nsi == 0) load_xs(nub, xsn);
+        }
         if (!ptx::mbar_wait_bounded(&bar[slot], (t / kStages) & 1)) {
             if (lane == 0) atomicExch(p.status, 600 + slot);
             ok = false;
@@ -285,40 +325,45 @@ gemv_packed_kernel(const GemvPackedParams p) {
         }
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch) {  // 64-byte K chunks
-            if (ch == 2) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-#pragma unroll
-                    for (int nt = 0; nt < MT; ++nt)
-                        xv[h][nt] = __ldg(reinterpret_cast<const uint4*>(xq[nt] + kbase + 128 + h * 64));
-            }
-            const uint32_t fa = st + (ch * 32 + lane) * 32;
-            const uint4 wa = lds128(fa), wb = lds128(fa + 16);
+            const uint32_t fa = st + ch * 1024 + lane * 16;
+            const uint4 wa = lds128(fa), wb = lds128(fa + 512);
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt) {
-                mma_s8(P[nt], wa.x, wb.x, wa.y, wb.y, xv[ch & 1][nt].x, xv[ch & 1][nt].y);
-                mma_s8(P[nt], wa.z, wb.z, wa.w, wb.w, xv[ch & 1][nt].z, xv[ch & 1][nt].w);
+                mma_s8(P[nt], wa.x, wb.x, wa.y, wb.y, xc[ch][nt].x, xc[ch][nt].y);
+                mma_s8(Q[nt], wa.z, wb.z, wa.w, wb.w, xc[ch][nt].z, xc[ch][nt].w);
             }
-            if (GM == 64) promote(rt, ub * 4 + ch, sa[ch % GPU], sb[ch % GPU]);
-            if (GM == 128 && (ch & 1)) promote(rt, ub * 2 + (ch >> 1), sa[(ch >> 1) % GPU], sb[(ch >> 1) % GPU]);
+            if (GM == 64) promote(rt, ub * 4 + ch, sa[ch % GPU], sb[ch % GPU], xsc[ch % GPU]);
+            if (GM == 128 && (ch & 1))
+                promote(rt, ub * 2 + (ch >> 1), sa[(ch >> 1) % GPU], sb[(ch >> 1) % GPU], xsc[(ch >> 1) % GPU]);
         }
         // The block's bytes are in registers: the slot may be refilled.
         __syncwarp();
-        if (lane == 0 && pt < T) {
-            ptx::fence_proxy_async();
-            issue();
-        }
+        // (No proxy fence: the shared-memory reads above have returned their data — the MMAs consumed it —
+        // before the copy that overwrites the slot is even issued.)
+        if (lane == 0 && pt < T) issue();
         if (++si == p.bpu) {
             si = 0;
-            if (GM == 256) promote(rt, ub, sa[0], sb[0]);
+            if (GM == 256) promote(rt, ub, sa[0], sb[0], xsc[0]);
             if (++ub == p.upt) {
                 finish_tile(rt);
                 ub = 0;
                 ++rt;
             }
+#pragma unroll
+            for (int q = 0; q < GPU; ++q)
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt) { xsc[q][nt][0] = xsn[q][nt][0]; xsc[q][nt][1] = xsn[q][nt][1]; }
         }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch)
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt) xc[ch][nt] = xn[ch][nt];
     }
     if (ok && T > 0 && ub != 0) finish_tile(rt);  // the range ended inside a tile
+    if (ok) {
+        if (npend > 0) resolve_pending(pend_rt[0], pend_old[0]);
+        if (npend > 1) resolve_pending(pend_rt[1], pend_old[1]);
+    }
     if (!ok) {
         // Leave only once every requested block has landed (or a second bounded wait ran out): a TMA write
         // must not arrive in shared memory that already belongs to another CTA.
@@ -428,8 +473,8 @@ __global__ void __launch_bounds__(256) pack_weight_kernel(const int8_t* __restri
     const int rt = static_cast<int>(blk / kblocks), kb = static_cast<int>(blk % kblocks);
     uint4 v = make_uint4(0, 0, 0, 0);
     if (r < kBlockW / 16) {
-        // [chunk][lane][2]: 16 bytes of row (lane/4) + 8*half at K offset chunk*64 + (lane%4)*16
-        const int half = r & 1, lane = (r >> 1) & 31, ch = r >> 6;
+        // [chunk][half][lane]: 16 bytes of row (lane/4) + 8*half at K offset chunk*64 + (lane%4)*16
+        const int lane = r & 31, half = (r >> 5) & 1, ch = r >> 6;
         const int row = rt * 16 + (lane >> 2) + 8 * half;
         const int k = kb * 256 + ch * 64 + (lane & 3) * 16;
         if (row < N) v = *reinterpret_cast<const uint4*>(W + static_cast<size_t>(row) * K + k);

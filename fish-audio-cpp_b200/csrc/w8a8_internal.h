@@ -74,6 +74,15 @@ size_t packed_weight_bytes(int N, int K, int g);
 int launch_pack_weight(const int8_t* W, const __half* S, int N, int K, int g, void* out, cudaStream_t s);
 bool gemv_packed_supports(const LinearArgs& a);
 int launch_linear_gemv_packed(const LinearArgs& a, int* device_status, cudaStream_t s);
+// w8a8_attn.cu : decode-step neighbours (qk-norm + RoPE + KV write; paged attention).
+int launch_qknorm_rope_kvwrite(const __half* qkv, const __half* q_norm_w, const __half* k_norm_w, float eps,
+                               const float* freqs, const int* positions, const int* block_table, int max_blocks,
+                               __half* k_cache, __half* v_cache, int layer, int n_layers, int B, int n_q, int n_kv,
+                               __half* q_out, cudaStream_t stream);
+int launch_paged_attention_decode(const __half* q, const __half* k_cache, const __half* v_cache,
+                                  const int* block_table, const int* seq_lens, int B, int n_q, int n_kv,
+                                  int max_blocks, float sm_scale, int layer, int n_layers, __half* out, int g,
+                                  int8_t* Xq, float* Xs, int splits, cudaStream_t stream);
 // w8a8_gemm_sm100.cu : tcgen05 + TMA.
 bool gemm_supports(const LinearArgs& a);
 int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t s);

@@ -162,6 +162,35 @@ W8A8_API int w8a8_linear_static_scratch(const void* W, const void* w_scale, int 
                                void* stream);
 
 /* ---- loader side --------------------------------------------------------- */
+/* ---- decode-step neighbours inside a layer ----------------------------------------------- */
+
+/* Replaces, per layer of DualAREngine::decode_step: the three device copies that split the fused qkv
+ * row, rms_norm on q and on k (qk-norm, skipped when the weight pointers are NULL), rope_qk, and the
+ * 2 x n_kv cudaMemcpyAsync calls that write k and v into the paged cache
+ * (src/engine/dual_ar_engine.cc:585-628; src/kernels/rope.cu:9-65; src/kernels/rms_norm.cu:10-58).
+ * qkv fp16 [batch, (n_q + 2 n_kv) * head_dim] laid out [q | k | v]; positions int32 [batch] = the new
+ * token's position (the reference handles batch 1 and passes it as `token_pos`); caches fp16
+ * [blocks, n_layers, n_kv, 16, head_dim] (src/engine/block_manager.h:73); q_out fp16
+ * [batch, n_q, head_dim]. Same rounding points and summation order as the reference chain. */
+W8A8_API int w8a8_qknorm_rope_kvwrite(w8a8_ctx* ctx, const void* qkv, const void* q_norm_w,
+                             const void* k_norm_w, float eps, const float* freqs, const int* positions,
+                             const int* block_table, int max_blocks_per_seq, void* k_cache, void* v_cache,
+                             int layer, int n_layers, int batch, int n_q_heads, int n_kv_heads,
+                             int head_dim, void* q_out, void* stream);
+
+/* Replaces fish::kernels::paged_attention_decode, src/kernels/kernels.h:51-69
+ * (src/kernels/paged_attention.cu:13-150); same arguments in the same order, then three additions:
+ * when Xq is not NULL the attention output is also quantised for the following o-projection
+ * (int8 codes [batch, n_heads*head_dim], fp32 scales per quant_group_size channels, the arithmetic of
+ * int8_gemm.cu:147-211), `out` may then be NULL; context_splits (0 = choose) is the number of CTAs
+ * that share one (sequence, kv head). Needs n_heads == 4 * n_kv_heads. */
+W8A8_API int w8a8_paged_attention_decode(w8a8_ctx* ctx, const void* q, const void* k_cache,
+                                const void* v_cache, const int* block_table, const int* seq_lens,
+                                void* out, int batch, int n_heads, int head_dim, int max_blocks_per_seq,
+                                float sm_scale, int layer, int n_layers, int n_kv_heads,
+                                int quant_group_size, void* Xq, void* Xs, int context_splits,
+                                void* stream);
+
 /* Decode-time weight layout. The reference uploads each weight as it lies in the container
  * (src/engine/dual_ar_engine.cc:231-278) and keys its quantisation metadata by the device pointer
  * (:275). A loader built on this library does one more step per weight: it packs the row-major

@@ -41,6 +41,8 @@ def lib() -> C.CDLL:
         _lib.fishref_silu.argtypes = [P, I, P]
         _lib.fishref_mul.argtypes = [P, P, I, P]
         _lib.fishref_residual_add.argtypes = [P, P, I, P]
+        _lib.fishref_rope_qk.argtypes = [P, P, P, I, I, I, I, I, I, P]
+        _lib.fishref_paged_attention_decode.argtypes = [P, P, P, P, P, P, I, I, I, I, C.c_float, I, I, I, P]
     return _lib
 
 
@@ -78,3 +80,13 @@ def mul(a, b, n, stream=None):
 
 def residual_add(a, b, n, stream=None):
     _check(lib().fishref_residual_add(a, b, n, stream))
+
+
+def rope_qk(q, k, freqs, batch, n_q, n_k, seq_len, head_dim, offset, stream=None):
+    _check(lib().fishref_rope_qk(q, k, freqs, batch, n_q, n_k, seq_len, head_dim, offset, stream))
+
+
+def paged_attention_decode(q, k_cache, v_cache, block_table, seq_lens, out, batch, n_heads, head_dim, max_blocks,
+                           sm_scale, layer, n_layers, n_kv, stream=None):
+    _check(lib().fishref_paged_attention_decode(q, k_cache, v_cache, block_table, seq_lens, out, batch, n_heads,
+                                                head_dim, max_blocks, sm_scale, layer, n_layers, n_kv, stream))

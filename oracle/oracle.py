@@ -157,8 +157,8 @@ def pack_gate_up(w_gate, s_gate, w_up, s_up):
 
 def pack_weight(W, S, g):
     """numpy restatement of the decode-time weight stream (see include/w8a8.h, w8a8_pack_weight):
-    blocks of 16 rows x 256 K-bytes, rt-major then K; inside a block [4 chunks of 64 K-bytes][32 lanes]
-    [row lane//4 | row lane//4 + 8][16 bytes at K offset chunk*64 + (lane%4)*16], then [16 rows][groups
+    blocks of 16 rows x 256 K-bytes, rt-major then K; inside a block [4 chunks of 64 K-bytes]
+    [row lane//4 | row lane//4 + 8][32 lanes][16 bytes at K offset chunk*64 + (lane%4)*16], then [16 rows][groups
     per block] fp16 scales. Rows past N are zeros."""
     N, K = W.shape
     g = K if g <= 0 or g > K else g
@@ -171,9 +171,9 @@ def pack_weight(W, S, g):
     Wp[:N] = W
     Sp = np.zeros((tiles * 16, G), np.float16)
     Sp[:N] = S
-    # [rt][r16][kb][ch][c][16] -> [rt][kb][ch][gq][c][half][16] with r16 = gq + 8*half, lane = gq*4 + c
+    # [rt][r16][kb][ch][c][16] -> [rt][kb][ch][half][gq][c][16] with r16 = gq + 8*half, lane = gq*4 + c
     w = Wp.reshape(tiles, 2, 8, kblocks, 4, 4, 16)          # rt, half, gq, kb, ch, c, byte
-    w = w.transpose(0, 3, 4, 2, 5, 1, 6).reshape(tiles, kblocks, 4096)
+    w = w.transpose(0, 3, 4, 1, 2, 5, 6).reshape(tiles, kblocks, 4096)
     if g >= 256:
         jidx = (np.arange(kblocks) * 256) // g               # group of each block
         s = Sp.reshape(tiles, 16, G)[:, :, jidx]             # rt, row, kb
@@ -182,6 +182,50 @@ def pack_weight(W, S, g):
         s = Sp.reshape(tiles, 16, kblocks, gpb).transpose(0, 2, 1, 3)  # rt, kb, row, q
     s = np.ascontiguousarray(s).view(np.uint8).reshape(tiles, kblocks, 32 * gpb)
     return np.concatenate([w.view(np.uint8), s], axis=2).reshape(-1)
+
+
+def rope_freqs(head_dim=128, base=1e6):
+    """fp32 frequencies as the engine builds them on the host (dual_ar_engine.cc:161-167)."""
+    i = np.arange(head_dim // 2, dtype=np.float32)
+    return (np.float32(1.0) / np.power(np.float32(base), (np.float32(2.0) * i / np.float32(head_dim)))).astype(np.float32)
+
+
+def qknorm_rope(x, w, eps, freqs, pos):
+    """x fp16 [heads, D]: per-head rms_norm (w may be None), then interleaved-pair RoPE at `pos`
+    (rms_norm.cu:10-58, rope.cu:36-45), every fp16 rounding of the reference chain kept."""
+    h = x
+    if w is not None:
+        h = rms_norm(np.ascontiguousarray(x), w, eps)
+    f = h.astype(np.float32)
+    ang = (freqs.astype(np.float32) * np.float32(pos)).astype(np.float32)
+    c, s = np.cos(ang.astype(np.float64)).astype(np.float32), np.sin(ang.astype(np.float64)).astype(np.float32)
+    x0, x1 = f[:, 0::2], f[:, 1::2]
+    out = np.empty_like(f)
+    out[:, 0::2] = x0 * c - x1 * s
+    out[:, 1::2] = x0 * s + x1 * c
+    return out.astype(np.float16)
+
+
+def paged_attention_decode(q, k_cache, v_cache, block_table, seq_lens, layer, sm_scale):
+    """float64 restatement of paged_attention.cu:13-110. q fp16 [B, H, D]; caches fp16
+    [blocks, layers, KvH, 16, D]; returns float64 [B, H, D] (callers compare at a tolerance)."""
+    B, H, D = q.shape
+    KvH = k_cache.shape[2]
+    out = np.zeros((B, H, D), np.float64)
+    for b in range(B):
+        L = int(seq_lens[b])
+        if L <= 0:
+            continue
+        nb = (L + 15) // 16
+        phys = block_table[b, :nb]
+        for h in range(H):
+            kv = (h * KvH) // H
+            K = k_cache[phys, layer, kv].reshape(-1, D)[:L].astype(np.float64)
+            V = v_cache[phys, layer, kv].reshape(-1, D)[:L].astype(np.float64)
+            sc = K @ q[b, h].astype(np.float64) * sm_scale
+            p = np.exp(sc - sc.max())
+            out[b, h] = (p / p.sum()) @ V
+    return out
 
 
 def host_threads() -> int:

@@ -11,6 +11,8 @@
 #include "kernels/int8_gemm.cu"        // reference: src/kernels/int8_gemm.cu
 #include "kernels/rms_norm.cu"         // reference: src/kernels/rms_norm.cu
 #include "kernels/ffn_activations.cu"  // reference: src/kernels/ffn_activations.cu
+#include "kernels/rope.cu"             // reference: src/kernels/rope.cu
+#include "kernels/paged_attention.cu"  // reference: src/kernels/paged_attention.cu
 
 #include <cstdio>
 
@@ -105,6 +107,25 @@ int fishref_residual_add(void* a, const void* b, int n, void* stream) {
     return guarded([&] {
         fish::kernels::residual_add(static_cast<__half*>(a), static_cast<const __half*>(b), n,
                                     static_cast<cudaStream_t>(stream));
+    });
+}
+
+int fishref_rope_qk(void* q, void* k, const float* freqs, int batch, int n_q, int n_k, int seq_len, int head_dim,
+                    int offset, void* stream) {
+    return guarded([&] {
+        fish::kernels::rope_qk(static_cast<const __half*>(q), static_cast<const __half*>(k), freqs, batch, n_q, n_k,
+                               seq_len, head_dim, offset, static_cast<cudaStream_t>(stream));
+    });
+}
+
+int fishref_paged_attention_decode(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                   const int* seq_lens, void* out, int batch, int n_heads, int head_dim,
+                                   int max_blocks, float sm_scale, int layer, int n_layers, int n_kv, void* stream) {
+    return guarded([&] {
+        fish::kernels::paged_attention_decode(static_cast<const __half*>(q), static_cast<const __half*>(k_cache),
+                                              static_cast<const __half*>(v_cache), block_table, seq_lens,
+                                              static_cast<__half*>(out), batch, n_heads, head_dim, max_blocks,
+                                              sm_scale, layer, n_layers, n_kv, static_cast<cudaStream_t>(stream));
     });
 }
 
