@@ -237,6 +237,182 @@ class DecodeSweep:
         return out
 
 
+class DecodeStack:
+    """configs[3]: the full slow-AR decoder stack, batch 8, context 1024, g256, tensor-parallel over the
+    ranks of the job. One step = one token for each of the 8 sequences, replayed from a CUDA graph."""
+
+    def __init__(self, torch, ctx, world, rank, dist, layers=36, batch=8, context=1024, group=256, reference=False):
+        from fish_audio_cpp_b200 import stack as S
+
+        self.torch, self.ctx, self.dist, self.world = torch, ctx, dist, world
+        cfg = S.SlowARConfig(n_layer=layers, group=group)
+        ar = None
+        if world > 1:
+            ar = lambda t: dist.all_reduce(t)  # noqa: E731  (fp16 sum over NVLink, NCCL)
+        self.st = S.SlowARStack(torch, ctx, cfg, batch, context, max_new=128, tp_rank=rank, tp_size=world,
+                                seed=7, all_reduce=ar, pack=not reference)
+        self.cfg, self.batch, self.context = cfg, batch, context
+        self.ref = ReferenceStack(torch, self.st) if reference else None
+        self.host_x = (torch.randn((batch, cfg.dim), generator=torch.Generator().manual_seed(3)) * 0.5).half().pin_memory()
+        self.dev_x = self.host_x.cuda()
+        self.host_out = torch.empty((batch, cfg.dim), dtype=torch.float16).pin_memory()
+        self.graphs = {}
+        self.eager = False
+        self.split_k = 0
+        self.launches_per_step = self.st.launches_per_step
+        self.h2d = self.host_x.numel() * 2
+        self.d2h = self.host_out.numel() * 2
+        self.cases = []
+        # algorithmic bytes of one step on one rank: its weight shards + scales, the KV it reads, activations ~0
+        self.bytes_per_step = self.st.weight_bytes + self.st.kv_bytes_per_step(context)
+        self.ops_per_step = 2 * batch * sum(lw[n].numel() for lw in self.st.layers for n in ("wqkv", "wo", "w13", "w2"))
+        self.steps_done = 0
+
+    def body(self, e2e):
+        if e2e:
+            self.dev_x.copy_(self.host_x, non_blocking=True)
+        self.st.decode_step(self.dev_x)
+        if e2e:
+            self.host_out.copy_(self.st.out, non_blocking=True)
+
+    def time_linears(self, reps=20):
+        """(average seconds per launch, algorithmic bytes per launch) of the four linears of every layer,
+        replayed alone from a graph: the dominant kernel on its own, timed with CUDA events."""
+        t = self.torch
+        self.st.linears_only()
+        t.cuda.synchronize()
+        gr = t.cuda.CUDAGraph()
+        with t.cuda.graph(gr):
+            self.st.linears_only()
+        for _ in range(3):
+            gr.replay()
+        e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            gr.replay()
+        e1.record()
+        t.cuda.synchronize()
+        launches = 4 * self.cfg.n_layer
+        acts = 2 * self.batch * (2 * self.cfg.dim + self.st.attn_k + self.st.inter_l) + \
+            2 * self.batch * (self.st.qkv_n + 2 * self.cfg.dim + self.st.inter_l)
+        per_launch_bytes = self.st.weight_bytes / launches + acts / 4
+        return e0.elapsed_time(e1) * 1e-3 / (reps * launches), per_launch_bytes
+
+    def step(self, e2e=False):
+        t = self.torch
+        if self.ref is not None:
+            self.st.reset_positions()
+            self.ref.decode_step(self.dev_x)
+            return
+        # the context grows by one token per step; go back to 1024 every 64 steps so that it stays "1024"
+        if self.steps_done and self.steps_done % 64 == 0:
+            self.st.reset_positions()
+        self.steps_done += 1
+        if self.eager:
+            self.body(e2e)
+        else:
+            key = ("step", e2e)
+            if key not in self.graphs:
+                self.body(e2e)
+                t.cuda.synchronize()
+                gr = t.cuda.CUDAGraph()
+                with t.cuda.graph(gr):
+                    self.body(e2e)
+                self.graphs[key] = gr
+            self.graphs[key].replay()
+        if e2e:
+            t.cuda.current_stream().synchronize()
+
+    def per_case(self, min_ms=3.0):
+        return []
+
+
+class ReferenceStack:
+    """configs[3] with the reference's own CUDA kernels (oracle/_ref, stock entry points) chained in the
+    order of DualAREngine::decode_step (src/engine/dual_ar_engine.cc:576-657) at batch 8: rms_norm,
+    int8_dequant_gemm_fp16 x5 (gate and up apart), silu, mul, residual_add x2, qk rms_norm x2, rope_qk,
+    paged_attention_decode. The engine itself cannot be built here (its build fetches dependencies from
+    the network and it wants a checkpoint); its per-head cudaMemcpyAsync KV writes, which are batch-1
+    host code, are stood in for by one vectorised scatter per layer. Launches are eager: the reference
+    linear allocates inside the call. Single GPU only (the reference has no multi-GPU path)."""
+
+    def __init__(self, torch, ours_stack):
+        from oracle import fishref
+
+        self.f, self.torch, self.st = fishref, torch, ours_stack
+        st, c = ours_stack, ours_stack.cfg
+        B, D = st.B, c.head_dim
+        h16 = dict(dtype=torch.float16, device="cuda")
+        self.ws1 = torch.empty((B, max(c.dim, c.inter)), **h16)
+        self.ws2 = torch.empty((B, max(st.qkv_n, c.inter, c.dim)), **h16)
+        self.up = torch.empty((B, c.inter), **h16)
+        self.qb = torch.empty((B, c.n_head, D), **h16)
+        self.kb = torch.empty((B, c.n_kv, D), **h16)
+        self.vb = torch.empty((B, c.n_kv, D), **h16)
+        self.att = torch.empty((B, c.n_head * D), **h16)
+        # un-interleave the packed gate/up weights back into the two matrices the reference expects
+        self.w1, self.w3 = [], []
+        for lw in st.layers:
+            W = lw["w13"].view(-1, 2, 8, c.dim)
+            Ssc = lw["s13"].view(-1, 2, 8, c.dim // c.group)
+            self.w1.append((W[:, 0].reshape(-1, c.dim).contiguous(), Ssc[:, 0].reshape(-1, c.dim // c.group).contiguous()))
+            self.w3.append((W[:, 1].reshape(-1, c.dim).contiguous(), Ssc[:, 1].reshape(-1, c.dim // c.group).contiguous()))
+        self.launches_per_step = 0
+
+    def gemm(self, W, S, X, Y, n_out, tokens, K):
+        self.f.int8_dequant_gemm_fp16(W.data_ptr(), S.data_ptr(), self.st.cfg.group, None, None, X.data_ptr(),
+                                      Y.data_ptr(), n_out, tokens, K)
+
+    def decode_step(self, x_in):
+        t, f, st = self.torch, self.f, self.st
+        c, B, D = st.cfg, st.B, st.cfg.head_dim
+        x = st.x
+        x.copy_(x_in)
+        p = lambda tt: tt.data_ptr()  # noqa: E731
+        pos = int(st.context0)
+        for l, lw in enumerate(st.layers):
+            f.rms_norm(p(x), p(lw["attn_norm"]), p(self.ws1), B, c.dim, c.eps)
+            self.gemm(lw["wqkv"], lw["sqkv"], self.ws1, self.ws2, st.qkv_n, B, c.dim)
+            qkv = self.ws2.view(-1)[:B * st.qkv_n].view(B, st.qkv_n)
+            self.qb.copy_(qkv[:, :c.n_head * D].reshape(B, c.n_head, D))
+            self.kb.copy_(qkv[:, c.n_head * D:(c.n_head + c.n_kv) * D].reshape(B, c.n_kv, D))
+            self.vb.copy_(qkv[:, (c.n_head + c.n_kv) * D:].reshape(B, c.n_kv, D))
+            f.rms_norm(p(self.qb), p(lw["q_norm"]), p(self.qb), B * c.n_head, D, c.eps)
+            f.rms_norm(p(self.kb), p(lw["k_norm"]), p(self.kb), B * c.n_kv, D, c.eps)
+            f.rope_qk(p(self.qb), p(self.kb), p(st.freqs), B, c.n_head, c.n_kv, 1, D, pos)
+            phys = st.block_table[:, pos // 16].long()
+            st.k_cache[phys, l, :, pos % 16] = self.kb
+            st.v_cache[phys, l, :, pos % 16] = self.vb
+            f.paged_attention_decode(p(self.qb), p(st.k_cache), p(st.v_cache), p(st.block_table), p(st.seq_lens),
+                                     p(self.att), B, c.n_head, D, st.max_blocks, 1.0 / D ** 0.5, l, c.n_layer, c.n_kv)
+            self.gemm(lw["wo"], lw["so"], self.att, self.ws1, c.dim, B, c.n_head * D)
+            f.residual_add(p(x), p(self.ws1), B * c.dim)
+            f.rms_norm(p(x), p(lw["ffn_norm"]), p(self.ws2), B, c.dim, c.eps)
+            self.gemm(self.w1[l][0], self.w1[l][1], self.ws2, self.ws1, c.inter, B, c.dim)
+            f.silu(p(self.ws1), B * c.inter)
+            self.gemm(self.w3[l][0], self.w3[l][1], self.ws2, self.up, c.inter, B, c.dim)
+            f.mul(p(self.ws1), p(self.up), B * c.inter)
+            self.gemm(lw["w2"], lw["s2"], self.ws1, self.ws2, c.dim, B, c.inter)
+            f.residual_add(p(x), p(self.ws2), B * c.dim)
+        f.rms_norm(p(x), p(st.final_norm), p(st.out), B, c.dim, c.eps)
+
+
+def cpu_baseline_stack(layers=1):
+    """The scalar oracle on the host cores over ONE decoder layer's four linears at batch 8 (g256), scaled
+    to 36 layers: the linears are > 99 % of a CPU step, norms/rope/attention are left out of the sample."""
+    from fish_audio_cpp_b200 import synth
+    from oracle import oracle
+
+    threads = oracle.host_threads()
+    rng = np.random.default_rng(99)
+    total_s = 0.0
+    for name, (K, N) in synth.PROJECTIONS.items():
+        X, W, ws = synth.activations(rng, 8, K), synth.weights(rng, N, K), synth.weight_scales(rng, N, K // 256)
+        total_s += oracle.timed_linear(W, ws, 256, X, N, threads)
+    return {"value": 8.0 / (total_s * 36), "unit": "tokens/s", "cores": threads, "kind": "port",
+            "sample": f"the four linears of one layer at batch 8, g256, all rows ({total_s:.2f} s), x36 layers"}
+
+
 def cpu_baseline_sweep(budget_s=20.0):
     """The scalar oracle on the host cores: the four projections at M=16, g=256, all rows, one pass."""
     from fish_audio_cpp_b200 import synth
@@ -263,10 +439,11 @@ def cpu_baseline_sweep(budget_s=20.0):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=2000)
-    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["decode_sweep"], default="decode_sweep")
+    ap.add_argument("--workload", choices=["decode_stack", "decode_sweep"], default="decode_stack")
+    ap.add_argument("--layers", type=int, default=36, help="decode_stack: number of layers (36 = the named config)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only", default=None, metavar="NAME:M:G",
                     help="restrict the sweep to one case, e.g. gate_up:16:256 (for profiling)")
@@ -300,6 +477,7 @@ def main():
 
     pkg = ge.package()
     reference = args.impl == "reference"
+    solo_reference = False
     if reference:
         from oracle import fishref
 
@@ -308,16 +486,29 @@ def main():
                 print(json.dumps({"impl": "reference", "unavailable":
                                   "oracle/_ref/libfishref.so was not built (no reference checkout at build time)"}))
             return
-        wl = DecodeSweep(torch, None, reference=True)
+        if args.workload == "decode_stack":
+            if rank != 0:  # the reference has no multi-GPU path: rank 0 alone runs it
+                if dist is not None:
+                    dist.barrier()
+                    dist.destroy_process_group()
+                return
+            ctx = pkg.Context(local_rank, 1 << 24)  # builds the weights and the cache; no kernel of ours is timed
+            wl = DecodeStack(torch, ctx, 1, 0, None, layers=args.layers, reference=True)
+            solo_reference = True
+        else:
+            wl = DecodeSweep(torch, None, reference=True)
     else:
         ctx = pkg.Context(local_rank, 0)
-        wl = DecodeSweep(torch, ctx, pack=not args.no_pack)
+        if args.workload == "decode_stack":
+            wl = DecodeStack(torch, ctx, world, rank, dist, layers=args.layers)
+        else:
+            wl = DecodeSweep(torch, ctx, pack=not args.no_pack)
 
     wl.eager = args.eager
     wl.split_k = args.split_k
 
     def barrier():
-        if dist is not None:
+        if dist is not None and not solo_reference:
             dist.barrier()
         torch.cuda.synchronize()
 
@@ -347,16 +538,63 @@ def main():
     cases = [] if args.no_detail else wl.per_case()
     clocks = sampler.stop()
 
-    times = torch.tensor([dev_ms, e2e_ms or 0.0], dtype=torch.float64, device="cuda")
-    if dist is not None:
+    lin = wl.time_linears() if (args.workload == "decode_stack" and not reference) else None
+    times = torch.tensor([dev_ms, e2e_ms or 0.0, lin[0] if lin else 0.0], dtype=torch.float64, device="cuda")
+    if dist is not None and not solo_reference:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    dev_ms, e2e_ms_max = times.tolist()
+    dev_ms, e2e_ms_max, lin_s = times.tolist()
+    if solo_reference and dist is not None:
+        dist.barrier()
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
         return
 
     pk = peaks()
+    if args.workload == "decode_stack":
+        ms_per_step = dev_ms / args.steps
+        n_gpus = 1 if solo_reference else world
+        tok_s = wl.batch / (ms_per_step * 1e-3)
+        line = {
+            "metric": "slow_ar_decode_tokens_per_s", "value": round(tok_s, 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": f"configs[3]: slow-AR decoder stack, {args.layers} layers, hidden 2560, 32q/8kv x128, "
+                                   "SwiGLU 9728, W8A8 g256, fp16 paged KV (16-token blocks), batch 8, context 1024, "
+                                   "random-init weights; LM head and sampling outside the step",
+                       "global_batch": wl.batch, "context": wl.context,
+                       "parallelism": f"tp{n_gpus}" + (" (NCCL fp16 all-reduce after wo and w2)" if n_gpus > 1 else ""),
+                       "l2": "inputs larger than L2: a step streams 3.6 GB of weights + 1.2 GB of KV",
+                       "step_hbm_gbs_per_gpu": round(wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9, 1),
+                       "step_hbm_frac_per_gpu": round(wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
+            "clocks": clocks,
+            "gpu_launches": wl.launches_per_step * args.steps,
+        }
+        if lin:
+            ach = lin[1] / lin_s / 1e9
+            line["roofline"] = {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                                "frac": round(ach / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"],
+                                "kernel": "gemv_packed_kernel (the 4 linears of each layer, timed alone)",
+                                "algorithmic_bytes_per_launch": int(lin[1]), "us_per_launch": round(lin_s * 1e6, 2)}
+        if reference:
+            line["impl"] = "reference"
+            line["n_gpus"] = world
+            line["config"]["parallelism"] = "single GPU (the reference has no multi-GPU path; rank 0 alone ran)"
+            line["gpu_launches"] = None
+            line["cpu_baseline"] = {"value": line["value"], "unit": "tokens/s", "cores": 0, "kind": "reference",
+                                    "sample": "the reference's own CUDA kernels (rebuilt for sm_100) chained in the "
+                                              "order of DualAREngine::decode_step at batch 8, eager launches, on the "
+                                              "GPU: the reference has no CPU implementation of this path"}
+            line["e2e"] = {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+        else:
+            line["e2e"] = {"value": round(wl.batch / (e2e_ms_max / args.steps * 1e-3), 1), "unit": "tokens/s",
+                           "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h}
+            if not args.no_cpu_baseline:
+                line["cpu_baseline"] = cpu_baseline_stack()
+        print(json.dumps(line))
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     ms_per_step = dev_ms / args.steps
     total_bytes = wl.bytes_per_step * world
     value = total_bytes / (ms_per_step * 1e-3) / 1e9

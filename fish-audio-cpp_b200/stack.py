@@ -1,0 +1,220 @@
+"""Slow-AR decoder stack harness: the layer loop of DualAREngine::decode_step
+(src/engine/dual_ar_engine.cc:554-658) on top of the C ABI, with random-init weights.
+
+It exists to measure decode tokens/s of the whole stack (36 layers, hidden 2560, 32 q / 8 kv heads of
+128, SwiGLU 9728, W8A8 at g256, fp16 paged KV with 16-token blocks) at tensor-parallel degree 1/2/4/8.
+Per layer it issues eight launches where the reference issues ~23 plus 19 device copies:
+
+    rmsnorm_quantize (+ residual add of the previous projection)      rms_norm + residual_add + quantiser
+    linear_q  wqkv                                                     int8_dequant_gemm_fp16
+    qknorm_rope_kvwrite                                                3 copies, 2 rms_norm, rope_qk, 16 copies
+    paged_attention_decode (+ quantiser for wo)                        paged_attention_decode + quantiser
+    linear_q  wo            -> partial        [all-reduce when TP > 1]
+    rmsnorm_quantize (+ residual add)                                  residual_add + rms_norm + quantiser
+    linear_q  w1|w3 packed, SwiGLU epilogue                            2 GEMMs + silu + mul
+    quantize ; linear_q  w2 -> partial        [all-reduce when TP > 1]
+
+Tensor parallelism (the reference has none): wqkv and w1|w3 are column-parallel (whole heads, whole
+SwiGLU channels per rank), wo and w2 row-parallel with K cut at quantisation-group boundaries, so every
+per-group int32 sum and every activation scale stays on one rank; the only exchange is one fp16 sum
+all-reduce of [batch, 2560] after wo and after w2.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+
+from . import capi
+
+
+@dataclass
+class SlowARConfig:
+    n_layer: int = 36
+    dim: int = 2560
+    n_head: int = 32
+    n_kv: int = 8
+    head_dim: int = 128
+    inter: int = 9728
+    rope_base: float = 1e6
+    eps: float = 1e-6
+    group: int = 256
+    block_tokens: int = 16
+
+
+def shard_bounds(total_groups: int, world: int):
+    """Row-parallel cut of K at group boundaries: rank r owns groups [b[r], b[r+1]). Sizes differ by at
+    most one group (38 groups over 4 ranks -> 10, 10, 9, 9)."""
+    base, rem = divmod(total_groups, world)
+    b = [0]
+    for r in range(world):
+        b.append(b[-1] + base + (1 if r < rem else 0))
+    return b
+
+
+class SlowARStack:
+    def __init__(self, torch, ctx: capi.Context, cfg: SlowARConfig, batch: int, context: int, max_new: int = 256,
+                 tp_rank: int = 0, tp_size: int = 1, seed: int = 0, all_reduce=None, pack: bool = True,
+                 attn_splits: int = 0):
+        self.torch, self.ctx, self.cfg = torch, ctx, cfg
+        self.B, self.tp_rank, self.tp_size = batch, tp_rank, tp_size
+        self.all_reduce = all_reduce
+        self.attn_splits = attn_splits
+        c = cfg
+        assert c.n_kv % tp_size == 0 and c.n_head == 4 * c.n_kv and c.head_dim == 128
+        g = c.group
+        self.nq_l, self.nkv_l = c.n_head // tp_size, c.n_kv // tp_size
+        self.qkv_n = (self.nq_l + 2 * self.nkv_l) * c.head_dim
+        self.attn_k = self.nq_l * c.head_dim
+        assert self.attn_k % g == 0, "attention shard must hold whole quantisation groups"
+        assert c.inter % g == 0
+        gb = shard_bounds(c.inter // g, tp_size)
+        self.inter_lo, self.inter_hi = gb[tp_rank] * g, gb[tp_rank + 1] * g
+        self.inter_l = self.inter_hi - self.inter_lo
+        assert self.inter_l > 0 and self.inter_l % 8 == 0
+        dev = "cuda"
+        gen = torch.Generator(device=dev)
+
+        def rand_w(n, k, tag):
+            gen.manual_seed(seed * 1000003 + tag)
+            w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev, generator=gen)
+            s = torch.empty((n, k // g), dtype=torch.float32, device=dev).uniform_(1e-3, 5e-3, generator=gen).half()
+            return w, s
+
+        def rand_vec(n, tag):
+            gen.manual_seed(seed * 1000003 + tag)
+            return torch.empty((n,), dtype=torch.float32, device=dev).uniform_(0.8, 1.2, generator=gen).half()
+
+        D = c.head_dim
+        q_lo, q_hi = tp_rank * self.nq_l * D, (tp_rank + 1) * self.nq_l * D
+        kv_lo, kv_hi = tp_rank * self.nkv_l * D, (tp_rank + 1) * self.nkv_l * D
+        self.layers = []
+        self._keep = []
+        for l in range(c.n_layer):
+            t = l * 16
+            wqkv_f, sqkv_f = rand_w((c.n_head + 2 * c.n_kv) * D, c.dim, t + 1)
+            kq, kk = c.n_head * D, c.n_kv * D
+            rows = torch.cat([torch.arange(q_lo, q_hi), kq + torch.arange(kv_lo, kv_hi),
+                              kq + kk + torch.arange(kv_lo, kv_hi)]).to(dev)
+            wqkv, sqkv = wqkv_f[rows].contiguous(), sqkv_f[rows].contiguous()
+            wo_f, so_f = rand_w(c.dim, c.n_head * D, t + 2)
+            wo = wo_f[:, q_lo:q_hi].contiguous()
+            so = so_f[:, q_lo // g:q_hi // g].contiguous()
+            w1_f, s1_f = rand_w(c.inter, c.dim, t + 3)
+            w3_f, s3_f = rand_w(c.inter, c.dim, t + 4)
+            w1, s1 = w1_f[self.inter_lo:self.inter_hi].contiguous(), s1_f[self.inter_lo:self.inter_hi].contiguous()
+            w3, s3 = w3_f[self.inter_lo:self.inter_hi].contiguous(), s3_f[self.inter_lo:self.inter_hi].contiguous()
+            G = c.dim // g
+            w13 = torch.empty((2 * self.inter_l, c.dim), dtype=torch.int8, device=dev)
+            s13 = torch.empty((2 * self.inter_l, G), dtype=torch.float16, device=dev)
+            ctx.pack_gate_up(w1, s1, w3, s3, self.inter_l, c.dim, G, w13, s13)
+            w2_f, s2_f = rand_w(c.dim, c.inter, t + 5)
+            w2 = w2_f[:, self.inter_lo:self.inter_hi].contiguous()
+            s2 = s2_f[:, self.inter_lo // g:self.inter_hi // g].contiguous()
+            torch.cuda.synchronize()
+            del wqkv_f, sqkv_f, wo_f, so_f, w1_f, s1_f, w3_f, s3_f, w2_f, s2_f, w1, w3, s1, s3
+            lw = dict(attn_norm=rand_vec(c.dim, t + 6), ffn_norm=rand_vec(c.dim, t + 7), q_norm=rand_vec(D, t + 8),
+                      k_norm=rand_vec(D, t + 9), wqkv=wqkv, sqkv=sqkv, wo=wo, so=so, w13=w13, s13=s13, w2=w2, s2=s2)
+            if pack:  # what the loader does once per weight: pack for the decode kernel and register the pair
+                for name, sname, n, k in (("wqkv", "sqkv", self.qkv_n, c.dim), ("wo", "so", c.dim, self.attn_k),
+                                          ("w13", "s13", 2 * self.inter_l, c.dim), ("w2", "s2", c.dim, self.inter_l)):
+                    nbytes = ctx.packed_weight_bytes(n, k, g)
+                    if nbytes:
+                        P = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
+                        ctx.pack_weight(lw[name], lw[sname], n, k, g, P)
+                        ctx.register_packed_weight(lw[name], P)
+                        self._keep.append(P)
+            self.layers.append(lw)
+        self.final_norm = rand_vec(c.dim, 999983)
+        freqs = (1.0 / np.power(np.float32(c.rope_base), (np.float32(2.0) * np.arange(D // 2, dtype=np.float32) /
+                                                           np.float32(D)))).astype(np.float32)
+        self.freqs = torch.from_numpy(freqs).to(dev)
+
+        # paged KV, already holding `context` tokens per sequence (synthetic prefill)
+        bt = c.block_tokens
+        self.max_blocks = (context + max_new + bt - 1) // bt
+        nblocks = batch * self.max_blocks
+        gen.manual_seed(seed + 4242 + tp_rank)
+        shape = (nblocks, c.n_layer, self.nkv_l, bt, D)
+        self.k_cache = (torch.randn(shape, dtype=torch.float32, device=dev, generator=gen) * 0.5).half()
+        self.v_cache = (torch.randn(shape, dtype=torch.float32, device=dev, generator=gen) * 0.5).half()
+        perm = torch.randperm(nblocks, device=dev, generator=gen).to(torch.int32)
+        self.block_table = perm.view(batch, self.max_blocks).contiguous()
+        self.positions = torch.full((batch,), context, dtype=torch.int32, device=dev)   # the new token's position
+        self.seq_lens = torch.full((batch,), context + 1, dtype=torch.int32, device=dev)
+        self.context0 = context
+
+        B = batch
+        h16 = dict(dtype=torch.float16, device=dev)
+        self.x = torch.zeros((B, c.dim), **h16)          # residual stream
+        self.delta = torch.zeros((B, c.dim), **h16)      # output of wo / w2 (summed over ranks when TP > 1)
+        self.have_delta = False
+        self.xq = torch.empty((B, c.dim), dtype=torch.int8, device=dev)
+        self.xs = torch.empty((B, c.dim // g), dtype=torch.float32, device=dev)
+        self.qkv = torch.empty((B, self.qkv_n), **h16)
+        self.q = torch.empty((B, self.nq_l, D), **h16)
+        self.aq = torch.empty((B, self.attn_k), dtype=torch.int8, device=dev)
+        self.as_ = torch.empty((B, self.attn_k // g), dtype=torch.float32, device=dev)
+        self.act = torch.empty((B, self.inter_l), **h16)
+        self.actq = torch.empty((B, self.inter_l), dtype=torch.int8, device=dev)
+        self.acts = torch.empty((B, self.inter_l // g), dtype=torch.float32, device=dev)
+        self.out = torch.empty((B, c.dim), **h16)
+        self.launches_per_step = c.n_layer * 9 + 2
+        # bytes the step must move at least once (per rank): weights + scales + the KV it reads
+        wbytes = sum(lw[n].numel() + lw[s].numel() * 2 for lw in self.layers
+                     for n, s in (("wqkv", "sqkv"), ("wo", "so"), ("w13", "s13"), ("w2", "s2")))
+        self.weight_bytes = wbytes
+        self.kv_bytes_per_step = lambda ctx_len: 2 * B * ctx_len * c.n_layer * self.nkv_l * D * 2
+
+    # ------------------------------------------------------------------------------------------
+    def decode_step(self, x_in=None):
+        """One token for every sequence. x_in fp16 [B, dim] (the embedding of the new token); returns
+        the final-normed hidden state in self.out. All launches go to the current stream."""
+        c, ctx, B, g = self.cfg, self.ctx, self.B, self.cfg.group
+        D = c.head_dim
+        if x_in is not None:
+            self.x.copy_(x_in, non_blocking=True)
+        sm_scale = 1.0 / math.sqrt(D)
+        pending = False  # a projection output waiting to be added to the residual stream
+        for l, lw in enumerate(self.layers):
+            ctx.rmsnorm_quantize(self.x, lw["attn_norm"], c.eps, B, c.dim, g, self.xq, self.xs,
+                                 residual=self.delta if pending else None)
+            ctx.linear_q(lw["wqkv"], lw["sqkv"], g, self.xq, self.xs, self.qkv, B, self.qkv_n, c.dim)
+            ctx.qknorm_rope_kvwrite(self.qkv, lw["q_norm"], lw["k_norm"], c.eps, self.freqs, self.positions,
+                                    self.block_table, self.max_blocks, self.k_cache, self.v_cache, l, c.n_layer, B,
+                                    self.nq_l, self.nkv_l, D, self.q)
+            ctx.paged_attention_decode(self.q, self.k_cache, self.v_cache, self.block_table, self.seq_lens, None, B,
+                                       self.nq_l, D, self.max_blocks, sm_scale, l, c.n_layer, self.nkv_l,
+                                       quant_group_size=g, Xq=self.aq, Xs=self.as_, context_splits=self.attn_splits)
+            ctx.linear_q(lw["wo"], lw["so"], g, self.aq, self.as_, self.delta, B, c.dim, self.attn_k)
+            if self.all_reduce is not None:
+                self.all_reduce(self.delta)
+            ctx.rmsnorm_quantize(self.x, lw["ffn_norm"], c.eps, B, c.dim, g, self.xq, self.xs, residual=self.delta)
+            ctx.linear_q(lw["w13"], lw["s13"], g, self.xq, self.xs, self.act, B, 2 * self.inter_l, c.dim,
+                         epilogue=capi.EPI_SWIGLU)
+            ctx.quantize(self.act, B, self.inter_l, g, self.actq, self.acts)
+            ctx.linear_q(lw["w2"], lw["s2"], g, self.actq, self.acts, self.delta, B, c.dim, self.inter_l)
+            if self.all_reduce is not None:
+                self.all_reduce(self.delta)
+            pending = True
+        ctx.residual_add(self.x, self.delta, B * c.dim)
+        ctx.rms_norm(self.x, self.final_norm, self.out, B, c.dim, c.eps)
+        self.positions.add_(1)
+        self.seq_lens.add_(1)
+        return self.out
+
+    def linears_only(self):
+        """Only the four W8A8 linears of every layer, on whatever the activation buffers hold: the
+        benchmark times these alone to put the dominant kernel on the roofline."""
+        c, ctx, B, g = self.cfg, self.ctx, self.B, self.cfg.group
+        for lw in self.layers:
+            ctx.linear_q(lw["wqkv"], lw["sqkv"], g, self.xq, self.xs, self.qkv, B, self.qkv_n, c.dim)
+            ctx.linear_q(lw["wo"], lw["so"], g, self.aq, self.as_, self.delta, B, c.dim, self.attn_k)
+            ctx.linear_q(lw["w13"], lw["s13"], g, self.xq, self.xs, self.act, B, 2 * self.inter_l, c.dim,
+                         epilogue=capi.EPI_SWIGLU)
+            ctx.linear_q(lw["w2"], lw["s2"], g, self.actq, self.acts, self.delta, B, c.dim, self.inter_l)
+
+    def reset_positions(self):
+        self.positions.fill_(self.context0)
+        self.seq_lens.fill_(self.context0 + 1)

@@ -1,0 +1,52 @@
+"""Rank body of tests/test_tp_sharding_cpu.py (a module of its own so that spawned children can import it:
+it registers the hyphen-named package directory before anything else)."""
+import os
+import sys
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+import __graft_entry__ as ge  # noqa: E402
+
+ge.package()
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+
+from fish_audio_cpp_b200 import stack as S  # noqa: E402
+from fish_audio_cpp_b200 import synth  # noqa: E402
+
+
+def worker(rank, world, port, q):
+    from oracle import oracle
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, N, K, g = 5, 48, 768, 256          # 3 groups over 2 ranks: 2 + 1
+        X, W, ws = synth.linear_case(3, M, N, K, g)
+        full = oracle.linear(W, ws, g, X)
+        # column-parallel: rows [rank*N/world, ...) — outputs are independent per row
+        lo, hi = rank * N // world, (rank + 1) * N // world
+        part = torch.from_numpy(oracle.linear(W[lo:hi], ws[lo:hi], g, X).view(np.uint16).astype(np.int32))
+        gathered = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(gathered, part)
+        col = np.concatenate([t.numpy().astype(np.uint16) for t in gathered], axis=1).view(np.float16)
+        ok_col = bool(np.array_equal(col.view(np.uint16), full.view(np.uint16)))
+        # row-parallel: K cut at group boundaries; activation scales are per (token, group) so the local
+        # quantiser needs nothing from the other rank
+        b = S.shard_bounds(K // g, world)
+        k0, k1 = b[rank] * g, b[rank + 1] * g
+        Xq, Xs = oracle.quantize(X[:, k0:k1], g)
+        fq, fs = oracle.quantize(X, g)
+        ok_quant = bool(np.array_equal(Xq, fq[:, k0:k1]) and np.array_equal(Xs, fs[:, b[rank]:b[rank + 1]]))
+        _, y32 = oracle.linear_q(np.ascontiguousarray(W[:, k0:k1]), ws.reshape(N, -1)[:, b[rank]:b[rank + 1]], Xq, Xs, g,
+                                 want_f32=True)
+        t = torch.from_numpy(y32.copy())
+        dist.all_reduce(t)
+        ulp = oracle.ulp_distance_fp16(t.numpy().astype(np.float16), full).max()
+        q.put((rank, ok_col, ok_quant, int(ulp)))
+    finally:
+        dist.destroy_process_group()
+
+

@@ -1,0 +1,73 @@
+"""The decoder-stack harness (layer loop of DualAREngine::decode_step) against the oracle chain, small config."""
+import numpy as np
+import pytest
+import torch
+
+from fish_audio_cpp_b200 import stack as S
+
+pytestmark = pytest.mark.gpu
+
+
+def oracle_step(oracle, st, x_in, k_cache, v_cache, bt, positions):
+    c = st.cfg
+    g, D, B = c.group, c.head_dim, x_in.shape[0]
+    cpu = lambda t: t.cpu().numpy()
+    freqs = cpu(st.freqs)
+    x = x_in.copy()
+    pending = None
+    for l, lw in enumerate(st.layers):
+        if pending is not None:
+            x = oracle.residual_add(x, pending)
+        h = oracle.rms_norm(x, cpu(lw["attn_norm"]), c.eps)
+        qkv = oracle.linear(cpu(lw["wqkv"]), cpu(lw["sqkv"]), g, h).reshape(B, st.nq_l + 2 * st.nkv_l, D)
+        q = np.empty((B, st.nq_l, D), np.float16)
+        for b in range(B):
+            pos = int(positions[b])
+            q[b] = oracle.qknorm_rope(qkv[b, :st.nq_l], cpu(lw["q_norm"]), c.eps, freqs, pos)
+            kk = oracle.qknorm_rope(qkv[b, st.nq_l:st.nq_l + st.nkv_l], cpu(lw["k_norm"]), c.eps, freqs, pos)
+            phys = bt[b, pos // 16]
+            k_cache[phys, l, :, pos % 16] = kk
+            v_cache[phys, l, :, pos % 16] = qkv[b, st.nq_l + st.nkv_l:]
+        att = oracle.paged_attention_decode(q, k_cache, v_cache, bt, positions + 1, l, 1.0 / np.sqrt(D))
+        att16 = att.astype(np.float16).reshape(B, st.attn_k)
+        delta = oracle.linear(cpu(lw["wo"]), cpu(lw["so"]), g, att16)
+        x = oracle.residual_add(x, delta)
+        h2 = oracle.rms_norm(x, cpu(lw["ffn_norm"]), c.eps)
+        act = oracle.linear(cpu(lw["w13"]), cpu(lw["s13"]), g, h2, epilogue=oracle.EPI_SWIGLU)
+        pending = oracle.linear(cpu(lw["w2"]), cpu(lw["s2"]), g, act)
+    x = oracle.residual_add(x, pending)
+    return oracle.rms_norm(x, cpu(st.final_norm), c.eps)
+
+
+@pytest.mark.parametrize("group", [64, 256])
+def test_stack_matches_oracle_chain(ctx, oracle, group):
+    cfg = S.SlowARConfig(n_layer=2, dim=512, n_head=4, n_kv=1, inter=512, group=group)
+    B, context = 3, 37
+    st = S.SlowARStack(torch, ctx, cfg, B, context, max_new=8, seed=5)
+    rng = np.random.default_rng(group)
+    x_in = rng.standard_normal((B, cfg.dim)).astype(np.float16)
+    kc, vc = st.k_cache.cpu().numpy().copy(), st.v_cache.cpu().numpy().copy()
+    bt, pos = st.block_table.cpu().numpy(), st.positions.cpu().numpy().copy()
+    out = st.decode_step(torch.from_numpy(x_in).cuda())
+    torch.cuda.synchronize()
+    ctx.check_device_status()
+    want = oracle_step(oracle, st, x_in, kc, vc, bt, pos).astype(np.float32)
+    got = out.cpu().numpy().astype(np.float32)
+    rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+    assert rel < 2e-2, rel
+    assert int(st.positions[0]) == context + 1 and int(st.seq_lens[0]) == context + 2
+    # graph replay gives the same bits as the eager step from the same state
+    st.reset_positions()
+    st.k_cache.copy_(torch.from_numpy(kc).cuda()); st.v_cache.copy_(torch.from_numpy(vc).cuda())
+    xin = torch.from_numpy(x_in).cuda()
+    st.decode_step(xin); torch.cuda.synchronize()   # warm (attributes set), state advanced
+    st.reset_positions()
+    st.k_cache.copy_(torch.from_numpy(kc).cuda()); st.v_cache.copy_(torch.from_numpy(vc).cuda())
+    gr = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(gr):
+        st.decode_step(xin)
+    st.reset_positions()
+    st.k_cache.copy_(torch.from_numpy(kc).cuda()); st.v_cache.copy_(torch.from_numpy(vc).cuda())
+    gr.replay(); torch.cuda.synchronize()
+    assert np.array_equal(st.out.cpu().numpy().view(np.uint16), out.cpu().numpy().view(np.uint16)) or \
+        np.linalg.norm(st.out.cpu().numpy().astype(np.float32) - got) / np.linalg.norm(got) < 1e-3

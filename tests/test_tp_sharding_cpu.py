@@ -1,0 +1,45 @@
+"""Tensor-parallel sharding of the linear path, checked on CPU with world_size-2 gloo ranks and the
+oracle as the arithmetic: column-parallel shards gather to exactly the full result; row-parallel shards
+(K cut at quantisation-group boundaries) all-reduce to the full result up to fp32 re-association."""
+import socket
+
+import sys
+from pathlib import Path
+
+import pytest
+import torch.multiprocessing as mp
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+from fish_audio_cpp_b200 import stack as S
+
+import _tp_worker
+
+
+def test_shard_bounds():
+    assert S.shard_bounds(38, 4) == [0, 10, 20, 29, 38]          # down at g256 over 4 ranks: 10/10/9/9
+    assert S.shard_bounds(38, 8) == [0, 5, 10, 15, 20, 25, 30, 34, 38]
+    assert S.shard_bounds(152, 8)[-1] == 152 and S.shard_bounds(16, 2) == [0, 8, 16]
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+@pytest.mark.timeout(120)
+def test_row_and_column_parallel_with_gloo():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_worker.worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=100) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    for rank, ok_col, ok_quant, ulp in res:
+        assert ok_col, "column-parallel shards must gather to the full result bit for bit"
+        assert ok_quant, "per-(token, group) quantisation must not depend on the shard"
+        assert ulp <= 1, f"row-parallel all-reduce differs by {ulp} fp16 ulp"
