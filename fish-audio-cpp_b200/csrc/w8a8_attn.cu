@@ -126,7 +126,7 @@ struct AttnParams {
     int S;                    // context slices = cluster size
 };
 
-constexpr int kAttnWarps = 8;
+constexpr int kAttnWarps = 4;
 constexpr int kQPerKv = 4;  // query heads per kv head handled by one CTA
 
 struct SoftState {  // per (head) running softmax state of one lane group: 16 of the 128 dims
@@ -151,17 +151,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32) paged_attention_decode_kernel
     const int n_blocks = (seq_len + kBlockTokens - 1) / kBlockTokens;
     const int heads_here = p.n_q / p.n_kv;  // == kQPerKv (checked on the host)
 
-    // q for this lane's 16 dims, all 4 heads, pre-scaled
-    float q[kQPerKv][16];
-#pragma unroll
-    for (int hh = 0; hh < kQPerKv; ++hh) {
-        const __half* qp = p.q + (static_cast<size_t>(b) * p.n_q + kvh * heads_here + hh) * kHeadDim + sub * 16;
-        const uint4 u0 = *reinterpret_cast<const uint4*>(qp), u1 = *reinterpret_cast<const uint4*>(qp + 8);
-        const __half* h0 = reinterpret_cast<const __half*>(&u0);
-        const __half* h1 = reinterpret_cast<const __half*>(&u1);
-#pragma unroll
-        for (int d = 0; d < 8; ++d) { q[hh][d] = __half2float(h0[d]); q[hh][8 + d] = __half2float(h1[d]); }
-    }
+    // q of the 4 heads as fp32 in shared memory (read back as broadcast 128-bit loads)
+    __shared__ __align__(16) float q_s[kQPerKv][kHeadDim];
+    for (int i = threadIdx.x; i < kQPerKv * kHeadDim; i += blockDim.x)
+        q_s[i / kHeadDim][i % kHeadDim] =
+            __half2float(p.q[(static_cast<size_t>(b) * p.n_q + kvh * heads_here + i / kHeadDim) * kHeadDim + i % kHeadDim]);
+    __syncthreads();
     SoftState st[kQPerKv];
 #pragma unroll
     for (int hh = 0; hh < kQPerKv; ++hh) {
@@ -170,26 +165,33 @@ __global__ void __launch_bounds__(kAttnWarps * 32) paged_attention_decode_kernel
         for (int d = 0; d < 16; ++d) st[hh].acc[d] = 0.0f;
     }
 
-    // 16-token blocks are dealt round-robin: first over the cluster's CTAs, then over the warps
+    // 16-token blocks are dealt round-robin: first over the cluster's CTAs, then over the warps. All 16
+    // loads of a block (4 passes x K and V halves) are requested before any arithmetic, so that a warp
+    // keeps 8 KB in flight instead of paying one memory round trip per pass.
     for (int bi = s + warp * S; bi < n_blocks; bi += S * kAttnWarps) {
         const int phys = p.block_table[static_cast<size_t>(b) * p.max_blocks + bi];
         const size_t base = (((static_cast<size_t>(phys) * p.n_layers + p.layer) * p.n_kv + kvh) * kBlockTokens) * kHeadDim;
         const int tokens = min(kBlockTokens, seq_len - bi * kBlockTokens);
+        uint4 kraw[4][2], vraw[4][2];
+#pragma unroll
+        for (int pass = 0; pass < 4; ++pass) {
+            const int t = pass * 4 + grp;
+            const size_t off = base + static_cast<size_t>(t < tokens ? t : 0) * kHeadDim + sub * 16;
+            kraw[pass][0] = *reinterpret_cast<const uint4*>(p.k_cache + off);
+            kraw[pass][1] = *reinterpret_cast<const uint4*>(p.k_cache + off + 8);
+            vraw[pass][0] = *reinterpret_cast<const uint4*>(p.v_cache + off);
+            vraw[pass][1] = *reinterpret_cast<const uint4*>(p.v_cache + off + 8);
+        }
 #pragma unroll
         for (int pass = 0; pass < 4; ++pass) {
             const int t = pass * 4 + grp;
             const bool live = t < tokens;
-            const size_t off = base + static_cast<size_t>(live ? t : 0) * kHeadDim + sub * 16;
-            const uint4 k0 = *reinterpret_cast<const uint4*>(p.k_cache + off);
-            const uint4 k1 = *reinterpret_cast<const uint4*>(p.k_cache + off + 8);
-            const uint4 v0 = *reinterpret_cast<const uint4*>(p.v_cache + off);
-            const uint4 v1 = *reinterpret_cast<const uint4*>(p.v_cache + off + 8);
             float kf[16], vf[16];
             {
-                const __half* a0 = reinterpret_cast<const __half*>(&k0);
-                const __half* a1 = reinterpret_cast<const __half*>(&k1);
-                const __half* b0 = reinterpret_cast<const __half*>(&v0);
-                const __half* b1 = reinterpret_cast<const __half*>(&v1);
+                const __half* a0 = reinterpret_cast<const __half*>(&kraw[pass][0]);
+                const __half* a1 = reinterpret_cast<const __half*>(&kraw[pass][1]);
+                const __half* b0 = reinterpret_cast<const __half*>(&vraw[pass][0]);
+                const __half* b1 = reinterpret_cast<const __half*>(&vraw[pass][1]);
 #pragma unroll
                 for (int d = 0; d < 8; ++d) {
                     kf[d] = __half2float(a0[d]); kf[8 + d] = __half2float(a1[d]);
@@ -200,7 +202,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32) paged_attention_decode_kernel
             for (int hh = 0; hh < kQPerKv; ++hh) {
                 float dot = 0.0f;
 #pragma unroll
-                for (int d = 0; d < 16; ++d) dot = fmaf(q[hh][d], kf[d], dot);
+                for (int d4 = 0; d4 < 4; ++d4) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(&q_s[hh][sub * 16 + d4 * 4]);
+                    dot = fmaf(q4.x, kf[d4 * 4 + 0], dot);
+                    dot = fmaf(q4.y, kf[d4 * 4 + 1], dot);
+                    dot = fmaf(q4.z, kf[d4 * 4 + 2], dot);
+                    dot = fmaf(q4.w, kf[d4 * 4 + 3], dot);
+                }
                 dot += __shfl_xor_sync(0xffffffffu, dot, 1);
                 dot += __shfl_xor_sync(0xffffffffu, dot, 2);
                 dot += __shfl_xor_sync(0xffffffffu, dot, 4);
@@ -241,45 +249,47 @@ __global__ void __launch_bounds__(kAttnWarps * 32) paged_attention_decode_kernel
         }
     }
     __syncthreads();
-    // ---- merge the warps: thread -> (head, 2 dims) ----
+    // ---- merge the warps: thread -> (head, 4 dims) ----
     {
-        const int hh = threadIdx.x >> 6, d0 = (threadIdx.x & 63) * 2;
+        const int hh = threadIdx.x >> 5, d0 = (threadIdx.x & 31) * 4;
         float m = -1e30f;
         for (int w = 0; w < kAttnWarps; ++w) m = fmaxf(m, red_m[w][hh]);
-        float l = 0.0f, a0 = 0.0f, a1 = 0.0f;
+        float l = 0.0f, a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (int w = 0; w < kAttnWarps; ++w) {
             const float sc = expf(red_m[w][hh] - m);
             l += red_l[w][hh] * sc;
-            a0 += red_acc[w][hh][d0] * sc;
-            a1 += red_acc[w][hh][d0 + 1] * sc;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) a[i] += red_acc[w][hh][d0 + i] * sc;
         }
-        cta_acc[hh][d0] = a0;
-        cta_acc[hh][d0 + 1] = a1;
-        if ((threadIdx.x & 63) == 0) { cta_m[hh] = m; cta_l[hh] = l; }
+#pragma unroll
+        for (int i = 0; i < 4; ++i) cta_acc[hh][d0 + i] = a[i];
+        if ((threadIdx.x & 31) == 0) { cta_m[hh] = m; cta_l[hh] = l; }
     }
     cg::cluster_group cluster = cg::this_cluster();
     if (S > 1) cluster.sync(); else __syncthreads();
     // ---- CTA 0 of the cluster merges the S context slices and writes the 4 heads ----
     if (s == 0) {
-        const int hh = threadIdx.x >> 6, d0 = (threadIdx.x & 63) * 2;
+        const int hh = threadIdx.x >> 5, d0 = (threadIdx.x & 31) * 4;
         float m = -1e30f;
         for (int r = 0; r < S; ++r) m = fmaxf(m, (S > 1 ? cluster.map_shared_rank(cta_m, r) : cta_m)[hh]);
-        float l = 0.0f, a0 = 0.0f, a1 = 0.0f;
+        float l = 0.0f, a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (int r = 0; r < S; ++r) {
             const float* pm = S > 1 ? cluster.map_shared_rank(cta_m, r) : cta_m;
             const float* pl = S > 1 ? cluster.map_shared_rank(cta_l, r) : cta_l;
             const float* pa = S > 1 ? cluster.map_shared_rank(&cta_acc[0][0], r) : &cta_acc[0][0];
             const float sc = expf(pm[hh] - m);
             l += pl[hh] * sc;
-            a0 += pa[hh * kHeadDim + d0] * sc;
-            a1 += pa[hh * kHeadDim + d0 + 1] * sc;
+            const float4 v4 = *reinterpret_cast<const float4*>(pa + hh * kHeadDim + d0);
+            a[0] += v4.x * sc; a[1] += v4.y * sc; a[2] += v4.z * sc; a[3] += v4.w * sc;
         }
         const float inv = seq_len > 0 ? 1.0f / l : 0.0f;  // empty sequence -> zeros (paged_attention.cu:44-50)
-        const __half o0 = __float2half(seq_len > 0 ? a0 * inv : 0.0f), o1 = __float2half(seq_len > 0 ? a1 * inv : 0.0f);
-        out_s[hh * kHeadDim + d0] = o0;
-        out_s[hh * kHeadDim + d0 + 1] = o1;
+        __align__(8) __half o4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o4[i] = __float2half(seq_len > 0 ? a[i] * inv : 0.0f);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) out_s[hh * kHeadDim + d0 + i] = o4[i];
         const size_t o = (static_cast<size_t>(b) * p.n_q + kvh * heads_here + hh) * kHeadDim + d0;
-        if (p.out) *reinterpret_cast<__half2*>(p.out + o) = __halves2half2(o0, o1);
+        if (p.out) *reinterpret_cast<uint2*>(p.out + o) = *reinterpret_cast<const uint2*>(o4);
     }
     if (S > 1) cluster.sync(); else __syncthreads();
     // ---- optional: quantise these 512 channels for the o-projection (int8_gemm.cu:147-211) ----

@@ -186,6 +186,107 @@ __global__ void __launch_bounds__(1024) rowquant_kernel(const RowQuantParams p) 
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Register-resident form of the fused row kernel for rows of at most 4 x blockDim elements (the decode
+// case: K = 2560 with 1024 threads). Same arithmetic and the same summation order as rowquant_kernel —
+// thread t owns elements t, t+T, t+2T, ... exactly like the reference's rms_norm launch — but nothing is
+// staged in shared memory and only three block barriers separate the first load from the last store;
+// at 8 rows per launch the kernel's length is a latency chain, not a bandwidth figure. Needs g % 32 == 0
+// so that the 32 lanes of a warp always sit in one quantisation group.
+constexpr int kFastElems = 4;
+__global__ void __launch_bounds__(1024) rowquant_fast_kernel(const RowQuantParams p) {
+    __shared__ float s_red[kWarp];
+    __shared__ unsigned s_gmax[160];  // absmax per group as float bits (non-negative floats order like uints)
+    const int tid = threadIdx.x, T = blockDim.x, K = p.K, g = p.g, G = p.G;
+    const int lane = tid & (kWarp - 1), warp = tid / kWarp;
+    const size_t base = static_cast<size_t>(blockIdx.x) * K;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    for (int j = tid; j < G; j += T) s_gmax[j] = 0u;
+
+    __half h[kFastElems];
+    float local_sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kFastElems; ++i) {
+        const int e = tid + i * T;
+        if (e < K) {
+            __half v = p.x_in[base + e];
+            if (p.residual) {
+                v = __float2half(__half2float(v) + __half2float(p.residual[base + e]));
+                if (p.x_out) p.x_out[base + e] = v;
+            }
+            h[i] = v;
+            float val = __half2float(v);
+            local_sum += val * val;
+        }
+    }
+    if (p.norm_weight) {
+        for (int offset = kWarp / 2; offset > 0; offset /= 2)
+            local_sum += __shfl_down_sync(0xffffffffu, local_sum, offset);
+        if (lane == 0) s_red[warp] = local_sum;
+        __syncthreads();
+        float total_sum = 0.0f;
+        const int num_warps = (T + kWarp - 1) / kWarp;
+        if (tid < num_warps) total_sum = s_red[tid];
+        if (warp == 0) {
+            for (int offset = kWarp / 2; offset > 0; offset /= 2)
+                total_sum += __shfl_down_sync(0xffffffffu, total_sum, offset);
+        }
+        __syncthreads();
+        if (tid == 0) s_red[0] = rsqrtf(total_sum / K + p.eps);
+        __syncthreads();
+        const float rms = s_red[0];
+#pragma unroll
+        for (int i = 0; i < kFastElems; ++i) {
+            const int e = tid + i * T;
+            if (e < K) {
+                float val = __half2float(h[i]) * rms;
+                h[i] = __float2half(val * __half2float(p.norm_weight[e]));
+                if (p.normed_out) p.normed_out[base + e] = h[i];
+            }
+        }
+    }
+    if (!p.Xq) return;
+    float v[kFastElems];
+#pragma unroll
+    for (int i = 0; i < kFastElems; ++i) {
+        const int e = tid + i * T;
+        v[i] = 0.0f;
+        if (e < K) {
+            v[i] = __half2float(h[i]);
+            if (p.smooth_inv) v[i] *= __half2float(p.smooth_inv[e]);
+        }
+    }
+    if (!p.act_scale) {
+#pragma unroll
+        for (int i = 0; i < kFastElems; ++i) {
+            const int e0 = warp * kWarp + i * T;  // first element of this warp's run
+            if (e0 < K) {
+                float m = warp_max(fabsf(v[i]));
+                if (lane == 0) atomicMax(&s_gmax[p.per_token ? 0 : e0 / g], __float_as_uint(m));
+            }
+        }
+    }
+    __syncthreads();
+    for (int j = tid; j < G; j += T) {
+        float sc = p.act_scale ? __half2float(p.act_scale[j]) : __uint_as_float(s_gmax[p.per_token ? 0 : j]) / 127.0f;
+        if (sc < 1e-8f) sc = 1e-8f;
+        p.Xs[static_cast<size_t>(blockIdx.x) * G + j] = sc;
+    }
+#pragma unroll
+    for (int i = 0; i < kFastElems; ++i) {
+        const int e = tid + i * T;
+        if (e < K) {
+            const int j = e / g;
+            float sc = p.act_scale ? __half2float(p.act_scale[j]) : __uint_as_float(s_gmax[p.per_token ? 0 : j]) / 127.0f;
+            if (sc < 1e-8f) sc = 1e-8f;
+            const float inv_scale = 1.0f / sc;
+            int q = __float2int_rn(v[i] * inv_scale);
+            q = max(-127, min(127, q));
+            p.Xq[base + e] = static_cast<int8_t>(q);
+        }
+    }
+}
+
 // The quantiser alone (int8_gemm.cu:147-211) for g in {64, 128, 256}: no shared memory, no block
 // barrier. A thread owns 8 consecutive activations (one 128-bit load), the g/8 threads of a group
 // find the absmax with shuffles, and each thread stores its 8 codes as one 64-bit word. At decode
@@ -297,6 +398,20 @@ int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
         if (threads < 32) threads = 32;  // shuffles need whole warps; lanes past K add 0.0f
     } else if (K >= 4096) {
         threads = 512;
+    }
+    if (norm_weight && threads >= 32 && K <= kFastElems * threads && p.g % 32 == 0 && p.G <= 160) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(M, 1, 1);
+        cfg.blockDim = dim3(threads, 1, 1);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled() ? 1 : 0;
+        cudaError_t e = cudaLaunchKernelEx(&cfg, rowquant_fast_kernel, p);
+        if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "rowquant_fast launch: %s", cudaGetErrorString(e));
+        return W8A8_OK;
     }
     size_t smem = ((static_cast<size_t>(K) * 2 + 15) & ~size_t(15)) + static_cast<size_t>(p.G) * 4;
     if (smem > 200 * 1024) return fail(W8A8_ERR_UNSUPPORTED, "row of K=%d does not fit shared memory", K);
