@@ -241,16 +241,23 @@ class DecodeStack:
     """configs[3]: the full slow-AR decoder stack, batch 8, context 1024, g256, tensor-parallel over the
     ranks of the job. One step = one token for each of the 8 sequences, replayed from a CUDA graph."""
 
-    def __init__(self, torch, ctx, world, rank, dist, layers=36, batch=8, context=1024, group=256, reference=False):
+    def __init__(self, torch, ctx, world, rank, dist, layers=36, batch=8, context=1024, group=256, reference=False,
+                 tp_mode="fused"):
         from fish_audio_cpp_b200 import stack as S
 
         self.torch, self.ctx, self.dist, self.world = torch, ctx, dist, world
         cfg = S.SlowARConfig(n_layer=layers, group=group)
-        ar = None
-        if world > 1:
-            ar = lambda t: dist.all_reduce(t)  # noqa: E731  (fp16 sum over NVLink, NCCL)
+        ar, gather = None, None
+        self.tp_mode = tp_mode if world > 1 else "none"
+        if world > 1 and tp_mode == "nccl":
+            ar = lambda t: dist.all_reduce(t)  # noqa: E731  (fp16 sum over NVLink, NCCL: the baseline)
+        if world > 1 and tp_mode == "fused":
+            def gather(handle):
+                out = [None] * world
+                dist.all_gather_object(out, handle)
+                return out
         self.st = S.SlowARStack(torch, ctx, cfg, batch, context, max_new=128, tp_rank=rank, tp_size=world,
-                                seed=7, all_reduce=ar, pack=not reference)
+                                seed=7, all_reduce=ar, pack=not reference, tp_mode=tp_mode, gather_handles=gather)
         self.cfg, self.batch, self.context = cfg, batch, context
         self.ref = ReferenceStack(torch, self.st) if reference else None
         self.host_x = (torch.randn((batch, cfg.dim), generator=torch.Generator().manual_seed(3)) * 0.5).half().pin_memory()
@@ -436,6 +443,20 @@ def cpu_baseline_sweep(budget_s=20.0):
 
 
 # ------------------------------------------------------------------------------------------
+def finish(dist, wl):
+    """Leaves a multi-rank job without tearing NCCL down: a communicator destroyed while captured graphs
+    that used it are alive has hung at exit, so graphs go first and the process exits hard."""
+    import torch
+
+    torch.cuda.synchronize()
+    if dist is None:
+        return
+    getattr(wl, "graphs", {}).clear()
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -443,6 +464,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=["decode_stack", "decode_sweep"], default="decode_stack")
+    ap.add_argument("--tp-mode", choices=["fused", "nccl"], default="fused",
+                    help="N > 1: all-reduce inside the norm kernel over peer memory (fused) or NCCL (baseline)")
     ap.add_argument("--layers", type=int, default=36, help="decode_stack: number of layers (36 = the named config)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only", default=None, metavar="NAME:M:G",
@@ -470,6 +493,14 @@ def main():
         raise SystemExit("bench.py needs a GPU: there is no CPU fallback for the product path")
     torch.cuda.set_device(local_rank)
     dist = None
+    if world > 1 and args.impl == "reference":
+        # the reference has no multi-GPU path: rank 0 alone runs it, the others leave at once
+        if rank != 0:
+            return
+        world = 1
+        declared_world = int(os.environ.get("WORLD_SIZE", "1"))
+    else:
+        declared_world = world
     if world > 1:
         import torch.distributed as dist
 
@@ -487,11 +518,6 @@ def main():
                                   "oracle/_ref/libfishref.so was not built (no reference checkout at build time)"}))
             return
         if args.workload == "decode_stack":
-            if rank != 0:  # the reference has no multi-GPU path: rank 0 alone runs it
-                if dist is not None:
-                    dist.barrier()
-                    dist.destroy_process_group()
-                return
             ctx = pkg.Context(local_rank, 1 << 24)  # builds the weights and the cache; no kernel of ours is timed
             wl = DecodeStack(torch, ctx, 1, 0, None, layers=args.layers, reference=True)
             solo_reference = True
@@ -500,7 +526,7 @@ def main():
     else:
         ctx = pkg.Context(local_rank, 0)
         if args.workload == "decode_stack":
-            wl = DecodeStack(torch, ctx, world, rank, dist, layers=args.layers)
+            wl = DecodeStack(torch, ctx, world, rank, dist, layers=args.layers, tp_mode=args.tp_mode)
         else:
             wl = DecodeSweep(torch, ctx, pack=not args.no_pack)
 
@@ -543,11 +569,8 @@ def main():
     if dist is not None and not solo_reference:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms_max, lin_s = times.tolist()
-    if solo_reference and dist is not None:
-        dist.barrier()
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        finish(dist, wl)
         return
 
     pk = peaks()
@@ -563,7 +586,9 @@ def main():
                                    "SwiGLU 9728, W8A8 g256, fp16 paged KV (16-token blocks), batch 8, context 1024, "
                                    "random-init weights; LM head and sampling outside the step",
                        "global_batch": wl.batch, "context": wl.context,
-                       "parallelism": f"tp{n_gpus}" + (" (NCCL fp16 all-reduce after wo and w2)" if n_gpus > 1 else ""),
+                       "parallelism": f"tp{n_gpus}" + ((" (all-reduce after wo and w2 fused into the norm kernel over NVLink peer "
+                                                              "memory)" if wl.tp_mode == "fused" else
+                                                              " (NCCL fp16 all-reduce after wo and w2)") if n_gpus > 1 else ""),
                        "l2": "inputs larger than L2: a step streams 3.6 GB of weights + 1.2 GB of KV",
                        "step_hbm_gbs_per_gpu": round(wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9, 1),
                        "step_hbm_frac_per_gpu": round(wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9 / pk["hbm_gbs"], 4)},
@@ -578,7 +603,7 @@ def main():
                                 "algorithmic_bytes_per_launch": int(lin[1]), "us_per_launch": round(lin_s * 1e6, 2)}
         if reference:
             line["impl"] = "reference"
-            line["n_gpus"] = world
+            line["n_gpus"] = declared_world
             line["config"]["parallelism"] = "single GPU (the reference has no multi-GPU path; rank 0 alone ran)"
             line["gpu_launches"] = None
             line["cpu_baseline"] = {"value": line["value"], "unit": "tokens/s", "cores": 0, "kind": "reference",
@@ -591,9 +616,8 @@ def main():
                            "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h}
             if not args.no_cpu_baseline:
                 line["cpu_baseline"] = cpu_baseline_stack()
-        print(json.dumps(line))
-        if dist is not None:
-            dist.destroy_process_group()
+        print(json.dumps(line), flush=True)
+        finish(dist, wl)
         return
     ms_per_step = dev_ms / args.steps
     total_bytes = wl.bytes_per_step * world
@@ -630,9 +654,8 @@ def main():
                        "d2h_bytes_per_step": wl.d2h}
         if not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_sweep()
-    print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    print(json.dumps(line), flush=True)
+    finish(dist, wl)
 
 
 if __name__ == "__main__":

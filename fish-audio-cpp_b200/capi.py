@@ -61,6 +61,9 @@ def load_library() -> C.CDLL:
         "w8a8_pack_gate_up": (I, [P, P, P, P, P, I, I, I, P, P, P]),
         "w8a8_qknorm_rope_kvwrite": (I, [P, P, P, P, F, P, P, P, I, P, P, I, I, I, I, I, I, P, P]),
         "w8a8_paged_attention_decode": (I, [P, P, P, P, P, P, P, I, I, I, I, F, I, I, I, I, P, P, I, P]),
+        "w8a8_tp_create": (I, [P, I, I, I, I, P]),
+        "w8a8_tp_connect": (I, [P, P]),
+        "w8a8_tp_allreduce_rmsnorm_quantize": (I, [P, P, P, P, F, P, P, I, I, I, I, P, P, P, P]),
         "w8a8_packed_weight_bytes": (Z, [I, I, I]),
         "w8a8_pack_weight": (I, [P, P, P, I, I, I, P, P]),
         "w8a8_register_packed_weight": (I, [P, P, P]),
@@ -79,7 +82,8 @@ EXPORTS = [
     "w8a8_status_string", "w8a8_last_error", "w8a8_create", "w8a8_destroy", "w8a8_workspace_bytes",
     "w8a8_ctx_workspace_bytes", "w8a8_check_device_status", "w8a8_quantize", "w8a8_rms_norm",
     "w8a8_rmsnorm_quantize", "w8a8_silu", "w8a8_mul", "w8a8_residual_add", "w8a8_linear", "w8a8_linear_q",
-    "w8a8_pack_gate_up", "w8a8_qknorm_rope_kvwrite", "w8a8_paged_attention_decode", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
+    "w8a8_pack_gate_up", "w8a8_qknorm_rope_kvwrite", "w8a8_paged_attention_decode", "w8a8_tp_create", "w8a8_tp_connect",
+    "w8a8_tp_allreduce_rmsnorm_quantize", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
     "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch",
 ]
 
@@ -223,6 +227,23 @@ class Context:
                                                          head_dim, max_blocks, sm_scale, layer, n_layers, n_kv,
                                                          quant_group_size, _ptr(Xq), _ptr(Xs), context_splits,
                                                          _stream(stream)), "w8a8_paged_attention_decode")
+
+    def tp_create(self, rank, world, max_tokens, dim) -> bytes:
+        """Allocates this rank's exchange buffer; returns its 64-byte IPC handle."""
+        buf = C.create_string_buffer(64)
+        self._check(self.lib.w8a8_tp_create(self.handle, rank, world, max_tokens, dim, buf), "w8a8_tp_create")
+        return buf.raw
+
+    def tp_connect(self, all_handles: bytes):
+        self._check(self.lib.w8a8_tp_connect(self.handle, all_handles), "w8a8_tp_connect")
+
+    def tp_allreduce_rmsnorm_quantize(self, x, partial, weight, eps, M, K, group_size, Xq=None, Xs=None,
+                                      smooth_inv=None, act_scale=None, act_mode=ACT_PER_TOKEN_GROUP, normed_out=None,
+                                      stream=None):
+        self._check(self.lib.w8a8_tp_allreduce_rmsnorm_quantize(self.handle, _ptr(x), _ptr(partial), _ptr(weight), eps,
+                                                                _ptr(smooth_inv), _ptr(act_scale), M, K, group_size,
+                                                                act_mode, _ptr(normed_out), _ptr(Xq), _ptr(Xs),
+                                                                _stream(stream)), "w8a8_tp_allreduce_rmsnorm_quantize")
 
     def packed_weight_bytes(self, N, K, group_size) -> int:
         return self.lib.w8a8_packed_weight_bytes(N, K, group_size)

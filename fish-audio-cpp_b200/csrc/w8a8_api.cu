@@ -19,6 +19,7 @@ struct w8a8_ctx {
     // same pointer-keyed lookup as DualAREngine::weight_quant_meta_ (src/engine/dual_ar_engine.h:105)
     std::unordered_map<const void*, const void*> packed;
     std::mutex packed_mu;
+    w8a8::TpState* tp = nullptr;  // tensor-parallel exchange, when w8a8_tp_create was called
 };
 
 static constexpr size_t kSplitkPartialBytes = size_t(16) << 20;
@@ -197,6 +198,7 @@ int w8a8_destroy(w8a8_ctx* ctx) {
     cudaFree(ctx->device_status);
     cudaFree(ctx->splitk_partials);
     cudaFree(ctx->splitk_counters);
+    tp_destroy(ctx->tp);
     delete ctx;
     return W8A8_OK;
 }
@@ -349,6 +351,30 @@ int w8a8_paged_attention_decode(w8a8_ctx* ctx, const void* q, const void* k_cach
                                          n_kv_heads, max_blocks_per_seq, sm_scale, layer, n_layers,
                                          static_cast<__half*>(out), quant_group_size, static_cast<int8_t*>(Xq),
                                          static_cast<float*>(Xs), context_splits, static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_tp_create(w8a8_ctx* ctx, int rank, int world, int max_tokens, int dim, void* ipc_handle_out) {
+    if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
+    if (ctx->tp) return fail(W8A8_ERR_INVALID_ARG, "this context already has a tensor-parallel exchange");
+    return tp_create(&ctx->tp, rank, world, max_tokens, dim, ipc_handle_out);
+}
+
+int w8a8_tp_connect(w8a8_ctx* ctx, const void* all_ipc_handles) {
+    if (!ctx || !ctx->tp) return fail(W8A8_ERR_INVALID_ARG, "w8a8_tp_create first");
+    return tp_connect(ctx->tp, all_ipc_handles);
+}
+
+int w8a8_tp_allreduce_rmsnorm_quantize(w8a8_ctx* ctx, void* x, const void* partial, const void* weight, float eps,
+                                       const void* smooth_inv, const void* act_scale, int M, int K, int group_size,
+                                       int act_mode, void* normed_out, void* Xq, void* Xs, void* stream) {
+    if (!ctx || !ctx->tp) return fail(W8A8_ERR_INVALID_ARG, "w8a8_tp_create first");
+    if (M < 0 || K <= 0 || (M > 0 && (!x || !partial))) return fail(W8A8_ERR_INVALID_ARG, "tp row kernel: bad arguments");
+    if (Xq && !Xs) return fail(W8A8_ERR_INVALID_ARG, "tp row kernel: Xq without Xs");
+    return launch_tp_allreduce_rowquant(ctx->tp, static_cast<__half*>(x), static_cast<const __half*>(partial),
+                                        static_cast<const __half*>(weight), eps, static_cast<const __half*>(smooth_inv),
+                                        static_cast<const __half*>(act_scale), M, K, group_size, act_mode,
+                                        static_cast<__half*>(normed_out), static_cast<int8_t*>(Xq),
+                                        static_cast<float*>(Xs), ctx->device_status, static_cast<cudaStream_t>(stream));
 }
 
 size_t w8a8_packed_weight_bytes(int N, int K, int group_size) { return packed_weight_bytes(N, K, group_size); }

@@ -83,6 +83,14 @@ int launch_paged_attention_decode(const __half* q, const __half* k_cache, const 
                                   const int* block_table, const int* seq_lens, int B, int n_q, int n_kv,
                                   int max_blocks, float sm_scale, int layer, int n_layers, __half* out, int g,
                                   int8_t* Xq, float* Xs, int splits, cudaStream_t stream);
+// w8a8_tp.cu : one-shot all-reduce over peer memory fused with residual add + RMSNorm + quantiser.
+struct TpState;
+int tp_create(TpState** out, int rank, int world, int max_tokens, int dim, void* ipc_handle_out64);
+int tp_connect(TpState* t, const void* all_handles);
+int tp_destroy(TpState* t);
+int launch_tp_allreduce_rowquant(TpState* t, __half* x, const __half* partial, const __half* norm_weight, float eps,
+                                 const __half* smooth_inv, const __half* act_scale, int M, int K, int g, int act_mode,
+                                 __half* normed_out, int8_t* Xq, float* Xs, int* status, cudaStream_t stream);
 // w8a8_gemm_sm100.cu : tcgen05 + TMA.
 bool gemm_supports(const LinearArgs& a);
 int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t s);

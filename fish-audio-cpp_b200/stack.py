@@ -56,11 +56,18 @@ def shard_bounds(total_groups: int, world: int):
 class SlowARStack:
     def __init__(self, torch, ctx: capi.Context, cfg: SlowARConfig, batch: int, context: int, max_new: int = 256,
                  tp_rank: int = 0, tp_size: int = 1, seed: int = 0, all_reduce=None, pack: bool = True,
-                 attn_splits: int = 0):
+                 attn_splits: int = 0, tp_mode: str = "fused", gather_handles=None):
         self.torch, self.ctx, self.cfg = torch, ctx, cfg
         self.B, self.tp_rank, self.tp_size = batch, tp_rank, tp_size
         self.all_reduce = all_reduce
         self.attn_splits = attn_splits
+        # "fused": the exchange happens inside the residual+norm+quant kernel over peer memory;
+        # "nccl": a library all-reduce between the projection and that kernel (the baseline).
+        self.tp_fused = tp_size > 1 and tp_mode == "fused"
+        if self.tp_fused:
+            handle = ctx.tp_create(tp_rank, tp_size, batch, cfg.dim)
+            ctx.tp_connect(b"".join(gather_handles(handle)))
+            self.all_reduce = None
         c = cfg
         assert c.n_kv % tp_size == 0 and c.n_head == 4 * c.n_kv and c.head_dim == 128
         g = c.group
@@ -178,8 +185,12 @@ class SlowARStack:
         sm_scale = 1.0 / math.sqrt(D)
         pending = False  # a projection output waiting to be added to the residual stream
         for l, lw in enumerate(self.layers):
-            ctx.rmsnorm_quantize(self.x, lw["attn_norm"], c.eps, B, c.dim, g, self.xq, self.xs,
-                                 residual=self.delta if pending else None)
+            if pending and self.tp_fused:
+                ctx.tp_allreduce_rmsnorm_quantize(self.x, self.delta, lw["attn_norm"], c.eps, B, c.dim, g,
+                                                  Xq=self.xq, Xs=self.xs)
+            else:
+                ctx.rmsnorm_quantize(self.x, lw["attn_norm"], c.eps, B, c.dim, g, self.xq, self.xs,
+                                     residual=self.delta if pending else None)
             ctx.linear_q(lw["wqkv"], lw["sqkv"], g, self.xq, self.xs, self.qkv, B, self.qkv_n, c.dim)
             ctx.qknorm_rope_kvwrite(self.qkv, lw["q_norm"], lw["k_norm"], c.eps, self.freqs, self.positions,
                                     self.block_table, self.max_blocks, self.k_cache, self.v_cache, l, c.n_layer, B,
@@ -190,7 +201,12 @@ class SlowARStack:
             ctx.linear_q(lw["wo"], lw["so"], g, self.aq, self.as_, self.delta, B, c.dim, self.attn_k)
             if self.all_reduce is not None:
                 self.all_reduce(self.delta)
-            ctx.rmsnorm_quantize(self.x, lw["ffn_norm"], c.eps, B, c.dim, g, self.xq, self.xs, residual=self.delta)
+            if self.tp_fused:
+                ctx.tp_allreduce_rmsnorm_quantize(self.x, self.delta, lw["ffn_norm"], c.eps, B, c.dim, g,
+                                                  Xq=self.xq, Xs=self.xs)
+            else:
+                ctx.rmsnorm_quantize(self.x, lw["ffn_norm"], c.eps, B, c.dim, g, self.xq, self.xs,
+                                     residual=self.delta)
             ctx.linear_q(lw["w13"], lw["s13"], g, self.xq, self.xs, self.act, B, 2 * self.inter_l, c.dim,
                          epilogue=capi.EPI_SWIGLU)
             ctx.quantize(self.act, B, self.inter_l, g, self.actq, self.acts)
@@ -198,8 +214,12 @@ class SlowARStack:
             if self.all_reduce is not None:
                 self.all_reduce(self.delta)
             pending = True
-        ctx.residual_add(self.x, self.delta, B * c.dim)
-        ctx.rms_norm(self.x, self.final_norm, self.out, B, c.dim, c.eps)
+        if self.tp_fused:
+            ctx.tp_allreduce_rmsnorm_quantize(self.x, self.delta, self.final_norm, c.eps, B, c.dim, g,
+                                              normed_out=self.out)
+        else:
+            ctx.residual_add(self.x, self.delta, B * c.dim)
+            ctx.rms_norm(self.x, self.final_norm, self.out, B, c.dim, c.eps)
         self.positions.add_(1)
         self.seq_lens.add_(1)
         return self.out

@@ -191,6 +191,26 @@ W8A8_API int w8a8_paged_attention_decode(w8a8_ctx* ctx, const void* q, const voi
                                 int quant_group_size, void* Xq, void* Xs, int context_splits,
                                 void* stream);
 
+/* ---- tensor parallelism (no counterpart in the reference, which is single-GPU) ------------- */
+
+/* Row-parallel projections (wo, w2 with K cut at quantisation-group boundaries) leave a partial
+ * [M, dim] on every rank. w8a8_tp_allreduce_rmsnorm_quantize is w8a8_rmsnorm_quantize whose residual
+ * is the SUM of all ranks' partials: the kernel pushes its rank's rows into every rank's exchange
+ * buffer over NVLink peer memory, waits (bounded; W8A8_ERR_TIMEOUT through w8a8_check_device_status)
+ * for the others' rows, adds them in rank order in fp32, rounds once to fp16, adds that to x in place,
+ * and continues with RMSNorm (weight == NULL: none) and the quantiser (Xq == NULL: none).
+ * Set-up, once per process: w8a8_tp_create allocates the exchange buffer for at most max_tokens rows of
+ * `dim` and returns a 64-byte CUDA IPC handle; the host gathers all ranks' handles (any transport) and
+ * passes the world*64 bytes, in rank order, to w8a8_tp_connect (NULL = loop-back onto this rank's own
+ * buffer: the other ranks' rows then never arrive — what the time-out test uses). One process per GPU,
+ * world <= 8. */
+W8A8_API int w8a8_tp_create(w8a8_ctx* ctx, int rank, int world, int max_tokens, int dim, void* ipc_handle_out);
+W8A8_API int w8a8_tp_connect(w8a8_ctx* ctx, const void* all_ipc_handles);
+W8A8_API int w8a8_tp_allreduce_rmsnorm_quantize(w8a8_ctx* ctx, void* x, const void* partial, const void* weight,
+                                       float eps, const void* smooth_inv, const void* act_scale, int M,
+                                       int K, int group_size, int act_mode, void* normed_out, void* Xq,
+                                       void* Xs, void* stream);
+
 /* Decode-time weight layout. The reference uploads each weight as it lies in the container
  * (src/engine/dual_ar_engine.cc:231-278) and keys its quantisation metadata by the device pointer
  * (:275). A loader built on this library does one more step per weight: it packs the row-major

@@ -50,3 +50,63 @@ def worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+
+
+def free_port():
+    import socket
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def gpu_exchange_worker(rank, world, port, q):
+    """One rank of tests/test_gpu_tp.py: three consecutive fused exchanges against the oracle."""
+    try:
+        from oracle import oracle
+        pkg = ge.package()
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        torch.cuda.set_device(rank)
+        dist.init_process_group("gloo", rank=rank, world_size=world)  # host-side plumbing only
+        ctx = pkg.Context(rank, 1 << 20)
+        M, K, g = 8, 2560, 256
+        handle = ctx.tp_create(rank, world, M, K)
+        handles = [None] * world
+        dist.all_gather_object(handles, handle)
+        ctx.tp_connect(b"".join(handles))
+        dist.barrier()
+        rng = np.random.default_rng(5)
+        x = rng.standard_normal((M, K)).astype(np.float16)
+        w = rng.uniform(0.5, 1.5, K).astype(np.float16)
+        dx = torch.from_numpy(x).cuda()
+        dw = torch.from_numpy(w).cuda()
+        ok, msg = True, ""
+        for it in range(3):
+            parts = [rng.standard_normal((M, K)).astype(np.float16) for _ in range(world)]
+            dpart = torch.from_numpy(parts[rank]).cuda()
+            dq = torch.empty((M, K), dtype=torch.int8, device="cuda")
+            ds = torch.empty((M, K // g), dtype=torch.float32, device="cuda")
+            dn = torch.empty((M, K), dtype=torch.float16, device="cuda")
+            ctx.tp_allreduce_rmsnorm_quantize(dx, dpart, dw, 1e-6, M, K, g, Xq=dq, Xs=ds, normed_out=dn)
+            torch.cuda.synchronize()
+            ctx.check_device_status()
+            s32 = np.zeros((M, K), np.float32)
+            for p_ in parts:                      # ascending rank order, fp32
+                s32 = (s32 + p_.astype(np.float32)).astype(np.float32)
+            x = oracle.residual_add(x, s32.astype(np.float16))
+            if not np.array_equal(dx.cpu().numpy().view(np.uint16), x.view(np.uint16)):
+                ok, msg = False, f"iteration {it}: residual stream differs"
+                break
+            normed = dn.cpu().numpy()
+            if oracle.ulp_distance_fp16(normed, oracle.rms_norm(x, w, 1e-6)).max() > 1:
+                ok, msg = False, f"iteration {it}: norm off"
+                break
+            wq, ws = oracle.quantize(normed, g)
+            if not (np.array_equal(dq.cpu().numpy(), wq) and np.array_equal(ds.cpu().numpy(), ws)):
+                ok, msg = False, f"iteration {it}: codes differ"
+                break
+        dist.barrier()
+        q.put((rank, ok, msg))
+        ctx.close()
+        dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001
+        q.put((rank, False, repr(e)))

@@ -1,0 +1,60 @@
+"""The fused tensor-parallel exchange (all-reduce inside the residual + RMSNorm + quantiser kernel).
+
+* Two real ranks on two GPUs (skipped when the box has one): every rank must end with the oracle's
+  bits, over several consecutive exchanges (epoch / double-buffer logic).
+* Failure detection on ONE GPU, without faulting it: a two-rank exchange whose peer never shows up
+  (loop-back connection) must give up its bounded wait and report W8A8_ERR_TIMEOUT, and the context
+  must stay usable afterwards.
+"""
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+import _tp_worker  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+
+def test_missing_peer_times_out_cleanly(pkg, oracle):
+    torch.cuda.set_device(0)
+    ctx = pkg.Context(0, 1 << 20)
+    M, K, g = 2, 512, 64
+    ctx.tp_create(0, 2, M, K)
+    ctx.tp_connect(None)  # loop-back: rank 1's rows never arrive
+    x = torch.zeros((M, K), dtype=torch.float16, device="cuda")
+    part = torch.ones((M, K), dtype=torch.float16, device="cuda")
+    w = torch.ones((K,), dtype=torch.float16, device="cuda")
+    xq = torch.empty((M, K), dtype=torch.int8, device="cuda")
+    xs = torch.empty((M, K // g), dtype=torch.float32, device="cuda")
+    ctx.tp_allreduce_rmsnorm_quantize(x, part, w, 1e-6, M, K, g, Xq=xq, Xs=xs)
+    with pytest.raises(pkg.W8A8Error) as e:
+        ctx.check_device_status()
+    assert e.value.status == 4  # W8A8_ERR_TIMEOUT
+    # the device and the context are still fine
+    ctx.check_device_status()
+    y = torch.empty((M, K), dtype=torch.float16, device="cuda")
+    ctx.rms_norm(part, w, y, M, K, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.isfinite(y.float()).all()
+    ctx.close()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_rank_exchange_matches_oracle():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _tp_worker.free_port()
+    procs = [ctx.Process(target=_tp_worker.gpu_exchange_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, ok, msg in res:
+        assert ok, f"rank {rank}: {msg}"
