@@ -237,6 +237,98 @@ class DecodeSweep:
         return out
 
 
+class PrefillSweep:
+    """configs[2]: the four projections x g{256,64} x M{2048,8192}, one W8A8 linear each (row quantiser +
+    tcgen05 GEMM), fp16 in, fp16 out. Activations + weights of a case (up to ~370 MB) exceed L2 together
+    with the rotation over the eight weight sets."""
+
+    def __init__(self, torch, ctx, seed=4321, Ms=(2048, 8192)):
+        from fish_audio_cpp_b200 import synth
+
+        self.torch, self.ctx = torch, ctx
+        gen = torch.Generator(device="cuda").manual_seed(seed)
+        rng = np.random.default_rng(seed)
+        self.cases, self.w = [], {}
+        for g in (256, 64):
+            for name, (K, N) in synth.PROJECTIONS.items():
+                G = K // g
+                self.w[(name, g)] = (
+                    torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda", generator=gen),
+                    torch.empty((N, G), dtype=torch.float32, device="cuda").uniform_(1e-3, 5e-3, generator=gen).half())
+        self.x = {}
+        for M in Ms:
+            for K in sorted({k for k, _ in synth.PROJECTIONS.values()}):
+                x = torch.randn((M, K), dtype=torch.float32, device="cuda", generator=gen)
+                idx = torch.randperm(K, device="cuda", generator=gen)[:max(1, round(0.005 * K))]
+                x[:, idx] *= 20.0
+                self.x[(M, K)] = x.half()
+        for M in Ms:
+            for g in (256, 64):
+                for name, (K, N) in synth.PROJECTIONS.items():
+                    if ONLY is None or ONLY == (name, M, g):
+                        self.cases.append({"name": name, "M": M, "N": N, "K": K, "g": g})
+        self.y = torch.empty((max(Ms), 19456), dtype=torch.float16, device="cuda")
+        self.ops_per_step = sum(2 * c["M"] * c["N"] * c["K"] for c in self.cases)
+        self.bytes_per_step = sum(algorithmic_bytes(c["M"], c["N"], c["K"], c["g"]) for c in self.cases)
+        self.launches_per_step = 2 * len(self.cases)
+        self.eager, self.split_k, self.graphs = False, 0, {}
+        self.host_x = {k: v.cpu().pin_memory() for k, v in self.x.items() if k[0] == min(Ms)}
+        self.host_y = torch.empty((min(Ms), 19456), dtype=torch.float16).pin_memory()
+        self.h2d = self.d2h = 0
+
+    def run_case(self, c):
+        W, S = self.w[(c["name"], c["g"])]
+        self.ctx.linear(W, S, c["g"], self.x[(c["M"], c["K"])], self.y, c["M"], c["N"], c["K"])
+
+    def step(self, e2e=False):
+        for c in self.cases:
+            self.run_case(c)
+
+    def per_case(self, min_ms=20.0):
+        t, out = self.torch, []
+        for c in self.cases:
+            for _ in range(2):
+                self.run_case(c)
+            t.cuda.synchronize()
+            reps = 1
+            while True:
+                e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(reps):
+                    self.run_case(c)
+                e1.record()
+                t.cuda.synchronize()
+                ms = e0.elapsed_time(e1)
+                if ms >= min_ms or reps >= 256:
+                    break
+                reps *= 2
+            us = ms * 1e3 / reps
+            out.append({"name": c["name"], "M": c["M"], "g": c["g"], "us": round(us, 1),
+                        "tops": round(2 * c["M"] * c["N"] * c["K"] / us / 1e6, 1)})
+        return out
+
+    def library_int8_tops(self):
+        """cuBLASLt int8 -> int32 at 8192^3 through torch._int_mm: a library figure for context only."""
+        t = self.torch
+        try:
+            a = t.randint(-127, 128, (8192, 8192), dtype=t.int8, device="cuda")
+            bm = t.randint(-127, 128, (8192, 8192), dtype=t.int8, device="cuda")
+            for _ in range(3):
+                t._int_mm(a, bm)
+            t.cuda.synchronize()
+            best = 1e9
+            for _ in range(10):
+                e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+                e0.record()
+                t._int_mm(a, bm)
+                e1.record()
+                t.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+            return round(2 * 8192 ** 3 / (best * 1e-3) / 1e12, 1)
+        except Exception:  # noqa: BLE001
+            return None
+
+
 class DecodeStack:
     """configs[3]: the full slow-AR decoder stack, batch 8, context 1024, g256, tensor-parallel over the
     ranks of the job. One step = one token for each of the 8 sequences, replayed from a CUDA graph."""
@@ -463,7 +555,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["decode_stack", "decode_sweep"], default="decode_stack")
+    ap.add_argument("--workload", choices=["decode_stack", "decode_sweep", "prefill"], default="decode_stack")
     ap.add_argument("--tp-mode", choices=["fused", "nccl"], default="fused",
                     help="N > 1: all-reduce inside the norm kernel over peer memory (fused) or NCCL (baseline)")
     ap.add_argument("--layers", type=int, default=36, help="decode_stack: number of layers (36 = the named config)")
@@ -527,6 +619,8 @@ def main():
         ctx = pkg.Context(local_rank, 0)
         if args.workload == "decode_stack":
             wl = DecodeStack(torch, ctx, world, rank, dist, layers=args.layers, tp_mode=args.tp_mode)
+        elif args.workload == "prefill":
+            wl = PrefillSweep(torch, ctx)
         else:
             wl = DecodeSweep(torch, ctx, pack=not args.no_pack)
 
@@ -552,7 +646,7 @@ def main():
     dev_ms = ev0.elapsed_time(ev1)
     # end to end: host buffers in, host buffers out, copies inside the timed region
     e2e_ms = None
-    if not reference:
+    if not reference and args.workload != "prefill":
         for _ in range(2):
             wl.step(e2e=True)
         barrier()
@@ -574,6 +668,36 @@ def main():
         return
 
     pk = peaks()
+    if args.workload == "prefill":
+        ms_per_step = dev_ms / args.steps
+        tops = wl.ops_per_step * world / (ms_per_step * 1e-3) / 1e12
+        bf16 = None
+        if MEASURED_PEAKS.exists():
+            bf16 = float(json.loads(MEASURED_PEAKS.read_text()).get("bf16_tflops", 0)) or None
+        peak = 2 * bf16 if bf16 else 2 * 1590.0
+        line = {
+            "metric": "w8a8_prefill_gemm_int8_tops", "value": round(tops, 1), "unit": "TOPS", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "configs[2]: slow-AR projections qkv/o/gate_up/down x g{256,64} x M{2048,8192}, one "
+                                   "W8A8 linear (row quantiser + tcgen05 GEMM) each per step", "cases_per_step": len(wl.cases),
+                       "l2": "inputs larger than L2: 8 weight sets + 8 activation sets in rotation (> 600 MB)",
+                       "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+                       "library_int8_tops_8192cubed": wl.library_int8_tops()},
+            "roofline": {"bound": "tensor", "achieved": round(tops / world, 1), "peak": round(peak, 1), "unit": "TOP/s",
+                         "frac": round(tops / world / peak, 4), "traffic": None,
+                         "peak_source": "2 x measured bf16 burst (int8 dense runs at twice the bf16 rate; no "
+                                        "int8 figure is in MEASURED_PEAKS.json)" if bf16 else "2 x fallback bf16",
+                         "kernel": "gemm_i8_kernel"},
+            "clocks": clocks, "gpu_launches": wl.launches_per_step * args.steps,
+            "cases": [dict(c, frac=round(c["tops"] / peak, 3)) for c in cases],
+            "e2e": {"value": None, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
+                    "note": "prefill activations are produced on the device by the embedding / previous layer; "
+                            "the end-to-end figure of this repository is the decode_stack workload's"},
+        }
+        print(json.dumps(line), flush=True)
+        finish(dist, wl)
+        return
     if args.workload == "decode_stack":
         ms_per_step = dev_ms / args.steps
         n_gpus = 1 if solo_reference else world

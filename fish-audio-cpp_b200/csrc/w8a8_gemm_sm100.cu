@@ -5,20 +5,24 @@
 // accumulate pass over the whole [tokens, rows] matrix per group and a cast pass
 // (int8_gemm.cu:423-505): here a K-group's exact int32 sums never leave the SM.
 //
-// One CTA computes a 128-token x 128-row output tile with three kinds of warps:
+// One CTA computes a 128-token x 256-row output tile (the larger the tile, the fewer operand bytes per
+// MAC have to come out of L2, which is what bounds this kernel) with three kinds of warps:
 //   warp 0      producer: one lane issues TMA loads of 128 x 128-byte boxes of the activation codes
 //               and of the weights (both are row-major with K contiguous, i.e. already the K-major
 //               operand; the 128-byte swizzle is applied by TMA) into a ring of kStages stages;
-//   warp 1      MMA issuer: one lane issues tcgen05.mma (M=128, N=128, K=32 per instruction), four per
-//               128-byte stage. Each K-group accumulates into its own 128-column slice of tensor
-//               memory (4 slices = all 512 columns), starting with "overwrite"; a tcgen05.commit
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (M=128, N=256, K=32 per instruction), four per
+//               128-byte stage. Each K-group accumulates into its own 256-column slice of tensor
+//               memory (2 slices = all 512 columns), starting with "overwrite"; a tcgen05.commit
 //               hands the slice to the epilogue and another frees the shared-memory stage;
-//   warps 2..5  epilogue: thread <-> token row (tensor-memory lane). For every K-group they read the
-//               int32 sums with tcgen05.ld, and promote  acc = fma(float(P) * ws[n,j], xs[m,j], acc)
-//               in ascending group order into 128 fp32 registers per thread — the arithmetic and
-//               order of accumulate_group_kernel (int8_gemm.cu:213-234) — while the MMA warp already
-//               fills the next slice. Weight scales of the group are staged in shared memory once
-//               per CTA; the final fp16 store applies the optional residual / SwiGLU epilogue.
+//   warps 4..11 epilogue (two warpgroups; setmaxnreg moves registers from warpgroup 0 to them): thread <-> (token row = tensor-memory lane, 128 of the 256 columns). For every
+//               K-group they read the int32 sums with tcgen05.ld and promote
+//               acc = fma(float(P) * ws[n,j], xs[m,j], acc) in ascending group order into 128 fp32
+//               registers per thread — the arithmetic and order of accumulate_group_kernel
+//               (int8_gemm.cu:213-234) — while the MMA warp already fills the next slice. The promote is
+//               the CUDA-core bottleneck of this kernel, so it uses packed fp32x2 add/mul/fma and, for
+//               groups of at most 256 (|P| < 2^22), an exact integer-add + float-subtract conversion
+//               instead of the quarter-rate I2F. Weight scales of the group are staged in shared memory
+//               once per CTA; the final fp16 store applies the optional residual / SwiGLU epilogue.
 // Every mbarrier wait is bounded; a wait that runs out records an error word, and the CTA still
 // frees its tensor memory before it returns.
 #include "sm100_ptx.cuh"
@@ -27,11 +31,12 @@
 namespace w8a8 {
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 128;  // BK in bytes = int8 elements
-constexpr int kStages = 5;
-constexpr int kAccStages = 4;  // 4 x 128 columns = the whole tensor memory
+constexpr int BM = 128, BN = 256, BK = 128;  // BK in bytes = int8 elements
+constexpr int kStages = 4;
+constexpr int kAccStages = 2;  // 2 x 256 columns = the whole tensor memory
 constexpr int kStageBytes = (BM + BN) * BK;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;                // two per tensor-memory lane quadrant, 128 columns each
+constexpr int kThreads = 128 + kEpiWarps * 32;  // warpgroup 0: producer, MMA issuer, two idle warps; 1-2: epilogue
 constexpr uint32_t kSpin = 1u << 21;
 
 struct GemmParams {
@@ -85,6 +90,33 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// ---- packed fp32x2 arithmetic (two IEEE round-to-nearest results per instruction) ----
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    return static_cast<uint64_t>(__float_as_uint(a)) | (static_cast<uint64_t>(__float_as_uint(b)) << 32);
+}
+__device__ __forceinline__ float lo2(uint64_t v) { return __uint_as_float(static_cast<uint32_t>(v)); }
+__device__ __forceinline__ float hi2(uint64_t v) { return __uint_as_float(static_cast<uint32_t>(v >> 32)); }
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+// Exact int32 -> fp32 for |v| < 2^22: the integer lands in the mantissa of 1.5 * 2^23, which is then removed.
+__device__ __forceinline__ uint64_t ints_to_floats_magic(uint32_t a, uint32_t b) {
+    const uint64_t biased = static_cast<uint64_t>(a + 0x4B400000u) | (static_cast<uint64_t>(b + 0x4B400000u) << 32);
+    return add2(biased, pack2(-12582912.0f, -12582912.0f));
+}
+
 // Shared-memory operand descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart.
 __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
     return static_cast<uint64_t>((saddr & 0x3ffffu) >> 4) | (1ull << 16) /* leading offset (unused) */ |
@@ -103,7 +135,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __shared__ __align__(8) uint64_t acc_full[kAccStages], acc_empty[kAccStages];
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
-    __shared__ __align__(16) float ws_s[2][BN];
+    __shared__ __align__(16) float ws_s[2][BN];  // one weight scale per tile column, double-buffered over groups
 
     const LinearArgs& a = p.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -113,7 +145,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStages; ++s) { ptx::mbar_init(&full_bar[s], 1); ptx::mbar_init(&empty_bar[s], 1); }
-        for (int s = 0; s < kAccStages; ++s) { ptx::mbar_init(&acc_full[s], 1); ptx::mbar_init(&acc_empty[s], 4); }
+        for (int s = 0; s < kAccStages; ++s) { ptx::mbar_init(&acc_full[s], 1); ptx::mbar_init(&acc_empty[s], kEpiWarps); }
         failed_s = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async();
@@ -129,7 +161,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     // The activation codes come from the kernel before this one (the row quantiser).
     ptx::pdl_wait();
 
-    if (warp == 0) {
+    if (warp < 4) {
+      // warpgroup 0 gives registers away; the two epilogue warpgroups take them
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
+      if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
             for (int kb = 0; kb < p.num_kblocks; ++kb) {
@@ -150,7 +185,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
+      } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
             const int total_mmas = p.num_kblocks * 4;
@@ -181,100 +216,114 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             }
         }
         __syncwarp();
+      }
     } else {
-        // ---------------- epilogue: 4 warps, thread <-> token row ----------------
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
+        // ---------------- epilogue: 8 warps, thread <-> (token row, 128 columns) ----------------
+        constexpr int HC = BN / 2;               // columns per thread
         const int quad = warp & 3;               // the tensor-memory lane quadrant this warp may read
+        const int half = (warp - 4) >> 2;        // which 128 columns
         const int row = quad * 32 + lane;        // row inside the tile
         const int m = m0 + row;
-        const int et = (warp - 2) * 32 + lane;   // 0..127: which weight row's scale this thread stages
+        const int et = (warp - 4) * 32 + lane;   // 0..255: stages the weight scale of tile column et
         const bool m_ok = m < a.M;
         const float* xs_row = a.Xs + static_cast<size_t>(m_ok ? m : 0) * G;
-        const int ncol = min(n0 + et, a.N - 1);
-        float acc[BN];
+        const int ncol = min(n0 + (et & (BN - 1)), a.N - 1);
+        const bool magic = a.g <= 256;           // |P| <= 127 * 127 * 256 < 2^22
+        uint64_t acc2[HC / 2];
 #pragma unroll
-        for (int c = 0; c < BN; ++c) acc[c] = 0.0f;
-        ws_s[0][et] = __half2float(a.w_scale[static_cast<size_t>(ncol) * G]);
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        for (int c = 0; c < HC / 2; ++c) acc2[c] = 0ull;
+        if (et < BN) ws_s[0][et] = __half2float(a.w_scale[static_cast<size_t>(ncol) * G]);
+        asm volatile("bar.sync 1, 256;" ::: "memory");
         bool ok = true;
         for (int j = 0; j < G && ok; ++j) {
             const int as = j % kAccStages, cur = j & 1;
             const float xs = xs_row[j];
+            const uint64_t xs2 = pack2(xs, xs);
             float ws_next = 0.0f;
-            if (j + 1 < G) ws_next = __half2float(a.w_scale[static_cast<size_t>(ncol) * G + j + 1]);
+            if (et < BN && j + 1 < G) ws_next = __half2float(a.w_scale[static_cast<size_t>(ncol) * G + j + 1]);
             if (!ptx::mbar_wait_bounded(&acc_full[as], (j / kAccStages) & 1, kSpin)) {
                 atomicExch(p.status, 500 + as); atomicExch(&failed_s, 1); ok = false; break;
             }
             tc_fence_after();
-            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * BN;
+            const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * BN + half * HC;
 #pragma unroll
-            for (int c0 = 0; c0 < BN; c0 += 32) {
+            for (int c0 = 0; c0 < HC; c0 += 32) {
                 uint32_t r[32];
                 tmem_ld32(taddr + c0, r);
                 tmem_ld_wait();
 #pragma unroll
                 for (int c = 0; c < 32; c += 4) {
-                    const float4 w4 = *reinterpret_cast<const float4*>(&ws_s[cur][c0 + c]);
-                    acc[c0 + c + 0] = __fmaf_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[c + 0])), w4.x), xs, acc[c0 + c + 0]);
-                    acc[c0 + c + 1] = __fmaf_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[c + 1])), w4.y), xs, acc[c0 + c + 1]);
-                    acc[c0 + c + 2] = __fmaf_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[c + 2])), w4.z), xs, acc[c0 + c + 2]);
-                    acc[c0 + c + 3] = __fmaf_rn(__fmul_rn(static_cast<float>(static_cast<int>(r[c + 3])), w4.w), xs, acc[c0 + c + 3]);
+                    const float4 w4 = *reinterpret_cast<const float4*>(&ws_s[cur][half * HC + c0 + c]);
+                    uint64_t f01, f23;
+                    if (magic) {
+                        f01 = ints_to_floats_magic(r[c + 0], r[c + 1]);
+                        f23 = ints_to_floats_magic(r[c + 2], r[c + 3]);
+                    } else {
+                        f01 = pack2(static_cast<float>(static_cast<int>(r[c + 0])), static_cast<float>(static_cast<int>(r[c + 1])));
+                        f23 = pack2(static_cast<float>(static_cast<int>(r[c + 2])), static_cast<float>(static_cast<int>(r[c + 3])));
+                    }
+                    acc2[(c0 + c) / 2] = fma2(mul2(f01, pack2(w4.x, w4.y)), xs2, acc2[(c0 + c) / 2]);
+                    acc2[(c0 + c) / 2 + 1] = fma2(mul2(f23, pack2(w4.z, w4.w)), xs2, acc2[(c0 + c) / 2 + 1]);
                 }
                 if (a.dump && m_ok) {
 #pragma unroll
                     for (int c = 0; c < 32; ++c)
-                        if (n0 + c0 + c < a.N)
-                            a.dump[(static_cast<size_t>(m) * a.N + n0 + c0 + c) * G + j] = static_cast<int>(r[c]);
+                        if (n0 + half * HC + c0 + c < a.N)
+                            a.dump[(static_cast<size_t>(m) * a.N + n0 + half * HC + c0 + c) * G + j] = static_cast<int>(r[c]);
                 }
             }
             // this slice of tensor memory may be overwritten by group j + kAccStages
             tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
-            ws_s[cur ^ 1][et] = ws_next;
-            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (et < BN) ws_s[cur ^ 1][et] = ws_next;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
         }
         // ---- final store: fp16, optional residual add or SwiGLU, 16 bytes at a time ----
         if (ok && m_ok) {
+            const int nb = n0 + half * HC;  // first column of this thread
+            auto accf = [&](int c) -> float { return (c & 1) ? hi2(acc2[c >> 1]) : lo2(acc2[c >> 1]); };
             if (a.epilogue == W8A8_EPI_SWIGLU) {
-                __half* yrow = a.Y + static_cast<size_t>(m) * (a.N / 2) + n0 / 2;
+                __half* yrow = a.Y + static_cast<size_t>(m) * (a.N / 2) + nb / 2;
 #pragma unroll
-                for (int b = 0; b < BN / 16; ++b) {
-                    if (n0 + b * 16 + 16 > a.N) break;
+                for (int b = 0; b < HC / 16; ++b) {
+                    if (nb + b * 16 + 16 > a.N) break;
                     __align__(16) __half o[8];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        const float g16 = __half2float(__float2half(acc[b * 16 + i]));
+                        const float g16 = __half2float(__float2half(accf(b * 16 + i)));
                         const __half s16 = __float2half(g16 / (1.0f + expf(-g16)));
-                        const float u16 = __half2float(__float2half(acc[b * 16 + 8 + i]));
+                        const float u16 = __half2float(__float2half(accf(b * 16 + 8 + i)));
                         o[i] = __float2half(__half2float(s16) * u16);
                     }
                     *reinterpret_cast<uint4*>(yrow + b * 8) = *reinterpret_cast<const uint4*>(o);
                 }
             } else {
-                __half* yrow = a.Y + static_cast<size_t>(m) * a.N + n0;
-                const __half* rrow = a.residual ? a.residual + static_cast<size_t>(m) * a.N + n0 : nullptr;
+                __half* yrow = a.Y + static_cast<size_t>(m) * a.N + nb;
+                const __half* rrow = a.residual ? a.residual + static_cast<size_t>(m) * a.N + nb : nullptr;
                 const bool vec = (a.N % 8) == 0;
 #pragma unroll
-                for (int b = 0; b < BN / 8; ++b) {
-                    if (n0 + b * 8 >= a.N) break;
+                for (int b = 0; b < HC / 8; ++b) {
+                    if (nb + b * 8 >= a.N) break;
                     __align__(16) __half o[8];
                     __align__(16) __half rr[8];
-                    const bool full = vec && n0 + b * 8 + 8 <= a.N;
+                    const bool full = vec && nb + b * 8 + 8 <= a.N;
                     if (a.epilogue == W8A8_EPI_RESIDUAL) {
                         if (full) *reinterpret_cast<uint4*>(rr) = *reinterpret_cast<const uint4*>(rrow + b * 8);
                         else
-                            for (int i = 0; i < 8; ++i) rr[i] = n0 + b * 8 + i < a.N ? rrow[b * 8 + i] : __float2half(0.f);
+                            for (int i = 0; i < 8; ++i) rr[i] = nb + b * 8 + i < a.N ? rrow[b * 8 + i] : __float2half(0.f);
                     }
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
-                        __half y = __float2half(acc[b * 8 + i]);
+                        __half y = __float2half(accf(b * 8 + i));
                         if (a.epilogue == W8A8_EPI_RESIDUAL) y = __float2half(__half2float(y) + __half2float(rr[i]));
                         o[i] = y;
                     }
                     if (full) *reinterpret_cast<uint4*>(yrow + b * 8) = *reinterpret_cast<const uint4*>(o);
                     else
                         for (int i = 0; i < 8; ++i)
-                            if (n0 + b * 8 + i < a.N) yrow[b * 8 + i] = o[i];
+                            if (nb + b * 8 + i < a.N) yrow[b * 8 + i] = o[i];
                 }
             }
         }

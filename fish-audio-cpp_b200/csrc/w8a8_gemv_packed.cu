@@ -22,6 +22,8 @@
 //
 // Launched with programmatic dependent launch: the first kStages blocks are requested before
 // griddepcontrol.wait. Every mbarrier wait is bounded; on expiry the warp records an error word.
+#include <cstdlib>
+
 #include "sm100_ptx.cuh"
 #include "w8a8_internal.h"
 
@@ -390,6 +392,15 @@ int num_sms() {
     return n;
 }
 
+int ctas_per_sm() {
+    static int n = [] {
+        const char* v = std::getenv("W8A8_GEMV_CTAS_PER_SM");
+        int k = v ? std::atoi(v) : 2;
+        return k < 1 ? 1 : (k > 2 ? 2 : k);
+    }();
+    return n;
+}
+
 bool packable(int N, int K, int g) {
     return N > 0 && K > 0 && K % 256 == 0 && K % g == 0 && (g == 64 || g == 128 || g % 256 == 0);
 }
@@ -407,7 +418,9 @@ bool make_plan(const LinearArgs& a, Plan& pl) {
     pl.block_bytes = kBlockW + 32 * (a.g >= 256 ? 1 : 256 / a.g);
     pl.tiles = (a.N + 15) / 16;
     pl.U = static_cast<long long>(pl.tiles) * pl.upt;
-    pl.ctas = num_sms();
+    // Two CTAs per SM, both working: the consumer side of each warp's pipeline is a chain of latencies
+    // (barrier, shared loads, MMAs, promote), so twice the warps per SM hides twice as much of it.
+    pl.ctas = ctas_per_sm() * num_sms();
     if ((pl.U + 1) * static_cast<long long>(pl.ctas) * kWarps >= (1ll << 32)) return false;  // 32-bit range math
     pl.partial_bytes = static_cast<size_t>(pl.ctas) * kWarps * 2 * pl.MT * 4 * 32 * sizeof(float);
     if (pl.partial_bytes > a.splitk_partial_bytes) return false;

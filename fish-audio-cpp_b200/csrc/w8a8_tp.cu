@@ -77,18 +77,20 @@ __global__ void __launch_bounds__(1024) tp_allreduce_rowquant_kernel(const TpRow
     const int ep = s_epoch, par = ep & 1;
     const size_t row_off = ((static_cast<size_t>(par) * p.world + p.rank) * p.max_tokens + m) * K * sizeof(__half);
 
-    // 1. push this rank's row to every rank (16 bytes per thread and peer), then raise the flags
+    // 1. push this rank's row to every rank (16 bytes per thread and peer), then raise the flags.
+    //    One system-scope fence by the flag-raising threads is enough: the block barrier orders the
+    //    other threads' peer stores before it, and the fence is cumulative.
     for (int v = tid; v < K / 8; v += T) {
         const uint4 u = *reinterpret_cast<const uint4*>(p.partial + base + v * 8);
         for (int r = 0; r < p.world; ++r) *reinterpret_cast<uint4*>(p.peers[r] + row_off + v * 16) = u;
     }
-    __threadfence_system();
     __syncthreads();
     if (tid < p.world) {
+        __threadfence_system();
         int* flag = reinterpret_cast<int*>(p.peers[tid] + p.flags_off) + (par * p.world + p.rank) * p.max_tokens + m;
         asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flag), "r"(ep) : "memory");
     }
-    // 2. wait for every rank's row m to have arrived here (bounded: ~a second at most)
+    // 2. wait for every rank's row m to have arrived here (bounded: about a second at most)
     if (tid < p.world) {
         const int* flag = reinterpret_cast<const int*>(mine + p.flags_off) + (par * p.world + tid) * p.max_tokens + m;
         int seen = 0;
@@ -96,30 +98,42 @@ __global__ void __launch_bounds__(1024) tp_allreduce_rowquant_kernel(const TpRow
         do {
             asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
             if (seen == ep) break;
-            if (++spins > 64) __nanosleep(100);
+            if (++spins > 256) __nanosleep(64);
         } while (spins < (1u << 23));
         if (seen != ep) { atomicExch(p.status, 700 + tid); s_fail = 1; }
     }
     __syncthreads();
 
-    // 3. sum the world partial rows in rank order; x += half(sum)   (ffn_activations.cu:41-45 for the add)
+    // 3. sum the world partial rows in rank order in fp32, round once, x += half(sum)
+    //    (ffn_activations.cu:41-45 for the add). The rows were written by other GPUs straight into this
+    //    GPU's L2: read them past L1 (ld.cg), 16 bytes at a time.
+    for (int v = tid; v < K / 8; v += T) {
+        float sum[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sum[i] = 0.0f;
+        for (int r = 0; r < p.world; ++r) {
+            const unsigned char* slot = mine + ((static_cast<size_t>(par) * p.world + r) * p.max_tokens + m) * K * sizeof(__half);
+            const uint4 u = __ldcg(reinterpret_cast<const uint4*>(slot) + v);
+            const __half* hh = reinterpret_cast<const __half*>(&u);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) sum[i] += __half2float(hh[i]);
+        }
+        uint4 xu = *reinterpret_cast<const uint4*>(p.x + base + v * 8);
+        __half* xh = reinterpret_cast<__half*>(&xu);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) xh[i] = __float2half(__half2float(xh[i]) + __half2float(__float2half(sum[i])));
+        *reinterpret_cast<uint4*>(p.x + base + v * 8) = xu;
+    }
+    __syncthreads();
+    // each thread now picks up the elements it owns in the reference's norm order: t, t+T, t+2T, ...
     __half h[kElems];
     float local_sum = 0.0f;
 #pragma unroll
     for (int i = 0; i < kElems; ++i) {
         const int e = tid + i * T;
         if (e < K) {
-            float sum = 0.0f;
-            for (int r = 0; r < p.world; ++r) {
-                const __half* slot = reinterpret_cast<const __half*>(
-                    mine + ((static_cast<size_t>(par) * p.world + r) * p.max_tokens + m) * K * sizeof(__half));
-                sum += __half2float(__ushort_as_half(__ldcv(reinterpret_cast<const unsigned short*>(slot) + e)));
-            }
-            const __half delta = __float2half(sum);
-            const __half v = __float2half(__half2float(p.x[base + e]) + __half2float(delta));
-            p.x[base + e] = v;
-            h[i] = v;
-            float val = __half2float(v);
+            h[i] = p.x[base + e];
+            float val = __half2float(h[i]);
             local_sum += val * val;
         }
     }
