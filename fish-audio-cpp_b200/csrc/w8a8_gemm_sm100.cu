@@ -5,7 +5,9 @@
 // accumulate pass over the whole [tokens, rows] matrix per group and a cast pass
 // (int8_gemm.cu:423-505): here a K-group's exact int32 sums never leave the SM.
 //
-// One CTA computes a 128-token x 256-row output tile (the larger the tile, the fewer operand bytes per
+// One persistent CTA per SM walks over 128-token x 256-row output tiles; the shared-memory stage ring and the
+// tensor-memory accumulator ring keep running across tiles, so the promote of a tile's last K-groups overlaps
+// the MMAs of the next tile. A tile is 128 x 256 (the larger the tile, the fewer operand bytes per
 // MAC have to come out of L2, which is what bounds this kernel) with three kinds of warps:
 //   warp 0      producer: one lane issues TMA loads of 128 x 128-byte boxes of the activation codes
 //               and of the weights (both are row-major with K contiguous, i.e. already the K-major
@@ -38,12 +40,14 @@ constexpr int kStageBytes = (BM + BN) * BK;
 constexpr int kEpiWarps = 8;                // two per tensor-memory lane quadrant, 128 columns each
 constexpr int kThreads = 128 + kEpiWarps * 32;  // warpgroup 0: producer, MMA issuer, two idle warps; 1-2: epilogue
 constexpr uint32_t kSpin = 1u << 21;
+constexpr int kWsGroups = 4;
 
 struct GemmParams {
     LinearArgs a;
     int* status;
     int mmas_per_group;  // g / 32
     int num_kblocks;     // K / 128
+    int tiles_m, tiles_total;
 };
 
 // ---- tcgen05 wrappers ----
@@ -135,11 +139,10 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     __shared__ __align__(8) uint64_t acc_full[kAccStages], acc_empty[kAccStages];
     __shared__ uint32_t tmem_base_s;
     __shared__ int failed_s;
-    __shared__ __align__(16) float ws_s[2][BN];  // one weight scale per tile column, double-buffered over groups
+    __shared__ __align__(16) float ws_s[2][kWsGroups][BN];  // weight scales of kWsGroups K-groups, double-buffered
 
     const LinearArgs& a = p.a;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const uint32_t tiles = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
     const int G = a.G;
 
@@ -167,28 +170,36 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       if (warp == 0) {
         // ---------------- producer ----------------
         if (lane == 0) {
-            for (int kb = 0; kb < p.num_kblocks; ++kb) {
+          int kb = 0;  // running K-block counter over all the tiles of this CTA: the stage ring never restarts
+          bool ok = true;
+          for (int tile = blockIdx.x; tile < p.tiles_total && ok; tile += gridDim.x) {
+            const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+            for (int kbt = 0; kbt < p.num_kblocks; ++kbt, ++kb) {
                 const int s = kb % kStages;
                 if (kb >= kStages && !ptx::mbar_wait_bounded(&empty_bar[s], ((kb / kStages) - 1) & 1, kSpin)) {
                     atomicExch(p.status, 200 + s);
                     atomicExch(&failed_s, 1);
+                    ok = false;
                     break;
                 }
                 ptx::mbar_arrive_expect_tx(&full_bar[s], kStageBytes);
                 const uint32_t dst = tiles + s * kStageBytes;
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                    ::"r"(dst), "l"(&map_x), "r"(ptx::smem_u32(&full_bar[s])), "r"(kb * BK), "r"(m0) : "memory");
+                    ::"r"(dst), "l"(&map_x), "r"(ptx::smem_u32(&full_bar[s])), "r"(kbt * BK), "r"(m0) : "memory");
                 asm volatile(
                     "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                    ::"r"(dst + BM * BK), "l"(&map_w), "r"(ptx::smem_u32(&full_bar[s])), "r"(kb * BK), "r"(n0) : "memory");
+                    ::"r"(dst + BM * BK), "l"(&map_w), "r"(ptx::smem_u32(&full_bar[s])), "r"(kbt * BK), "r"(n0) : "memory");
             }
+          }
         }
         __syncwarp();
       } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (lane == 0) {
-            const int total_mmas = p.num_kblocks * 4;
+            int my_tiles = 0;
+            for (int tile = blockIdx.x; tile < p.tiles_total; tile += gridDim.x) ++my_tiles;
+            const int total_mmas = my_tiles * p.num_kblocks * 4;  // K-block and group counters run across tiles
             int q_in_group = 0, group = 0;
             bool ok = true;
             for (int q = 0; q < total_mmas && ok; ++q) {
@@ -220,65 +231,79 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     } else {
         asm volatile("setmaxnreg.inc.sync.aligned.u32 232;" ::: "memory");
         // ---------------- epilogue: 8 warps, thread <-> (token row, 128 columns) ----------------
-        constexpr int HC = BN / 2;               // columns per thread
+        constexpr int HC = BN / (kEpiWarps / 4);  // columns per thread
         const int quad = warp & 3;               // the tensor-memory lane quadrant this warp may read
-        const int half = (warp - 4) >> 2;        // which 128 columns
+        const int half = (warp - 4) >> 2;        // which HC columns
         const int row = quad * 32 + lane;        // row inside the tile
-        const int m = m0 + row;
         const int et = (warp - 4) * 32 + lane;   // 0..255: stages the weight scale of tile column et
+        const bool magic = a.g <= 256;           // |P| <= 127 * 127 * 256 < 2^22
+        int jrun = 0;                            // running group counter over all the tiles of this CTA
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < p.tiles_total && ok; tile += gridDim.x) {
+        const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
+        const int m = m0 + row;
         const bool m_ok = m < a.M;
         const float* xs_row = a.Xs + static_cast<size_t>(m_ok ? m : 0) * G;
         const int ncol = min(n0 + (et & (BN - 1)), a.N - 1);
-        const bool magic = a.g <= 256;           // |P| <= 127 * 127 * 256 < 2^22
         uint64_t acc2[HC / 2];
 #pragma unroll
         for (int c = 0; c < HC / 2; ++c) acc2[c] = 0ull;
-        if (et < BN) ws_s[0][et] = __half2float(a.w_scale[static_cast<size_t>(ncol) * G]);
+        // Weight scales are staged kWsGroups K-groups at a time (one block barrier per kWsGroups groups,
+        // not per group); the activation scale of the next group is requested while this one is promoted.
+        auto stage_ws = [&](int j0, int buf) {
+#pragma unroll
+            for (int q = 0; q < kWsGroups; ++q)
+                if (et < BN && j0 + q < G) ws_s[buf][q][et] = __half2float(a.w_scale[static_cast<size_t>(ncol) * G + j0 + q]);
+        };
+        stage_ws(0, 0);
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        bool ok = true;
-        for (int j = 0; j < G && ok; ++j) {
-            const int as = j % kAccStages, cur = j & 1;
-            const float xs = xs_row[j];
+        float xs_next = xs_row[0];
+        for (int j = 0; j < G && ok; ++j, ++jrun) {
+            const int as = jrun % kAccStages, buf = (j / kWsGroups) & 1, q = j % kWsGroups;
+            const float xs = xs_next;
+            if (j + 1 < G) xs_next = xs_row[j + 1];
             const uint64_t xs2 = pack2(xs, xs);
-            float ws_next = 0.0f;
-            if (et < BN && j + 1 < G) ws_next = __half2float(a.w_scale[static_cast<size_t>(ncol) * G + j + 1]);
-            if (!ptx::mbar_wait_bounded(&acc_full[as], (j / kAccStages) & 1, kSpin)) {
+            if (q == 0 && j + kWsGroups < G) stage_ws(j + kWsGroups, buf ^ 1);  // lands long before it is read
+            if (!ptx::mbar_wait_bounded(&acc_full[as], (jrun / kAccStages) & 1, kSpin)) {
                 atomicExch(p.status, 500 + as); atomicExch(&failed_s, 1); ok = false; break;
             }
             tc_fence_after();
             const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * BN + half * HC;
+            constexpr int CH = 32;  // columns per tensor-memory load
+            uint32_t r[2][CH];
+            tmem_ld32(taddr, r[0]);
 #pragma unroll
-            for (int c0 = 0; c0 < HC; c0 += 32) {
-                uint32_t r[32];
-                tmem_ld32(taddr + c0, r);
+            for (int ci = 0; ci < HC / CH; ++ci) {
+                const int c0 = ci * CH;
                 tmem_ld_wait();
+                if (ci + 1 < HC / CH) tmem_ld32(taddr + c0 + CH, r[(ci + 1) & 1]);  // next chunk while this one is promoted
+                const uint32_t (&rr)[CH] = r[ci & 1];
 #pragma unroll
-                for (int c = 0; c < 32; c += 4) {
-                    const float4 w4 = *reinterpret_cast<const float4*>(&ws_s[cur][half * HC + c0 + c]);
+                for (int c = 0; c < CH; c += 4) {
+                    const float4 w4 = *reinterpret_cast<const float4*>(&ws_s[buf][q][half * HC + c0 + c]);
                     uint64_t f01, f23;
                     if (magic) {
-                        f01 = ints_to_floats_magic(r[c + 0], r[c + 1]);
-                        f23 = ints_to_floats_magic(r[c + 2], r[c + 3]);
+                        f01 = ints_to_floats_magic(rr[c + 0], rr[c + 1]);
+                        f23 = ints_to_floats_magic(rr[c + 2], rr[c + 3]);
                     } else {
-                        f01 = pack2(static_cast<float>(static_cast<int>(r[c + 0])), static_cast<float>(static_cast<int>(r[c + 1])));
-                        f23 = pack2(static_cast<float>(static_cast<int>(r[c + 2])), static_cast<float>(static_cast<int>(r[c + 3])));
+                        f01 = pack2(static_cast<float>(static_cast<int>(rr[c + 0])), static_cast<float>(static_cast<int>(rr[c + 1])));
+                        f23 = pack2(static_cast<float>(static_cast<int>(rr[c + 2])), static_cast<float>(static_cast<int>(rr[c + 3])));
                     }
                     acc2[(c0 + c) / 2] = fma2(mul2(f01, pack2(w4.x, w4.y)), xs2, acc2[(c0 + c) / 2]);
                     acc2[(c0 + c) / 2 + 1] = fma2(mul2(f23, pack2(w4.z, w4.w)), xs2, acc2[(c0 + c) / 2 + 1]);
                 }
                 if (a.dump && m_ok) {
 #pragma unroll
-                    for (int c = 0; c < 32; ++c)
+                    for (int c = 0; c < CH; ++c)
                         if (n0 + half * HC + c0 + c < a.N)
-                            a.dump[(static_cast<size_t>(m) * a.N + n0 + half * HC + c0 + c) * G + j] = static_cast<int>(r[c]);
+                            a.dump[(static_cast<size_t>(m) * a.N + n0 + half * HC + c0 + c) * G + j] = static_cast<int>(rr[c]);
                 }
             }
             // this slice of tensor memory may be overwritten by group j + kAccStages
             tc_fence_before();
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
-            if (et < BN) ws_s[cur ^ 1][et] = ws_next;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
+            if (q == kWsGroups - 1) asm volatile("bar.sync 1, 256;" ::: "memory");
         }
         // ---- final store: fp16, optional residual add or SwiGLU, 16 bytes at a time ----
         if (ok && m_ok) {
@@ -327,6 +352,8 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 }
             }
         }
+        asm volatile("bar.sync 1, 256;" ::: "memory");  // nobody still reads this tile's weight scales
+        }  // tiles
     }
     // ---- teardown: everyone meets, then the allocating warp frees the tensor memory ----
     tc_fence_before();
@@ -363,6 +390,8 @@ int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t str
     p.status = device_status;
     p.mmas_per_group = a.g / 32;
     p.num_kblocks = a.K / BK;
+    p.tiles_m = (a.M + BM - 1) / BM;
+    p.tiles_total = p.tiles_m * ((a.N + BN - 1) / BN);
     const size_t smem = static_cast<size_t>(kStages) * kStageBytes + 1024;
     static bool attr_set = false;
     if (!attr_set) {
@@ -372,7 +401,10 @@ int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t str
         attr_set = true;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((a.N + BN - 1) / BN, (a.M + BM - 1) / BM, 1);
+    int sms = 148, dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    // persistent: one CTA per SM walks its tiles (m fastest, so that concurrent CTAs share weight tiles in L2)
+    cfg.gridDim = dim3(p.tiles_total < sms ? p.tiles_total : sms, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
