@@ -35,6 +35,16 @@ def peaks():
     return {"hbm_gbs": FALLBACK_HBM_GBS, "source": "fallback"}
 
 
+# DRAM traffic / algorithmic bytes of the dominant kernels, from one ncu capture each (dram__bytes_read.sum +
+# dram__bytes_write.sum of a launch, summaries under profiles/): gemv_packed_kernel on gate_up M=1 g=256 moved
+# 50.274 MB against 50.241 MB; gemm_i8_kernel on gate_up M=2048 g=256 moved 130.8 MB against 135.2 MB (weights,
+# scales, codes and activation scales in, fp16 out; part of the output was still in L2 when the kernel ended).
+# Traffic of both grows in proportion to the bytes a launch touches, so a launch's traffic is that ratio times
+# its own algorithmic bytes.
+GEMV_TRAFFIC_RATIO = 50.274 / 50.241
+GEMM_TRAFFIC_RATIO = 130.8 / 135.2
+
+
 def algorithmic_bytes(M, N, K, g):
     """int8 weights + fp16 weight scales + fp16 activations in + fp16 out; intermediates count zero."""
     G = (K + g - 1) // g
@@ -685,7 +695,12 @@ def main():
                        "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
                        "library_int8_tops_8192cubed": wl.library_int8_tops()},
             "roofline": {"bound": "tensor", "achieved": round(tops / world, 1), "peak": round(peak, 1), "unit": "TOP/s",
-                         "frac": round(tops / world / peak, 4), "traffic": None,
+                         "frac": round(tops / world / peak, 4),
+                         "traffic": int(GEMM_TRAFFIC_RATIO * sum(
+                             c["N"] * c["K"] + 2 * c["N"] * (c["K"] // c["g"]) + c["M"] * c["K"]
+                             + 4 * c["M"] * (c["K"] // c["g"]) + 2 * c["M"] * c["N"] for c in wl.cases) / len(wl.cases)),
+                         "traffic_source": "bytes per launch (mean over the cases) scaled by the DRAM/algorithmic ratio "
+                                           "of one ncu capture (gate_up M=2048 g=256)",
                          "peak_source": "2 x measured bf16 burst (int8 dense runs at twice the bf16 rate; no "
                                         "int8 figure is in MEASURED_PEAKS.json)" if bf16 else "2 x fallback bf16",
                          "kernel": "gemm_i8_kernel"},
@@ -722,7 +737,11 @@ def main():
         if lin:
             ach = lin[1] / lin_s / 1e9
             line["roofline"] = {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                                "frac": round(ach / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"],
+                                "frac": round(ach / pk["hbm_gbs"], 4),
+                                "traffic": int(GEMV_TRAFFIC_RATIO * lin[1]),
+                                "traffic_source": "algorithmic bytes per launch scaled by the DRAM/algorithmic ratio of "
+                                                  "one ncu capture (gate_up M=1 g=256)",
+                                "peak_source": pk["source"],
                                 "kernel": "gemv_packed_kernel (the 4 linears of each layer, timed alone)",
                                 "algorithmic_bytes_per_launch": int(lin[1]), "us_per_launch": round(lin_s * 1e6, 2)}
         if reference:
@@ -759,7 +778,9 @@ def main():
                    "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
                    "tops": round(wl.ops_per_step * world / (ms_per_step * 1e-3) / 1e12, 2)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"],
+                     "frac": round(achieved / pk["hbm_gbs"], 4),
+                     "traffic": None if reference else int(GEMV_TRAFFIC_RATIO * per_launch_bytes),
+                     "peak_source": pk["source"],
                      "kernel": "gemv_kernel" if not reference else "reference kernels",
                      "algorithmic_bytes_per_launch": int(per_launch_bytes)},
         "clocks": clocks,

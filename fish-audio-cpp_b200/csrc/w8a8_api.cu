@@ -37,12 +37,14 @@ int fail(int status, const char* fmt, ...) {
     return status;
 }
 
-bool pdl_enabled() {
-    static const bool on = [] {
-        const char* v = std::getenv("W8A8_NO_PDL");
-        return !(v && *v && *v != '0');
+bool pdl_enabled(int kernel_class) {
+    static const int mask = [] {
+        const char* off = std::getenv("W8A8_NO_PDL");
+        if (off && *off && *off != '0') return 0;
+        const char* v = std::getenv("W8A8_PDL");
+        return v && *v ? std::atoi(v) : kPdlDefaultMask;
     }();
-    return on;
+    return (mask & kernel_class) != 0;
 }
 
 int check_launch(const char* what) {

@@ -126,16 +126,45 @@ struct AttnParams {
     int S;                    // context slices = cluster size
 };
 
-constexpr int kAttnWarps = 4;
+constexpr int kAttnWarps = 8;
 constexpr int kQPerKv = 4;  // query heads per kv head handled by one CTA
 
-struct SoftState {  // per (head) running softmax state of one lane group: 16 of the 128 dims
-    float m, l;
-    float acc[16];
+// K and V of one 16-token block as one lane sees them (64 registers):
+//   k[j][i]: token j*8 + (lane>>2), 16-byte piece i*4 + (lane&3) of its 128 dims;
+//   v[q][h]: token {2t, 2t+1, 2t+8, 2t+9}[q] with t = lane&3, 16-byte piece (lane>>2) + 8h.
+struct KvFrag {
+    uint4 k[2][4];
+    uint4 v[4][2];
 };
 
-// grid (S, n_kv, B), cluster (S,1,1). Lane layout: 8 lanes per token (16 dims each), 4 tokens per pass.
-__global__ void __launch_bounds__(kAttnWarps * 32) paged_attention_decode_kernel(const AttnParams p) {
+__device__ __forceinline__ uint4 ld_stream16(const __half* ptr) {
+    uint4 r;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(ptr));
+    return r;
+}
+
+// D(16x8, fp32) += A(16x16 fp16, rows 8..15 zero) x B(16x8 fp16). Only rows 0..7 of D are kept.
+__device__ __forceinline__ void mma_top_rows(float& d0, float& d1, uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+    float j2, j3;
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};"
+        : "=f"(d0), "=f"(d1), "=f"(j2), "=f"(j3)
+        : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(d0), "f"(d1), "f"(0.0f), "f"(0.0f));
+}
+
+__device__ __forceinline__ uint32_t reg_of(const uint4& v, int i) {
+    return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+}
+
+// grid (S, n_kv, B), cluster (S,1,1), 8 warps. The four query heads of a kv group are rows 0..3 of a
+// 16-row tensor-core tile (mma.sync.m16n8k16, fp32 accumulate): scores = Q K^T with tokens as the
+// n index, then out += P V with P rounded to fp16 (the softmax denominator is summed from the same
+// rounded values, so the weights stay normalised). The sums over head dims (QK) and over tokens (PV)
+// do not depend on order, so each lane takes whole 16-byte pieces straight from the cache and the
+// "k index" of an MMA is a permutation of the real one, applied to q alike; V's token pairs are put
+// side by side with one byte-permute per register. Nothing is staged in shared memory. Each warp
+// keeps the next block's 8 KB in flight while it works on the current one.
+__global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_kernel(const AttnParams p) {
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
     __shared__ float red_m[kAttnWarps][kQPerKv], red_l[kAttnWarps][kQPerKv];
@@ -146,120 +175,145 @@ __global__ void __launch_bounds__(kAttnWarps * 32) paged_attention_decode_kernel
 
     const int s = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, S = p.S;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int grp = lane >> 3, sub = lane & 7;  // token within a pass, 16-dim slice
+    const int g = lane >> 2, t = lane & 3;
     const int seq_len = p.seq_lens[b];
     const int n_blocks = (seq_len + kBlockTokens - 1) / kBlockTokens;
     const int heads_here = p.n_q / p.n_kv;  // == kQPerKv (checked on the host)
 
-    // q of the 4 heads as fp32 in shared memory (read back as broadcast 128-bit loads)
-    __shared__ __align__(16) float q_s[kQPerKv][kHeadDim];
-    for (int i = threadIdx.x; i < kQPerKv * kHeadDim; i += blockDim.x)
-        q_s[i / kHeadDim][i % kHeadDim] =
-            __half2float(p.q[(static_cast<size_t>(b) * p.n_q + kvh * heads_here + i / kHeadDim) * kHeadDim + i % kHeadDim]);
-    __syncthreads();
-    SoftState st[kQPerKv];
+    // q of head g (rows 4..15 of the tile are zero), in the same piece order as K
+    uint32_t qa[4][4];
 #pragma unroll
-    for (int hh = 0; hh < kQPerKv; ++hh) {
-        st[hh].m = -1e30f; st[hh].l = 0.0f;
-#pragma unroll
-        for (int d = 0; d < 16; ++d) st[hh].acc[d] = 0.0f;
+    for (int i = 0; i < 4; ++i) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (g < kQPerKv)
+            v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(b) * p.n_q + kvh * heads_here + g) * kHeadDim +
+                                                (i * 4 + t) * 8);
+        qa[i][0] = v.x; qa[i][1] = v.y; qa[i][2] = v.z; qa[i][3] = v.w;
     }
 
-    // 16-token blocks are dealt round-robin: first over the cluster's CTAs, then over the warps. All 16
-    // loads of a block (4 passes x K and V halves) are requested before any arithmetic, so that a warp
-    // keeps 8 KB in flight instead of paying one memory round trip per pass.
-    for (int bi = s + warp * S; bi < n_blocks; bi += S * kAttnWarps) {
-        const int phys = p.block_table[static_cast<size_t>(b) * p.max_blocks + bi];
-        const size_t base = (((static_cast<size_t>(phys) * p.n_layers + p.layer) * p.n_kv + kvh) * kBlockTokens) * kHeadDim;
+    // 16-token blocks are dealt round-robin: first over the cluster's CTAs, then over the warps.
+    const int stride = S * kAttnWarps, first = s + warp * S;
+    const int n_mine = first < n_blocks ? (n_blocks - first + stride - 1) / stride : 0;
+    // physical block numbers of this warp's next 32 blocks, one per lane
+    auto fetch_phys = [&](int it0) -> int {
+        const int bi = first + (it0 + lane) * stride;
+        return bi < n_blocks ? p.block_table[static_cast<size_t>(b) * p.max_blocks + bi] : 0;
+    };
+    int phys_mine = fetch_phys(0);
+
+    auto load = [&](KvFrag& f, int it) {
+        if ((it & 31) == 0 && it > 0) phys_mine = fetch_phys(it);
+        const int phys = __shfl_sync(0xffffffffu, phys_mine, it & 31);
+        const int bi = first + it * stride;
         const int tokens = min(kBlockTokens, seq_len - bi * kBlockTokens);
-        uint4 kraw[4][2], vraw[4][2];
+        const size_t base = (((static_cast<size_t>(phys) * p.n_layers + p.layer) * p.n_kv + kvh) * kBlockTokens) * kHeadDim;
 #pragma unroll
-        for (int pass = 0; pass < 4; ++pass) {
-            const int t = pass * 4 + grp;
-            const size_t off = base + static_cast<size_t>(t < tokens ? t : 0) * kHeadDim + sub * 16;
-            kraw[pass][0] = *reinterpret_cast<const uint4*>(p.k_cache + off);
-            kraw[pass][1] = *reinterpret_cast<const uint4*>(p.k_cache + off + 8);
-            vraw[pass][0] = *reinterpret_cast<const uint4*>(p.v_cache + off);
-            vraw[pass][1] = *reinterpret_cast<const uint4*>(p.v_cache + off + 8);
+        for (int j = 0; j < 2; ++j) {
+            const int tok = j * 8 + g;
+            const __half* row = p.k_cache + base + static_cast<size_t>(tok < tokens ? tok : 0) * kHeadDim;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) f.k[j][i] = ld_stream16(row + (i * 4 + t) * 8);
         }
 #pragma unroll
-        for (int pass = 0; pass < 4; ++pass) {
-            const int t = pass * 4 + grp;
-            const bool live = t < tokens;
-            float kf[16], vf[16];
-            {
-                const __half* a0 = reinterpret_cast<const __half*>(&kraw[pass][0]);
-                const __half* a1 = reinterpret_cast<const __half*>(&kraw[pass][1]);
-                const __half* b0 = reinterpret_cast<const __half*>(&vraw[pass][0]);
-                const __half* b1 = reinterpret_cast<const __half*>(&vraw[pass][1]);
+        for (int q = 0; q < 4; ++q) {
+            const int tok = 2 * t + (q & 1) + 8 * (q >> 1);
+            const __half* row = p.v_cache + base + static_cast<size_t>(tok < tokens ? tok : 0) * kHeadDim;
 #pragma unroll
-                for (int d = 0; d < 8; ++d) {
-                    kf[d] = __half2float(a0[d]); kf[8 + d] = __half2float(a1[d]);
-                    vf[d] = __half2float(b0[d]); vf[8 + d] = __half2float(b1[d]);
-                }
+            for (int h = 0; h < 2; ++h) f.v[q][h] = ld_stream16(row + (g + 8 * h) * 8);
+        }
+    };
+
+    float m_run = -1e30f, l_run = 0.0f;
+    float o[16][2];  // head g; tile n = 8h + e holds dims (2t + 8h)*8 + e and (2t + 1 + 8h)*8 + e
+#pragma unroll
+    for (int n = 0; n < 16; ++n) { o[n][0] = 0.0f; o[n][1] = 0.0f; }
+
+    auto compute = [&](const KvFrag& f, int it) {
+        const int bi = first + it * stride;
+        const int tokens = min(kBlockTokens, seq_len - bi * kBlockTokens);
+        float sc[2][2];
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+            sc[j][0] = 0.0f; sc[j][1] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    mma_top_rows(sc[j][0], sc[j][1], qa[i][2 * h], qa[i][2 * h + 1], reg_of(f.k[j][i], 2 * h),
+                                 reg_of(f.k[j][i], 2 * h + 1));
             }
+        }
+        float mx = -1e30f;
 #pragma unroll
-            for (int hh = 0; hh < kQPerKv; ++hh) {
-                float dot = 0.0f;
+        for (int j = 0; j < 2; ++j)
 #pragma unroll
-                for (int d4 = 0; d4 < 4; ++d4) {
-                    const float4 q4 = *reinterpret_cast<const float4*>(&q_s[hh][sub * 16 + d4 * 4]);
-                    dot = fmaf(q4.x, kf[d4 * 4 + 0], dot);
-                    dot = fmaf(q4.y, kf[d4 * 4 + 1], dot);
-                    dot = fmaf(q4.z, kf[d4 * 4 + 2], dot);
-                    dot = fmaf(q4.w, kf[d4 * 4 + 3], dot);
-                }
-                dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-                if (live) {
-                    const float score = dot * p.sm_scale;
-                    const float new_max = fmaxf(st[hh].m, score);
-                    const float scale = expf(st[hh].m - new_max);
-                    const float e = expf(score - new_max);
-                    st[hh].l = st[hh].l * scale + e;
-#pragma unroll
-                    for (int d = 0; d < 16; ++d) st[hh].acc[d] = st[hh].acc[d] * scale + e * vf[d];
-                    st[hh].m = new_max;
-                }
+            for (int e = 0; e < 2; ++e) {
+                const int tok = j * 8 + 2 * t + e;
+                sc[j][e] = tok < tokens ? sc[j][e] * p.sm_scale : -1e30f;
+                mx = fmaxf(mx, sc[j][e]);
             }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float new_m = fmaxf(m_run, mx);
+        const float corr = __expf(m_run - new_m);
+        m_run = new_m;
+        const __half2 p0 = __floats2half2_rn(__expf(sc[0][0] - new_m), __expf(sc[0][1] - new_m));
+        const __half2 p1 = __floats2half2_rn(__expf(sc[1][0] - new_m), __expf(sc[1][1] - new_m));
+        const float2 f0 = __half22float2(p0), f1 = __half22float2(p1);
+        l_run = l_run * corr + ((f0.x + f0.y) + (f1.x + f1.y));
+        const uint32_t pa0 = *reinterpret_cast<const uint32_t*>(&p0), pa2 = *reinterpret_cast<const uint32_t*>(&p1);
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int n = h * 8 + e;
+                const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
+                const uint32_t b0 = __byte_perm(reg_of(f.v[0][h], e >> 1), reg_of(f.v[1][h], e >> 1), sel);
+                const uint32_t b1 = __byte_perm(reg_of(f.v[2][h], e >> 1), reg_of(f.v[3][h], e >> 1), sel);
+                o[n][0] *= corr;
+                o[n][1] *= corr;
+                mma_top_rows(o[n][0], o[n][1], pa0, pa2, b0, b1);
+            }
+    };
+
+    {
+        KvFrag fa, fb;
+        int it = 0;
+        if (n_mine > 0) load(fa, 0);
+        while (it < n_mine) {
+            if (it + 1 < n_mine) load(fb, it + 1);
+            compute(fa, it);
+            if (++it >= n_mine) break;
+            if (it + 1 < n_mine) load(fa, it + 1);
+            compute(fb, it);
+            ++it;
         }
     }
-    // ---- merge the 4 lane groups of the warp (xor 8, 16), same 16-dim slice in each ----
+    // the four lanes of a quad hold the same head: their partial denominators add up
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (g < kQPerKv) {
+        if (t == 0) { red_m[warp][g] = m_run; red_l[warp][g] = l_run; }
 #pragma unroll
-    for (int hh = 0; hh < kQPerKv; ++hh) {
+        for (int h = 0; h < 2; ++h)
 #pragma unroll
-        for (int o = 8; o <= 16; o <<= 1) {
-            const float om = __shfl_xor_sync(0xffffffffu, st[hh].m, o);
-            const float ol = __shfl_xor_sync(0xffffffffu, st[hh].l, o);
-            const float nm = fmaxf(st[hh].m, om);
-            const float sa = expf(st[hh].m - nm), sb = expf(om - nm);
-            st[hh].l = st[hh].l * sa + ol * sb;
-#pragma unroll
-            for (int d = 0; d < 16; ++d) {
-                const float oa = __shfl_xor_sync(0xffffffffu, st[hh].acc[d], o);
-                st[hh].acc[d] = st[hh].acc[d] * sa + oa * sb;
+            for (int e = 0; e < 8; ++e) {
+                red_acc[warp][g][(2 * t + 8 * h) * 8 + e] = o[h * 8 + e][0];
+                red_acc[warp][g][(2 * t + 1 + 8 * h) * 8 + e] = o[h * 8 + e][1];
             }
-            st[hh].m = nm;
-        }
-        if (grp == 0) {
-            if (sub == 0) { red_m[warp][hh] = st[hh].m; red_l[warp][hh] = st[hh].l; }
-#pragma unroll
-            for (int d = 0; d < 16; ++d) red_acc[warp][hh][sub * 16 + d] = st[hh].acc[d];
-        }
     }
     __syncthreads();
     // ---- merge the warps: thread -> (head, 4 dims) ----
-    {
+    if (threadIdx.x < kQPerKv * 32) {
         const int hh = threadIdx.x >> 5, d0 = (threadIdx.x & 31) * 4;
         float m = -1e30f;
         for (int w = 0; w < kAttnWarps; ++w) m = fmaxf(m, red_m[w][hh]);
         float l = 0.0f, a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
         for (int w = 0; w < kAttnWarps; ++w) {
-            const float sc = expf(red_m[w][hh] - m);
-            l += red_l[w][hh] * sc;
+            const float scw = __expf(red_m[w][hh] - m);
+            l += red_l[w][hh] * scw;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) a[i] += red_acc[w][hh][d0 + i] * sc;
+            for (int i = 0; i < 4; ++i) a[i] += red_acc[w][hh][d0 + i] * scw;
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) cta_acc[hh][d0 + i] = a[i];
@@ -268,7 +322,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) paged_attention_decode_kernel
     cg::cluster_group cluster = cg::this_cluster();
     if (S > 1) cluster.sync(); else __syncthreads();
     // ---- CTA 0 of the cluster merges the S context slices and writes the 4 heads ----
-    if (s == 0) {
+    if (s == 0 && threadIdx.x < kQPerKv * 32) {
         const int hh = threadIdx.x >> 5, d0 = (threadIdx.x & 31) * 4;
         float m = -1e30f;
         for (int r = 0; r < S; ++r) m = fmaxf(m, (S > 1 ? cluster.map_shared_rank(cta_m, r) : cta_m)[hh]);
@@ -277,10 +331,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32) paged_attention_decode_kernel
             const float* pm = S > 1 ? cluster.map_shared_rank(cta_m, r) : cta_m;
             const float* pl = S > 1 ? cluster.map_shared_rank(cta_l, r) : cta_l;
             const float* pa = S > 1 ? cluster.map_shared_rank(&cta_acc[0][0], r) : &cta_acc[0][0];
-            const float sc = expf(pm[hh] - m);
-            l += pl[hh] * sc;
+            const float scr = __expf(pm[hh] - m);
+            l += pl[hh] * scr;
             const float4 v4 = *reinterpret_cast<const float4*>(pa + hh * kHeadDim + d0);
-            a[0] += v4.x * sc; a[1] += v4.y * sc; a[2] += v4.z * sc; a[3] += v4.w * sc;
+            a[0] += v4.x * scr; a[1] += v4.y * scr; a[2] += v4.z * scr; a[3] += v4.w * scr;
         }
         const float inv = seq_len > 0 ? 1.0f / l : 0.0f;  // empty sequence -> zeros (paged_attention.cu:44-50)
         __align__(8) __half o4[4];
@@ -288,28 +342,27 @@ __global__ void __launch_bounds__(kAttnWarps * 32) paged_attention_decode_kernel
         for (int i = 0; i < 4; ++i) o4[i] = __float2half(seq_len > 0 ? a[i] * inv : 0.0f);
 #pragma unroll
         for (int i = 0; i < 4; ++i) out_s[hh * kHeadDim + d0 + i] = o4[i];
-        const size_t o = (static_cast<size_t>(b) * p.n_q + kvh * heads_here + hh) * kHeadDim + d0;
-        if (p.out) *reinterpret_cast<uint2*>(p.out + o) = *reinterpret_cast<const uint2*>(o4);
+        const size_t oo = (static_cast<size_t>(b) * p.n_q + kvh * heads_here + hh) * kHeadDim + d0;
+        if (p.out) *reinterpret_cast<uint2*>(p.out + oo) = *reinterpret_cast<const uint2*>(o4);
     }
     if (S > 1) cluster.sync(); else __syncthreads();
     // ---- optional: quantise these 512 channels for the o-projection (int8_gemm.cu:147-211) ----
     if (s == 0 && p.Xq) {
-        const int g = p.g, K = p.n_q * kHeadDim, G = K / g;
-        const int ch0 = kvh * heads_here * kHeadDim;        // first channel of this CTA
-        const int groups_here = (kQPerKv * kHeadDim) / g;   // 2 at g=256, 8 at g=64
-        // warp per group (8 warps)
+        const int gsz = p.g, K = p.n_q * kHeadDim, G = K / gsz;
+        const int ch0 = kvh * heads_here * kHeadDim;          // first channel of this CTA
+        const int groups_here = (kQPerKv * kHeadDim) / gsz;   // 2 at g=256, 8 at g=64
         for (int j = warp; j < groups_here; j += kAttnWarps) {
             float amax = 0.0f;
-            for (int e = lane; e < g; e += 32) amax = fmaxf(amax, fabsf(__half2float(out_s[j * g + e])));
-            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            for (int e = lane; e < gsz; e += 32) amax = fmaxf(amax, fabsf(__half2float(out_s[j * gsz + e])));
+            for (int off = 16; off > 0; off >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, off));
             float scale = amax / 127.0f;
             if (scale < 1e-8f) scale = 1e-8f;
-            if (lane == 0) p.Xs[static_cast<size_t>(b) * G + ch0 / g + j] = scale;
+            if (lane == 0) p.Xs[static_cast<size_t>(b) * G + ch0 / gsz + j] = scale;
             const float inv_scale = 1.0f / scale;
-            for (int e = lane; e < g; e += 32) {
-                int qv = __float2int_rn(__half2float(out_s[j * g + e]) * inv_scale);
+            for (int e = lane; e < gsz; e += 32) {
+                int qv = __float2int_rn(__half2float(out_s[j * gsz + e]) * inv_scale);
                 qv = max(-127, min(127, qv));
-                p.Xq[static_cast<size_t>(b) * K + ch0 + j * g + e] = static_cast<int8_t>(qv);
+                p.Xq[static_cast<size_t>(b) * K + ch0 + j * gsz + e] = static_cast<int8_t>(qv);
             }
         }
     }
@@ -332,7 +385,7 @@ int launch_qknorm_rope_kvwrite(const __half* qkv, const __half* q_norm_w, const 
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = pdl_enabled(kPdlAttn) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, qknorm_rope_kvwrite_kernel, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "qknorm_rope_kvwrite launch: %s", cudaGetErrorString(e));
     return W8A8_OK;
@@ -347,7 +400,14 @@ int launch_paged_attention_decode(const __half* q, const __half* k_cache, const 
         return fail(W8A8_ERR_UNSUPPORTED, "paged attention here handles 4 query heads per kv head (got %d / %d)", n_q, n_kv);
     if (Xq && (g <= 0 || (kQPerKv * kHeadDim) % g != 0))
         return fail(W8A8_ERR_UNSUPPORTED, "fused output quantisation needs a group size dividing 512 (got %d)", g);
-    if (splits <= 0) splits = 4;
+    if (splits <= 0) {  // one CTA per SM: as many context slices as the (sequence, kv head) pairs leave room for
+        int dev = 0, sms = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess ||
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+        const int want = sms / (B * n_kv);
+        splits = want >= 8 ? 8 : want >= 4 ? 4 : want >= 2 ? 2 : 1;
+    }
     if (splits > 8) splits = 8;
     AttnParams p = {q, k_cache, v_cache, block_table, seq_lens, max_blocks, n_q, n_kv, layer, n_layers, sm_scale,
                     out, Xq, Xs, g, splits};
@@ -363,7 +423,7 @@ int launch_paged_attention_decode(const __half* q, const __half* k_cache, const 
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cfg.numAttrs = pdl_enabled(kPdlAttn) ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, paged_attention_decode_kernel, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "paged_attention_decode launch: %s", cudaGetErrorString(e));
     return W8A8_OK;

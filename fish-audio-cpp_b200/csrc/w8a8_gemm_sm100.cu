@@ -412,7 +412,7 @@ int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t str
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = pdl_enabled(kPdlLinear) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_kernel, map_x, map_w, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
     return W8A8_OK;

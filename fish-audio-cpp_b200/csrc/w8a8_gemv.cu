@@ -306,7 +306,7 @@ int launch_variant(const GemvParams& p, const Plan& pl, cudaStream_t stream) {
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 2 : 1;
+    cfg.numAttrs = pdl_enabled(kPdlLinear) ? 2 : 1;
     cudaError_t e = cudaLaunchKernelEx(&cfg, gemv_kernel<MT, CPG>, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "gemv launch: %s", cudaGetErrorString(e));
     return W8A8_OK;

@@ -469,7 +469,7 @@ int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = pdl_enabled(kPdlLinear) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "gemv_tma launch: %s", cudaGetErrorString(e));
     return W8A8_OK;

@@ -15,8 +15,14 @@ namespace w8a8 {
 int fail(int status, const char* fmt, ...);
 // cudaGetLastError() after a launch -> status.
 int check_launch(const char* what);
-// Programmatic dependent launch is on unless the environment says W8A8_NO_PDL=1 (debugging aid).
-bool pdl_enabled();
+// Which launches carry the programmatic-dependent-launch attribute (may start while the kernel before
+// them is still running, and wait inside the kernel for its results). Classes are a bit mask so that
+// the environment variable W8A8_PDL=<mask> can switch them one by one; W8A8_NO_PDL=1 switches all off.
+enum { kPdlLinear = 1, kPdlRow = 2, kPdlAttn = 4 };
+// Measured over the decode stack: early launch pays for the linears (weights are requested while the
+// small kernel before them runs) and the row kernels, and costs time on the clustered attention launch.
+constexpr int kPdlDefaultMask = kPdlLinear | kPdlRow;
+bool pdl_enabled(int kernel_class);
 
 inline int norm_group(int K, int group_size) {
     return (group_size <= 0 || group_size > K) ? K : group_size;

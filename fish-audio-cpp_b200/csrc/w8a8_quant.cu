@@ -348,7 +348,7 @@ int launch_groupquant(const __half* X, const __half* smooth_inv, const __half* a
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = pdl_enabled(kPdlRow) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, groupquant_kernel<LANES>, X, smooth_inv, act_scale, Xq, Xs, K, G);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "groupquant launch: %s", cudaGetErrorString(e));
     return W8A8_OK;
@@ -408,7 +408,7 @@ int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
-        cfg.numAttrs = pdl_enabled() ? 1 : 0;
+        cfg.numAttrs = pdl_enabled(kPdlRow) ? 1 : 0;
         cudaError_t e = cudaLaunchKernelEx(&cfg, rowquant_fast_kernel, p);
         if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "rowquant_fast launch: %s", cudaGetErrorString(e));
         return W8A8_OK;
@@ -429,7 +429,7 @@ int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = pdl_enabled(kPdlRow) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, rowquant_kernel, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "rowquant launch: %s", cudaGetErrorString(e));
     return W8A8_OK;

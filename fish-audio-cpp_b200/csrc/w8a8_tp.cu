@@ -294,7 +294,7 @@ int launch_tp_allreduce_rowquant(TpState* t, __half* x, const __half* partial, c
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = pdl_enabled(kPdlRow) ? 1 : 0;
     cudaError_t e = cudaLaunchKernelEx(&cfg, tp_allreduce_rowquant_kernel, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "tp row kernel launch: %s", cudaGetErrorString(e));
     return W8A8_OK;
