@@ -58,6 +58,7 @@ def load_library() -> C.CDLL:
         "w8a8_residual_add": (I, [P, P, P, L, P]),
         "w8a8_linear": (I, [P, P, P, I, P, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_linear_q": (I, [P, P, P, I, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
+        "w8a8_rmsnorm_linear": (I, [P, P, P, I, P, P, P, P, F, P, I, I, I, C.POINTER(LinearOpts), P, P, P]),
         "w8a8_pack_gate_up": (I, [P, P, P, P, P, I, I, I, P, P, P]),
         "w8a8_qknorm_rope_kvwrite": (I, [P, P, P, P, F, P, P, P, I, P, P, I, I, I, I, I, I, P, P]),
         "w8a8_paged_attention_decode": (I, [P, P, P, P, P, P, P, I, I, I, I, F, I, I, I, I, P, P, I, P]),
@@ -82,6 +83,7 @@ EXPORTS = [
     "w8a8_status_string", "w8a8_last_error", "w8a8_create", "w8a8_destroy", "w8a8_workspace_bytes",
     "w8a8_ctx_workspace_bytes", "w8a8_check_device_status", "w8a8_quantize", "w8a8_rms_norm",
     "w8a8_rmsnorm_quantize", "w8a8_silu", "w8a8_mul", "w8a8_residual_add", "w8a8_linear", "w8a8_linear_q",
+    "w8a8_rmsnorm_linear",
     "w8a8_pack_gate_up", "w8a8_qknorm_rope_kvwrite", "w8a8_paged_attention_decode", "w8a8_tp_create", "w8a8_tp_connect",
     "w8a8_tp_allreduce_rmsnorm_quantize", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
     "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch",
@@ -205,6 +207,15 @@ class Context:
         self._check(self.lib.w8a8_linear_q(self.handle, _ptr(W), _ptr(w_scale), group_size, _ptr(Xq), _ptr(Xs),
                                            _ptr(Y), M, N, K, self._opts(0, epilogue, residual, dump, kernel, split_k),
                                            _stream(stream)), "w8a8_linear_q")
+
+    def rmsnorm_linear(self, W, w_scale, group_size, x, norm_weight, eps, Y, M, N, K, residual=None, x_out=None,
+                       epilogue=EPI_NONE, epi_residual=None, kernel=KERNEL_AUTO, act_mode=ACT_PER_TOKEN_GROUP,
+                       codes_out=None, scales_out=None, stream=None):
+        self._check(self.lib.w8a8_rmsnorm_linear(self.handle, _ptr(W), _ptr(w_scale), group_size, _ptr(x),
+                                                 _ptr(residual), _ptr(x_out), _ptr(norm_weight), eps, _ptr(Y), M, N, K,
+                                                 self._opts(act_mode, epilogue, epi_residual, None, kernel, 0),
+                                                 _ptr(codes_out), _ptr(scales_out), _stream(stream)),
+                    "w8a8_rmsnorm_linear")
 
     def pack_gate_up(self, w_gate, s_gate, w_up, s_up, inter, K, G, W_out, scale_out, stream=None):
         self._check(self.lib.w8a8_pack_gate_up(self.handle, _ptr(w_gate), _ptr(s_gate), _ptr(w_up), _ptr(s_up),

@@ -116,8 +116,8 @@ int dispatch_linear_q(const LinearArgs& a, int kernel, int* device_status, cudaS
     return launch_linear_generic(a, s);
 }
 
-static int dispatch_q(w8a8_ctx* ctx, const LinearArgs& args, int kernel, cudaStream_t s) {
-    LinearArgs a = args;
+// Points the arguments at the context's split-K scratch and at the packed image of the weight, if registered.
+static void fill_scratch(w8a8_ctx* ctx, LinearArgs& a) {
     a.splitk_partials = ctx->splitk_partials;
     a.splitk_partial_bytes = kSplitkPartialBytes;
     a.splitk_counters = ctx->splitk_counters;
@@ -127,6 +127,11 @@ static int dispatch_q(w8a8_ctx* ctx, const LinearArgs& args, int kernel, cudaStr
         auto it = ctx->packed.find(a.W);
         if (it != ctx->packed.end()) a.packed = it->second;
     }
+}
+
+static int dispatch_q(w8a8_ctx* ctx, const LinearArgs& args, int kernel, cudaStream_t s) {
+    LinearArgs a = args;
+    fill_scratch(ctx, a);
     return dispatch_linear_q(a, kernel, ctx->device_status, s);
 }
 
@@ -290,6 +295,49 @@ int w8a8_linear_q(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_s
     a.Xq = static_cast<const int8_t*>(Xq);
     a.Xs = static_cast<const float*>(Xs);
     return dispatch_q(ctx, a, opts ? opts->kernel : W8A8_KERNEL_AUTO, static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_rmsnorm_linear(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size, const void* x,
+                        const void* residual, void* x_out, const void* norm_weight, float eps, void* Y, int M, int N,
+                        int K, const w8a8_linear_opts* opts, void* codes_out, void* scales_out, void* stream) {
+    int rc = check_linear_common(ctx, W, w_scale, Y, M, N, K, opts);
+    if (rc) return rc;
+    if (M > 0 && (!x || !norm_weight)) return fail(W8A8_ERR_INVALID_ARG, "null x or norm weight");
+    if (residual && (!x_out || x_out == x))
+        return fail(W8A8_ERR_INVALID_ARG, "with a residual, x_out must be a buffer other than x");
+    if ((codes_out == nullptr) != (scales_out == nullptr))
+        return fail(W8A8_ERR_INVALID_ARG, "codes_out and scales_out go together");
+    if (M == 0) return W8A8_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int kernel = opts ? opts->kernel : W8A8_KERNEL_AUTO;
+    const int act_mode = opts ? opts->act_mode : W8A8_ACT_PER_TOKEN_GROUP;
+    LinearArgs a = make_args(W, w_scale, group_size, Y, M, N, K, opts);
+    if (act_mode == W8A8_ACT_PER_TOKEN_GROUP && (kernel == W8A8_KERNEL_AUTO || kernel == W8A8_KERNEL_GEMV_PACKED)) {
+        LinearArgs f = a;
+        f.X = static_cast<const __half*>(x);
+        f.norm_weight = static_cast<const __half*>(norm_weight);
+        f.norm_eps = eps;
+        f.norm_residual = static_cast<const __half*>(residual);
+        f.norm_x_out = static_cast<__half*>(x_out);
+        f.codes_out = static_cast<int8_t*>(codes_out);
+        f.scales_out = static_cast<float*>(scales_out);
+        fill_scratch(ctx, f);
+        if (gemv_packed_supports(f)) return launch_linear_gemv_packed(f, ctx->device_status, s);
+    }
+    // the two-launch form: row kernel into scratch (or the caller's buffers), then the integer kernel
+    const size_t need = quant_scratch_bytes(M, K, group_size);
+    if (!codes_out && need > ctx->workspace_bytes)
+        return fail(W8A8_ERR_WORKSPACE, "need %zu bytes of scratch, context has %zu", need, ctx->workspace_bytes);
+    int8_t* Xq = codes_out ? static_cast<int8_t*>(codes_out) : reinterpret_cast<int8_t*>(ctx->workspace);
+    float* Xs = scales_out ? static_cast<float*>(scales_out)
+                           : reinterpret_cast<float*>(ctx->workspace + align256(static_cast<size_t>(M) * K));
+    rc = launch_rowquant(static_cast<const __half*>(x), static_cast<__half*>(x_out),
+                         static_cast<const __half*>(residual), static_cast<const __half*>(norm_weight), eps, nullptr,
+                         nullptr, M, K, group_size, act_mode, nullptr, Xq, Xs, s);
+    if (rc) return rc;
+    a.Xq = Xq;
+    a.Xs = Xs;
+    return dispatch_q(ctx, a, kernel, s);
 }
 
 int w8a8_linear(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size, const void* act_scale,

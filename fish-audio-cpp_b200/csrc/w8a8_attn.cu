@@ -44,7 +44,6 @@ struct RopeParams {
 // trees followed by (p0+p2)+(p1+p3) reproduce its sum bit for bit (rms_norm.cu:23-49).
 __global__ void __launch_bounds__(128) qknorm_rope_kvwrite_kernel(const RopeParams p) {
     ptx::pdl_launch_dependents();
-    ptx::pdl_wait();
     const int b = blockIdx.x;
     const int head = blockIdx.y * 4 + (threadIdx.x >> 5);  // 0..n_q-1 q, then k heads, then v heads
     const int lane = threadIdx.x & 31;
@@ -52,14 +51,25 @@ __global__ void __launch_bounds__(128) qknorm_rope_kvwrite_kernel(const RopePara
     if (head >= total_heads) return;
     const __half* src = p.qkv + (static_cast<size_t>(b) * total_heads + head) * kHeadDim;
     const bool is_q = head < p.n_q, is_k = !is_q && head < p.n_q + p.n_kv;
+    // parameters (norm weights, rotation frequencies) are requested before the wait for the qkv projection
+    const __half* w = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+    __half wv[4];
+    float fr[4];
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        wv[v] = w ? w[v * 32 + lane] : __float2half(1.0f);
+        fr[v] = p.freqs[(v * 32 + lane) >> 1];
+    }
+    ptx::pdl_wait();
     const int pos = p.positions[b];
-
     __half h[4];
 #pragma unroll
     for (int v = 0; v < 4; ++v) h[v] = src[v * 32 + lane];
+    // the cache slot of the new token: a second dependent load, started now rather than after the arithmetic
+    int phys = 0;
+    if (!is_q) phys = p.block_table[static_cast<size_t>(b) * p.max_blocks + pos / kBlockTokens];
 
     if (is_q || is_k) {
-        const __half* w = is_q ? p.q_norm_w : p.k_norm_w;
         if (w) {
             float part[4];
 #pragma unroll
@@ -77,14 +87,13 @@ __global__ void __launch_bounds__(128) qknorm_rope_kvwrite_kernel(const RopePara
 #pragma unroll
             for (int v = 0; v < 4; ++v) {
                 float val = __half2float(h[v]) * rms;
-                h[v] = __float2half(val * __half2float(w[v * 32 + lane]));
+                h[v] = __float2half(val * __half2float(wv[v]));
             }
         }
         // RoPE on interleaved pairs (2i, 2i+1): neighbours in the same run (rope.cu:36-45)
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
-            const int e = v * 32 + lane;
-            const float freq = p.freqs[e >> 1];
+            const float freq = fr[v];
             float angle = freq * static_cast<float>(pos);
             float cos_a = cosf(angle), sin_a = sinf(angle);
             const float mine = __half2float(h[v]);
@@ -99,7 +108,6 @@ __global__ void __launch_bounds__(128) qknorm_rope_kvwrite_kernel(const RopePara
         for (int v = 0; v < 4; ++v) dst[v * 32 + lane] = h[v];
     } else {
         const int kvh = is_k ? head - p.n_q : head - p.n_q - p.n_kv;
-        const int phys = p.block_table[static_cast<size_t>(b) * p.max_blocks + pos / kBlockTokens];
         if (phys < 0) return;
         __half* cache = is_k ? p.k_cache : p.v_cache;
         __half* dst = cache + ((((static_cast<size_t>(phys) * p.n_layers + p.layer) * p.n_kv + kvh) * kBlockTokens) +

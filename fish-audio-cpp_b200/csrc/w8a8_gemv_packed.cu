@@ -70,6 +70,12 @@ __device__ __forceinline__ uint32_t lds16(uint32_t addr) {
     return v;
 }
 
+__device__ __forceinline__ uint4 ld_cg16(const __half* p) {
+    uint4 v;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
 __device__ __forceinline__ float ld_cg(const float* p) {
     float v;
     asm volatile("ld.global.cg.f32 %0, [%1];\n" : "=f"(v) : "l"(p));
@@ -78,9 +84,16 @@ __device__ __forceinline__ float ld_cg(const float* p) {
 
 // GM: 64 or 128 = the group size itself; 256 = any group size that is a multiple of 256 (a unit is then
 // one whole group = g/256 blocks).
-template <int MT, int GM>
-__global__ void __launch_bounds__(kThreads, MT == 4 ? 1 : 2)
+//
+// FUSED: the activations arrive as fp16 rows and every CTA forms codes and scales itself, in shared memory,
+// before it consumes its first block (whose copy is already in flight): [x + residual] -> RMSNorm with the
+// summation order of the reference's 1024-thread launch (rms_norm.cu:23-49) -> group quantiser
+// (int8_gemm.cu:147-211). One warp per token row, so M <= 8. This replaces a separate launch of a kernel
+// that runs on M CTAs and leaves the rest of the GPU idle.
+template <int MT, int GM, bool FUSED>
+__global__ void __launch_bounds__(kThreads, (MT == 4 || FUSED) ? 1 : 2)
 gemv_packed_kernel(const GemvPackedParams p) {
+    static_assert(!FUSED || MT == 1, "the fused prologue handles one row per warp");
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bars[kWarps][kStages];
     const LinearArgs& a = p.a;
@@ -119,6 +132,12 @@ gemv_packed_kernel(const GemvPackedParams p) {
         const int pre = T < kStages ? T : kStages;
         for (int i = 0; i < pre; ++i) issue();
     }
+    if constexpr (FUSED) {  // the norm weight is a parameter too: stage it before the wait
+        unsigned char* fbase = smem_raw + (ring - warp * kRingBytes - ptx::smem_u32(smem_raw)) + kWarps * kRingBytes;
+        __half* normw_s = reinterpret_cast<__half*>(fbase) + 8 * a.K;
+        for (int c8 = threadIdx.x; c8 < a.K / 8; c8 += kThreads)
+            reinterpret_cast<uint4*>(normw_s)[c8] = __ldg(reinterpret_cast<const uint4*>(a.norm_weight) + c8);
+    }
     // Everything above touches only weights. Let the next launch begin its own prologue, then wait
     // for the kernel before this one: it produces the activations.
     ptx::pdl_launch_dependents();
@@ -126,11 +145,144 @@ gemv_packed_kernel(const GemvPackedParams p) {
 
     const int8_t* xq[MT];
     const float* xsp[MT][2];
+    uint32_t xq_s = 0;                    // FUSED: this lane's code row in shared memory
+    const float* xsp_s[2] = {nullptr, nullptr};
+    if constexpr (FUSED) {
+        const int K = a.K, pitch = K + 64;  // the pitch puts rows gq and gq+1 in different bank halves
+        unsigned char* fbase = smem_raw + (ring - warp * kRingBytes - ptx::smem_u32(smem_raw)) + kWarps * kRingBytes;
+        __half* rows_s = reinterpret_cast<__half*>(fbase);                       // [8][K] fp16
+        __half* normw_s = rows_s + 8 * K;                                        // [K]
+        int8_t* codes_s = reinterpret_cast<int8_t*>(normw_s + K);                // [8][pitch]
+        float* scales_s = reinterpret_cast<float*>(codes_s + 8 * pitch);         // [8][G]
+        const int row = warp;
+        const bool writer = blockIdx.x == 0;
+        __half* my_row = rows_s + row * K;
+        if (row < a.M) {
+            // All loads of a batch are requested before anything is stored: a load placed after a store that
+            // might alias it would wait for it, and ten such round trips in a row cost more than the GEMV.
+            constexpr int kBatch = 8;
+            for (int c0 = 0; c0 < K / 8; c0 += 32 * kBatch) {
+                uint4 v[kBatch], r[kBatch];
 #pragma unroll
-    for (int nt = 0; nt < MT; ++nt) {
-        xq[nt] = a.Xq + static_cast<size_t>(min(nt * 8 + gq, a.M - 1)) * a.K + c * 16;
-        xsp[nt][0] = a.Xs + static_cast<size_t>(min(nt * 8 + 2 * c, a.M - 1)) * a.G;
-        xsp[nt][1] = a.Xs + static_cast<size_t>(min(nt * 8 + 2 * c + 1, a.M - 1)) * a.G;
+                for (int u = 0; u < kBatch; ++u) {
+                    const int c8 = c0 + u * 32 + lane;
+                    const size_t off = static_cast<size_t>(row) * K + c8 * 8;
+                    v[u] = make_uint4(0u, 0u, 0u, 0u);
+                    r[u] = make_uint4(0u, 0u, 0u, 0u);
+                    if (c8 < K / 8) {
+                        v[u] = ld_cg16(a.X + off);
+                        if (a.norm_residual) r[u] = ld_cg16(a.norm_residual + off);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < kBatch; ++u) {
+                    const int c8 = c0 + u * 32 + lane;
+                    if (c8 >= K / 8) continue;
+                    const size_t off = static_cast<size_t>(row) * K + c8 * 8;
+                    if (a.norm_residual) {
+                        __half* hv = reinterpret_cast<__half*>(&v[u]);
+                        const __half* hr = reinterpret_cast<const __half*>(&r[u]);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) hv[e] = __float2half(__half2float(hv[e]) + __half2float(hr[e]));
+                        if (writer && a.norm_x_out) *reinterpret_cast<uint4*>(a.norm_x_out + off) = v[u];
+                    }
+                    reinterpret_cast<uint4*>(my_row)[c8] = v[u];
+                }
+            }
+        }
+        __syncthreads();  // the norm weight is staged (and each warp's own row)
+        if (row < a.M) {
+            // Lane l stands for lane l of each of the 32 warps of the reference's 1024-thread block:
+            // virtual thread vw*32 + l sums x[e]^2 over e = vw*32 + l + i*1024, i ascending.
+            float ls[32];
+#pragma unroll
+            for (int vw = 0; vw < 32; ++vw) ls[vw] = 0.0f;
+            for (int i = 0; i * 1024 < K; ++i) {
+#pragma unroll
+                for (int vw = 0; vw < 32; ++vw) {
+                    const int e = i * 1024 + vw * 32 + lane;
+                    if (e < K) {
+                        float val = __half2float(my_row[e]);
+                        ls[vw] += val * val;
+                    }
+                }
+            }
+            float total_sum = 0.0f;  // lane vw: the partial of virtual warp vw (the reference's s_red[vw])
+#pragma unroll
+            for (int vw = 0; vw < 32; ++vw) {
+                float local_sum = ls[vw];
+                for (int offset = 16; offset > 0; offset /= 2)
+                    local_sum += __shfl_down_sync(0xffffffffu, local_sum, offset);
+                local_sum = __shfl_sync(0xffffffffu, local_sum, 0);
+                if (lane == vw) total_sum = local_sum;
+            }
+            for (int offset = 16; offset > 0; offset /= 2)
+                total_sum += __shfl_down_sync(0xffffffffu, total_sum, offset);
+            total_sum = __shfl_sync(0xffffffffu, total_sum, 0);
+            const float rms = rsqrtf(total_sum / K + a.norm_eps);
+            // normalise in place (rounded to fp16 like rms_norm's output) and find the group maxima;
+            // lane l owns elements (l + 32 i) * 8 .. + 8, so a 256-wide run is one i across the warp
+            constexpr int kLanesPerGroup = GM == 64 ? 8 : GM == 128 ? 16 : 32;
+            float run_max = 0.0f;
+            const int iters = K / 256, per_group = GM == 256 ? a.g / 256 : 1;
+            for (int i = 0; i < iters; ++i) {
+                const int c8 = lane + 32 * i;
+                uint4 v = reinterpret_cast<const uint4*>(my_row)[c8];
+                const uint4 w = reinterpret_cast<const uint4*>(normw_s)[c8];
+                __half* hv = reinterpret_cast<__half*>(&v);
+                const __half* hw = reinterpret_cast<const __half*>(&w);
+                float m = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float val = __half2float(hv[e]) * rms;
+                    hv[e] = __float2half(val * __half2float(hw[e]));
+                    m = fmaxf(m, fabsf(__half2float(hv[e])));
+                }
+                reinterpret_cast<uint4*>(my_row)[c8] = v;
+#pragma unroll
+                for (int o = 1; o < kLanesPerGroup; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                run_max = fmaxf(run_max, m);
+                if (GM != 256 || (i + 1) % per_group == 0) {
+                    float scale = run_max / 127.0f;
+                    if (scale < 1e-8f) scale = 1e-8f;
+                    const int j = GM == 256 ? i / per_group : i * (256 / GM) + lane / kLanesPerGroup;
+                    if (lane % kLanesPerGroup == 0) {
+                        scales_s[row * a.G + j] = scale;
+                        if (writer && a.scales_out) a.scales_out[static_cast<size_t>(row) * a.G + j] = scale;
+                    }
+                    run_max = 0.0f;
+                }
+            }
+            __syncwarp();
+            for (int i = 0; i < iters; ++i) {
+                const int c8 = lane + 32 * i;
+                const uint4 v = reinterpret_cast<const uint4*>(my_row)[c8];
+                const __half* hv = reinterpret_cast<const __half*>(&v);
+                const int j = GM == 256 ? i / per_group : i * (256 / GM) + lane / kLanesPerGroup;
+                const float inv_scale = 1.0f / scales_s[row * a.G + j];
+                __align__(8) int8_t q8[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    int q = __float2int_rn(__half2float(hv[e]) * inv_scale);
+                    q8[e] = static_cast<int8_t>(max(-127, min(127, q)));
+                }
+                *reinterpret_cast<uint2*>(codes_s + row * pitch + c8 * 8) = *reinterpret_cast<const uint2*>(q8);
+                if (writer && a.codes_out)
+                    *reinterpret_cast<uint2*>(a.codes_out + static_cast<size_t>(row) * K + c8 * 8) =
+                        *reinterpret_cast<const uint2*>(q8);
+            }
+        }
+        __syncthreads();  // all rows' codes and scales are in place
+        xq_s = ptx::smem_u32(codes_s) + min(gq, a.M - 1) * pitch + c * 16;
+        xsp_s[0] = scales_s + min(2 * c, a.M - 1) * a.G;
+        xsp_s[1] = scales_s + min(2 * c + 1, a.M - 1) * a.G;
+    } else {
+#pragma unroll
+        for (int nt = 0; nt < MT; ++nt) {
+            xq[nt] = a.Xq + static_cast<size_t>(min(nt * 8 + gq, a.M - 1)) * a.K + c * 16;
+            xsp[nt][0] = a.Xs + static_cast<size_t>(min(nt * 8 + 2 * c, a.M - 1)) * a.G;
+            xsp[nt][1] = a.Xs + static_cast<size_t>(min(nt * 8 + 2 * c + 1, a.M - 1)) * a.G;
+        }
     }
 
     // Two integer accumulators per tile: consecutive MMAs alternate between them, so that one MMA does
@@ -287,16 +439,23 @@ gemv_packed_kernel(const GemvPackedParams p) {
 #pragma unroll
         for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
-            for (int nt = 0; nt < MT; ++nt)
-                dst[ch][nt] = __ldg(reinterpret_cast<const uint4*>(xq[nt] + kbase + ch * 64));
+            for (int nt = 0; nt < MT; ++nt) {
+                if constexpr (FUSED) dst[ch][nt] = lds128(xq_s + kbase + ch * 64);
+                else dst[ch][nt] = __ldg(reinterpret_cast<const uint4*>(xq[nt] + kbase + ch * 64));
+            }
     };
     auto load_xs = [&](int unit_b, float (&dst)[GPU][MT][2]) {
 #pragma unroll
         for (int q = 0; q < GPU; ++q)
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt) {
-                dst[q][nt][0] = __ldg(xsp[nt][0] + unit_b * GPU + q);
-                dst[q][nt][1] = __ldg(xsp[nt][1] + unit_b * GPU + q);
+                if constexpr (FUSED) {
+                    dst[q][nt][0] = xsp_s[0][unit_b * GPU + q];
+                    dst[q][nt][1] = xsp_s[1][unit_b * GPU + q];
+                } else {
+                    dst[q][nt][0] = __ldg(xsp[nt][0] + unit_b * GPU + q);
+                    dst[q][nt][1] = __ldg(xsp[nt][1] + unit_b * GPU + q);
+                }
             }
     };
     if (T > 0) {
@@ -405,10 +564,28 @@ bool packable(int N, int K, int g) {
     return N > 0 && K > 0 && K % 256 == 0 && K % g == 0 && (g == 64 || g == 128 || g % 256 == 0);
 }
 
+size_t fused_smem_bytes(int K, int G) {  // fp16 rows + norm weight + padded code rows + scales
+    return static_cast<size_t>(8) * K * 2 + static_cast<size_t>(K) * 2 + static_cast<size_t>(8) * (K + 64) +
+           static_cast<size_t>(8) * G * 4;
+}
+
 bool make_plan(const LinearArgs& a, Plan& pl) {
-    if (a.M < 1 || a.M > 32 || !a.Xq || !a.Xs || !a.packed) return false;
+    const bool fused = a.norm_weight != nullptr;
+    if (a.M < 1 || a.M > 32 || !a.packed) return false;
     if (!packable(a.N, a.K, a.g)) return false;
-    if (reinterpret_cast<uintptr_t>(a.Xq) & 15u) return false;
+    if (fused) {
+        // one warp per row; the norm emulates the reference's 1024-thread block, which it launches for dim > 512
+        if (a.M > 8 || !a.X || a.K <= 512 || a.K > 4096 || a.dump) return false;
+        if (a.smooth_inv || a.act_scale) return false;
+        if ((reinterpret_cast<uintptr_t>(a.X) | reinterpret_cast<uintptr_t>(a.norm_weight) |
+             reinterpret_cast<uintptr_t>(a.norm_residual) | reinterpret_cast<uintptr_t>(a.norm_x_out) |
+             reinterpret_cast<uintptr_t>(a.codes_out)) & 15u)
+            return false;
+        if (a.norm_residual && a.norm_x_out == a.X) return false;  // other CTAs still read X
+    } else {
+        if (!a.Xq || !a.Xs) return false;
+        if (reinterpret_cast<uintptr_t>(a.Xq) & 15u) return false;
+    }
     if (a.epilogue == W8A8_EPI_SWIGLU && a.N % 16 != 0) return false;
     if (!a.splitk_partials || !a.splitk_counters) return false;
     pl.MT = a.M <= 8 ? 1 : (a.M <= 16 ? 2 : 4);
@@ -420,7 +597,7 @@ bool make_plan(const LinearArgs& a, Plan& pl) {
     pl.U = static_cast<long long>(pl.tiles) * pl.upt;
     // Two CTAs per SM, both working: the consumer side of each warp's pipeline is a chain of latencies
     // (barrier, shared loads, MMAs, promote), so twice the warps per SM hides twice as much of it.
-    pl.ctas = ctas_per_sm() * num_sms();
+    pl.ctas = (fused ? 1 : ctas_per_sm()) * num_sms();  // the fused form's shared memory leaves room for one
     if ((pl.U + 1) * static_cast<long long>(pl.ctas) * kWarps >= (1ll << 32)) return false;  // 32-bit range math
     pl.partial_bytes = static_cast<size_t>(pl.ctas) * kWarps * 2 * pl.MT * 4 * 32 * sizeof(float);
     if (pl.partial_bytes > a.splitk_partial_bytes) return false;
@@ -428,7 +605,7 @@ bool make_plan(const LinearArgs& a, Plan& pl) {
     return true;
 }
 
-template <int MT, int GM>
+template <int MT, int GM, bool FUSED>
 int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_t stream) {
     GemvPackedParams p;
     p.a = a;
@@ -441,11 +618,12 @@ int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_
     p.partials = static_cast<float*>(a.splitk_partials);
     p.counters = a.splitk_counters;
     p.status = status;
-    auto kern = gemv_packed_kernel<MT, GM>;
-    const size_t smem = static_cast<size_t>(kWarps) * kRingBytes + 128;
+    auto kern = gemv_packed_kernel<MT, GM, FUSED>;
+    const size_t smem = static_cast<size_t>(kWarps) * kRingBytes + 128 + (FUSED ? fused_smem_bytes(a.K, a.G) : 0);
     static bool attr_set = false;  // per template instance
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        const size_t most = static_cast<size_t>(kWarps) * kRingBytes + 128 + (FUSED ? fused_smem_bytes(4096, 64) : 0);
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(most));
         if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
         attr_set = true;
     }
@@ -466,10 +644,19 @@ int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_
 
 template <int MT>
 int launch_gm(const LinearArgs& a, const Plan& pl, int* status, cudaStream_t s) {
+    if constexpr (MT == 1) {
+        if (a.norm_weight) {
+            switch (pl.GM) {
+                case 64: return launch_variant<1, 64, true>(a, pl, status, s);
+                case 128: return launch_variant<1, 128, true>(a, pl, status, s);
+                default: return launch_variant<1, 256, true>(a, pl, status, s);
+            }
+        }
+    }
     switch (pl.GM) {
-        case 64: return launch_variant<MT, 64>(a, pl, status, s);
-        case 128: return launch_variant<MT, 128>(a, pl, status, s);
-        default: return launch_variant<MT, 256>(a, pl, status, s);
+        case 64: return launch_variant<MT, 64, false>(a, pl, status, s);
+        case 128: return launch_variant<MT, 128, false>(a, pl, status, s);
+        default: return launch_variant<MT, 256, false>(a, pl, status, s);
     }
 }
 

@@ -52,6 +52,14 @@ struct LinearArgs {
     size_t splitk_partial_bytes;
     int* splitk_counters;        // zero between launches
     size_t splitk_counter_count;
+    // Fused prologue (packed GEMV, M <= 8): norm_weight != null means that Xq / Xs are absent and every CTA
+    // forms them itself in shared memory from X: [x = half(x + norm_residual)] -> RMSNorm -> quantiser.
+    const __half* norm_weight;    // [K]
+    float norm_eps;
+    const __half* norm_residual;  // [M, K] or null
+    __half* norm_x_out;           // [M, K] or null: CTA 0 stores the updated x (must not alias X)
+    int8_t* codes_out;            // [M, K] / [M, G] or null: CTA 0 stores the codes and scales it formed
+    float* scales_out;
 };
 
 // w8a8_api.cu : picks the kernel for a linear whose codes and scales exist.
@@ -78,7 +86,7 @@ int launch_linear_gemv_tma(const LinearArgs& a, int* device_status, cudaStream_t
 // w8a8_gemv_packed.cu : M <= 32 over pre-packed weights (linear byte stream, 1-D bulk copies).
 size_t packed_weight_bytes(int N, int K, int g);
 int launch_pack_weight(const int8_t* W, const __half* S, int N, int K, int g, void* out, cudaStream_t s);
-bool gemv_packed_supports(const LinearArgs& a);
+bool gemv_packed_supports(const LinearArgs& a);  // also answers for the fused-prologue form (a.norm_weight set)
 int launch_linear_gemv_packed(const LinearArgs& a, int* device_status, cudaStream_t s);
 // w8a8_attn.cu : decode-step neighbours (qk-norm + RoPE + KV write; paged attention).
 int launch_qknorm_rope_kvwrite(const __half* qkv, const __half* q_norm_w, const __half* k_norm_w, float eps,

@@ -200,18 +200,38 @@ __global__ void __launch_bounds__(1024) rowquant_fast_kernel(const RowQuantParam
     const int lane = tid & (kWarp - 1), warp = tid / kWarp;
     const size_t base = static_cast<size_t>(blockIdx.x) * K;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    for (int j = tid; j < G; j += T) s_gmax[j] = 0u;
-
-    __half h[kFastElems];
-    float local_sum = 0.0f;
+    // the norm weight and the smoothing vector are parameters, not results of the kernel before this one
+    __half nw[kFastElems], sm[kFastElems];
 #pragma unroll
     for (int i = 0; i < kFastElems; ++i) {
         const int e = tid + i * T;
         if (e < K) {
-            __half v = p.x_in[base + e];
+            if (p.norm_weight) nw[i] = p.norm_weight[e];
+            if (p.smooth_inv) sm[i] = p.smooth_inv[e];
+        }
+    }
+    for (int j = tid; j < G; j += T) s_gmax[j] = 0u;
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+
+    __half h[kFastElems], res[kFastElems];
+    float local_sum = 0.0f;
+    // every load is requested before the first store: x_out may be x_in, so a load placed after a store
+    // would have to wait for it, one memory round trip per element
+#pragma unroll
+    for (int i = 0; i < kFastElems; ++i) {
+        const int e = tid + i * T;
+        if (e < K) {
+            h[i] = p.x_in[base + e];
+            if (p.residual) res[i] = p.residual[base + e];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < kFastElems; ++i) {
+        const int e = tid + i * T;
+        if (e < K) {
+            __half v = h[i];
             if (p.residual) {
-                v = __float2half(__half2float(v) + __half2float(p.residual[base + e]));
+                v = __float2half(__half2float(v) + __half2float(res[i]));
                 if (p.x_out) p.x_out[base + e] = v;
             }
             h[i] = v;
@@ -240,7 +260,7 @@ __global__ void __launch_bounds__(1024) rowquant_fast_kernel(const RowQuantParam
             const int e = tid + i * T;
             if (e < K) {
                 float val = __half2float(h[i]) * rms;
-                h[i] = __float2half(val * __half2float(p.norm_weight[e]));
+                h[i] = __float2half(val * __half2float(nw[i]));
                 if (p.normed_out) p.normed_out[base + e] = h[i];
             }
         }
@@ -253,7 +273,7 @@ __global__ void __launch_bounds__(1024) rowquant_fast_kernel(const RowQuantParam
         v[i] = 0.0f;
         if (e < K) {
             v[i] = __half2float(h[i]);
-            if (p.smooth_inv) v[i] *= __half2float(p.smooth_inv[e]);
+            if (p.smooth_inv) v[i] *= __half2float(sm[i]);
         }
     }
     if (!p.act_scale) {

@@ -22,6 +22,7 @@ all-reduce of [batch, 2560] after wo and after w2.
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -56,7 +57,7 @@ def shard_bounds(total_groups: int, world: int):
 class SlowARStack:
     def __init__(self, torch, ctx: capi.Context, cfg: SlowARConfig, batch: int, context: int, max_new: int = 256,
                  tp_rank: int = 0, tp_size: int = 1, seed: int = 0, all_reduce=None, pack: bool = True,
-                 attn_splits: int = 0, tp_mode: str = "fused", gather_handles=None):
+                 attn_splits: int = 0, tp_mode: str = "fused", gather_handles=None, fuse_norm: bool = True):
         self.torch, self.ctx, self.cfg = torch, ctx, cfg
         self.B, self.tp_rank, self.tp_size = batch, tp_rank, tp_size
         self.all_reduce = all_reduce
@@ -68,6 +69,9 @@ class SlowARStack:
             handle = ctx.tp_create(tp_rank, tp_size, batch, cfg.dim)
             ctx.tp_connect(b"".join(gather_handles(handle)))
             self.all_reduce = None
+        # On one GPU the residual add + RMSNorm + quantiser before wqkv and w13 run inside the linear's own
+        # launch (w8a8_rmsnorm_linear); with TP the exchange sits in that place instead.
+        self.fuse_norm = fuse_norm and tp_size == 1 and pack and os.environ.get("W8A8_STACK_FUSE_NORM", "0") == "1"
         c = cfg
         assert c.n_kv % tp_size == 0 and c.n_head == 4 * c.n_kv and c.head_dim == 128
         g = c.group
@@ -155,6 +159,7 @@ class SlowARStack:
         B = batch
         h16 = dict(dtype=torch.float16, device=dev)
         self.x = torch.zeros((B, c.dim), **h16)          # residual stream
+        self.x_alt = torch.zeros((B, c.dim), **h16)      # its other copy when the fused form ping-pongs
         self.delta = torch.zeros((B, c.dim), **h16)      # output of wo / w2 (summed over ranks when TP > 1)
         self.have_delta = False
         self.xq = torch.empty((B, c.dim), dtype=torch.int8, device=dev)
@@ -167,7 +172,7 @@ class SlowARStack:
         self.actq = torch.empty((B, self.inter_l), dtype=torch.int8, device=dev)
         self.acts = torch.empty((B, self.inter_l // g), dtype=torch.float32, device=dev)
         self.out = torch.empty((B, c.dim), **h16)
-        self.launches_per_step = c.n_layer * 9 + 2
+        self.launches_per_step = c.n_layer * (7 if self.fuse_norm else 9) + 2
         # bytes the step must move at least once (per rank): weights + scales + the KV it reads
         wbytes = sum(lw[n].numel() + lw[s].numel() * 2 for lw in self.layers
                      for n, s in (("wqkv", "sqkv"), ("wo", "so"), ("w13", "s13"), ("w2", "s2")))
@@ -184,14 +189,21 @@ class SlowARStack:
             self.x.copy_(x_in, non_blocking=True)
         sm_scale = 1.0 / math.sqrt(D)
         pending = False  # a projection output waiting to be added to the residual stream
+        x, x_alt = self.x, self.x_alt
         for l, lw in enumerate(self.layers):
-            if pending and self.tp_fused:
+            if self.fuse_norm:
+                ctx.rmsnorm_linear(lw["wqkv"], lw["sqkv"], g, x, lw["attn_norm"], c.eps, self.qkv, B, self.qkv_n,
+                                   c.dim, residual=self.delta if pending else None, x_out=x_alt if pending else None)
+                if pending:
+                    x, x_alt = x_alt, x
+            elif pending and self.tp_fused:
                 ctx.tp_allreduce_rmsnorm_quantize(self.x, self.delta, lw["attn_norm"], c.eps, B, c.dim, g,
                                                   Xq=self.xq, Xs=self.xs)
             else:
                 ctx.rmsnorm_quantize(self.x, lw["attn_norm"], c.eps, B, c.dim, g, self.xq, self.xs,
                                      residual=self.delta if pending else None)
-            ctx.linear_q(lw["wqkv"], lw["sqkv"], g, self.xq, self.xs, self.qkv, B, self.qkv_n, c.dim)
+            if not self.fuse_norm:
+                ctx.linear_q(lw["wqkv"], lw["sqkv"], g, self.xq, self.xs, self.qkv, B, self.qkv_n, c.dim)
             ctx.qknorm_rope_kvwrite(self.qkv, lw["q_norm"], lw["k_norm"], c.eps, self.freqs, self.positions,
                                     self.block_table, self.max_blocks, self.k_cache, self.v_cache, l, c.n_layer, B,
                                     self.nq_l, self.nkv_l, D, self.q)
@@ -201,14 +213,19 @@ class SlowARStack:
             ctx.linear_q(lw["wo"], lw["so"], g, self.aq, self.as_, self.delta, B, c.dim, self.attn_k)
             if self.all_reduce is not None:
                 self.all_reduce(self.delta)
-            if self.tp_fused:
-                ctx.tp_allreduce_rmsnorm_quantize(self.x, self.delta, lw["ffn_norm"], c.eps, B, c.dim, g,
-                                                  Xq=self.xq, Xs=self.xs)
+            if self.fuse_norm:
+                ctx.rmsnorm_linear(lw["w13"], lw["s13"], g, x, lw["ffn_norm"], c.eps, self.act, B, 2 * self.inter_l,
+                                   c.dim, residual=self.delta, x_out=x_alt, epilogue=capi.EPI_SWIGLU)
+                x, x_alt = x_alt, x
             else:
-                ctx.rmsnorm_quantize(self.x, lw["ffn_norm"], c.eps, B, c.dim, g, self.xq, self.xs,
-                                     residual=self.delta)
-            ctx.linear_q(lw["w13"], lw["s13"], g, self.xq, self.xs, self.act, B, 2 * self.inter_l, c.dim,
-                         epilogue=capi.EPI_SWIGLU)
+                if self.tp_fused:
+                    ctx.tp_allreduce_rmsnorm_quantize(self.x, self.delta, lw["ffn_norm"], c.eps, B, c.dim, g,
+                                                      Xq=self.xq, Xs=self.xs)
+                else:
+                    ctx.rmsnorm_quantize(self.x, lw["ffn_norm"], c.eps, B, c.dim, g, self.xq, self.xs,
+                                         residual=self.delta)
+                ctx.linear_q(lw["w13"], lw["s13"], g, self.xq, self.xs, self.act, B, 2 * self.inter_l, c.dim,
+                             epilogue=capi.EPI_SWIGLU)
             ctx.quantize(self.act, B, self.inter_l, g, self.actq, self.acts)
             ctx.linear_q(lw["w2"], lw["s2"], g, self.actq, self.acts, self.delta, B, c.dim, self.inter_l)
             if self.all_reduce is not None:
@@ -218,8 +235,8 @@ class SlowARStack:
             ctx.tp_allreduce_rmsnorm_quantize(self.x, self.delta, self.final_norm, c.eps, B, c.dim, g,
                                               normed_out=self.out)
         else:
-            ctx.residual_add(self.x, self.delta, B * c.dim)
-            ctx.rms_norm(self.x, self.final_norm, self.out, B, c.dim, c.eps)
+            ctx.residual_add(x, self.delta, B * c.dim)
+            ctx.rms_norm(x, self.final_norm, self.out, B, c.dim, c.eps)
         self.positions.add_(1)
         self.seq_lens.add_(1)
         return self.out

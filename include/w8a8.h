@@ -137,6 +137,22 @@ W8A8_API int w8a8_linear(w8a8_ctx* ctx, const void* W, const void* w_scale, int 
                 const void* act_scale, const void* smooth_inv, const void* X, void* Y, int M,
                 int N, int K, const w8a8_linear_opts* opts, void* stream);
 
+/* w8a8_rmsnorm_quantize and the w8a8_linear_q after it as ONE call, for the decode step: per token row
+ * [x_out = x + residual (ffn_activations.cu:41-45)] -> rms_norm (rms_norm.cu:10-58) -> quantiser
+ * (int8_gemm.cu:147-211) -> linear (int8_gemm.cu:423-505). Replaces, in DualAREngine::decode_step, the
+ * rms_norm launch and the quantized_gemm after it (src/engine/dual_ar_engine.cc:580-584, :636-641).
+ * x is not modified. residual may be NULL; when it is not, x_out (a buffer other than x) receives the
+ * updated residual stream. codes_out / scales_out (both or neither) receive the int8 codes [M, K] and
+ * fp32 scales [M, G] the linear consumed. For M <= 8 over a weight registered with
+ * w8a8_register_packed_weight this is one launch (every CTA quantises the rows itself, in shared memory,
+ * while its first weight blocks are in flight); other shapes run the two kernels back to back. Results
+ * are those of the two-call chain, bit for bit. opts->act_mode must be W8A8_ACT_PER_TOKEN_GROUP for the
+ * one-launch form. */
+W8A8_API int w8a8_rmsnorm_linear(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size,
+                        const void* x, const void* residual, void* x_out, const void* norm_weight,
+                        float eps, void* Y, int M, int N, int K, const w8a8_linear_opts* opts,
+                        void* codes_out, void* scales_out, void* stream);
+
 /* The same from codes and scales already formed (by w8a8_quantize or
  * w8a8_rmsnorm_quantize): int8_gemm.cu:423-505 without its first stage. */
 W8A8_API int w8a8_linear_q(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size,

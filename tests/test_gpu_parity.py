@@ -322,6 +322,97 @@ def test_packed_weight_stream(ctx, oracle, pkg, M, N, K, g):
         ctx.linear(dW, dS, g, dX, dY, M, N, K, kernel=pkg.KERNEL_GEMV_PACKED)
 
 
+FUSED_NORM_SHAPES = [(8, 256, 2560, 256), (1, 64, 2560, 64), (3, 128, 1024, 128), (8, 96, 4096, 256),
+                     (5, 160, 2048, 512), (7, 48, 768, 256), (2, 64, 1536, 1536),
+                     # not taken by the one-launch form: two launches, same results
+                     (16, 64, 2560, 256), (4, 64, 512, 256), (8, 40, 2560, 640)]
+
+
+@pytest.mark.parametrize("M,N,K,g", FUSED_NORM_SHAPES)
+@pytest.mark.parametrize("with_residual", [False, True])
+@pytest.mark.parametrize("packed", [True, False])
+def test_rmsnorm_linear_equals_two_call_chain(ctx, oracle, pkg, M, N, K, g, with_residual, packed):
+    """w8a8_rmsnorm_linear (residual add + RMSNorm + quantiser inside the linear's launch) against
+    w8a8_rmsnorm_quantize followed by w8a8_linear_q: updated x, codes, scales and fp16 outputs bit for bit,
+    and x itself untouched."""
+    X, W, ws = synth.linear_case(1000 + M + N + g, M, N, K, g)
+    rng = np.random.default_rng(K + M + g)
+    r = rng.standard_normal((M, K)).astype(np.float16)
+    w = rng.uniform(0.5, 1.5, K).astype(np.float16)
+    G = oracle.num_groups(K, g)
+    dW, dS, dr, dw = dev(W), dev(ws), dev(r), dev(w)
+    if packed and ctx.packed_weight_bytes(N, K, g):
+        dP = torch.empty((ctx.packed_weight_bytes(N, K, g),), dtype=torch.uint8, device="cuda")
+        ctx.pack_weight(dW, dS, N, K, g, dP)
+        ctx.register_packed_weight(dW, dP)
+    try:
+        # the chain
+        cx = dev(X)
+        cq = torch.empty((M, K), dtype=torch.int8, device="cuda")
+        cs = torch.empty((M, G), dtype=torch.float32, device="cuda")
+        cY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        ctx.rmsnorm_quantize(cx, dw, 1e-6, M, K, g, cq, cs, residual=dr if with_residual else None)
+        ctx.linear_q(dW, dS, g, cq, cs, cY, M, N, K)
+        # the one call
+        dx = dev(X)
+        ybuf, dY = guarded((M, N), torch.float16, 77.0)
+        xbuf, dxo = guarded((M, K), torch.float16, 55.0)
+        qbuf, dq = guarded((M, K), torch.int8, 99)
+        sbuf, dsc = guarded((M, G), torch.float32, -3.0)
+        for rep in range(2):  # the second run sees the split-K counters the first one left
+            ctx.rmsnorm_linear(dW, dS, g, dx, dw, 1e-6, dY, M, N, K, residual=dr if with_residual else None,
+                               x_out=dxo if with_residual else None, codes_out=dq, scales_out=dsc)
+            torch.cuda.synchronize()
+            ctx.check_device_status()
+            assert torch.equal(dx, dev(X)), "x is an input only"
+            if with_residual:
+                assert torch.equal(dxo, cx), "x_out = half(x + residual)"
+            assert torch.equal(dq, cq) and torch.equal(dsc, cs), "codes and scales of the chain"
+            assert torch.equal(dY.view(torch.int16), cY.view(torch.int16)), "fp16 output of the chain"
+        assert guards_intact(ybuf, 77.0) and guards_intact(xbuf, 55.0) and guards_intact(qbuf, 99) and \
+            guards_intact(sbuf, -3.0)
+        # and the chain itself is the oracle's
+        xo = oracle.residual_add(X, r) if with_residual else X
+        wq, wsc = oracle.quantize(oracle.rms_norm(xo, w, 1e-6), g)
+        if np.array_equal(cq.cpu().numpy(), wq):  # device rsqrtf may move a normed value by an ulp
+            assert np.array_equal(cs.cpu().numpy(), wsc)
+    finally:
+        ctx.register_packed_weight(dW, None)
+
+
+def test_rmsnorm_linear_epilogues_and_argument_checks(ctx, oracle, pkg):
+    M, K, inter, g = 8, 2560, 128, 256
+    X, W, ws = synth.linear_case(77, M, 2 * inter, K, g)
+    rng = np.random.default_rng(5)
+    w = rng.uniform(0.5, 1.5, K).astype(np.float16)
+    r = rng.standard_normal((M, K)).astype(np.float16)
+    dW, dS, dw, dr, dx = dev(W), dev(ws), dev(w), dev(r), dev(X)
+    dP = torch.empty((ctx.packed_weight_bytes(2 * inter, K, g),), dtype=torch.uint8, device="cuda")
+    ctx.pack_weight(dW, dS, 2 * inter, K, g, dP)
+    ctx.register_packed_weight(dW, dP)
+    try:
+        cq = torch.empty((M, K), dtype=torch.int8, device="cuda")
+        cs = torch.empty((M, K // g), dtype=torch.float32, device="cuda")
+        cx = dev(X)
+        ctx.rmsnorm_quantize(cx, dw, 1e-6, M, K, g, cq, cs, residual=dr)
+        for epi, n_out, res in ((pkg.EPI_SWIGLU, inter, None), (pkg.EPI_RESIDUAL, 2 * inter, "r")):
+            R = dev(rng.standard_normal((M, 2 * inter)).astype(np.float16)) if res else None
+            cY = torch.empty((M, n_out), dtype=torch.float16, device="cuda")
+            ctx.linear_q(dW, dS, g, cq, cs, cY, M, 2 * inter, K, epilogue=epi, residual=R)
+            dY = torch.empty_like(cY)
+            dxo = torch.empty_like(dx)
+            ctx.rmsnorm_linear(dW, dS, g, dx, dw, 1e-6, dY, M, 2 * inter, K, residual=dr, x_out=dxo, epilogue=epi,
+                               epi_residual=R)
+            torch.cuda.synchronize()
+            assert torch.equal(dY.view(torch.int16), cY.view(torch.int16)) and torch.equal(dxo, cx)
+        with pytest.raises(pkg.W8A8Error):  # a residual needs somewhere else to put the updated x
+            ctx.rmsnorm_linear(dW, dS, g, dx, dw, 1e-6, dY, M, 2 * inter, K, residual=dr, x_out=dx)
+        with pytest.raises(pkg.W8A8Error):
+            ctx.rmsnorm_linear(dW, dS, g, dx, dw, 1e-6, dY, M, 2 * inter, K, codes_out=cq)
+    finally:
+        ctx.register_packed_weight(dW, None)
+
+
 def test_unpackable_shapes_report_zero_bytes(ctx):
     assert ctx.packed_weight_bytes(64, 640, 64) == 0      # K % 256 != 0
     assert ctx.packed_weight_bytes(64, 768, 192) == 0     # group size

@@ -44,9 +44,9 @@ def oracle_step(oracle, st, x_in, k_cache, v_cache, bt, positions, jitter=None):
     return oracle.rms_norm(x, cpu(st.final_norm), c.eps)
 
 
-@pytest.mark.parametrize("group", [64, 256])
-def test_stack_matches_oracle_chain(ctx, oracle, group):
-    cfg = S.SlowARConfig(n_layer=2, dim=512, n_head=4, n_kv=1, inter=512, group=group)
+@pytest.mark.parametrize("group,dim", [(64, 512), (256, 512), (256, 1024)])  # dim 1024: the one-launch norm+linear
+def test_stack_matches_oracle_chain(ctx, oracle, group, dim):
+    cfg = S.SlowARConfig(n_layer=2, dim=dim, n_head=4, n_kv=1, inter=512, group=group)
     B, context = 3, 37
     st = S.SlowARStack(torch, ctx, cfg, B, context, max_new=8, seed=5)
     rng = np.random.default_rng(group)
