@@ -368,6 +368,7 @@ class DecodeStack:
         self.graphs = {}
         self.eager = False
         self.split_k = 0
+        self.one_launch = False
         self.launches_per_step = self.st.launches_per_step
         self.h2d = self.host_x.numel() * 2
         self.d2h = self.host_out.numel() * 2
@@ -380,7 +381,10 @@ class DecodeStack:
     def body(self, e2e):
         if e2e:
             self.dev_x.copy_(self.host_x, non_blocking=True)
-        self.st.decode_step(self.dev_x)
+        if self.one_launch:
+            self.st.decode_step_one_launch(self.dev_x)
+        else:
+            self.st.decode_step(self.dev_x)
         if e2e:
             self.host_out.copy_(self.st.out, non_blocking=True)
 
@@ -576,6 +580,9 @@ def main():
     ap.add_argument("--split-k", type=int, default=0, help="force the GEMV's K-slice count (tuning aid)")
     ap.add_argument("--no-pack", action="store_true", help="leave weights row-major (skip the loader-side pack)")
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a graph")
+    ap.add_argument("--step-form", choices=["one-launch", "chain"], default="chain",
+                    help="decode_stack on one GPU: the whole step as one persistent kernel (w8a8_decode_stack_step) "
+                         "or as nine launches per layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -635,6 +642,10 @@ def main():
             wl = DecodeSweep(torch, ctx, pack=not args.no_pack)
 
     wl.eager = args.eager
+    if args.workload == "decode_stack" and not reference and world == 1:
+        wl.one_launch = args.step_form == "one-launch"
+        if wl.one_launch:
+            wl.launches_per_step = 1
     wl.split_k = args.split_k
 
     def barrier():

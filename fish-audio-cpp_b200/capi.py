@@ -28,6 +28,19 @@ class LinearOpts(C.Structure):
     ]
 
 
+class DecodeStack(C.Structure):
+    """w8a8_decode_stack of include/w8a8.h."""
+    _fields_ = [("n_layers", C.c_int), ("batch", C.c_int), ("dim", C.c_int), ("n_q_heads", C.c_int),
+                ("n_kv_heads", C.c_int), ("head_dim", C.c_int), ("inter", C.c_int), ("group_size", C.c_int),
+                ("eps", C.c_float), ("sm_scale", C.c_float), ("layers", C.c_void_p), ("final_norm", C.c_void_p),
+                ("rope_freqs", C.c_void_p), ("positions", C.c_void_p), ("seq_lens", C.c_void_p),
+                ("block_table", C.c_void_p), ("max_blocks_per_seq", C.c_int), ("k_cache", C.c_void_p),
+                ("v_cache", C.c_void_p), ("x", C.c_void_p), ("out", C.c_void_p)]
+
+
+DECODE_LAYER_POINTERS = 8  # w8a8_decode_layer: attn_norm, ffn_norm, q_norm, k_norm, packed[4]
+
+
 def library_path() -> Path:
     return Path(__file__).resolve().parent / "lib" / "libw8a8.so"
 
@@ -60,6 +73,9 @@ def load_library() -> C.CDLL:
         "w8a8_linear_q": (I, [P, P, P, I, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_rmsnorm_linear": (I, [P, P, P, I, P, P, P, P, F, P, I, I, I, C.POINTER(LinearOpts), P, P, P]),
         "w8a8_pack_gate_up": (I, [P, P, P, P, P, I, I, I, P, P, P]),
+        "w8a8_decode_stack_workspace_bytes": (Z, [C.POINTER(DecodeStack)]),
+        "w8a8_decode_stack_step": (I, [P, C.POINTER(DecodeStack), P]),
+        "w8a8_decode_stack_timeline": (I, [P, C.POINTER(DecodeStack), P, I, P]),
         "w8a8_qknorm_rope_kvwrite": (I, [P, P, P, P, F, P, P, P, I, P, P, I, I, I, I, I, I, P, P]),
         "w8a8_paged_attention_decode": (I, [P, P, P, P, P, P, P, I, I, I, I, F, I, I, I, I, P, P, I, P]),
         "w8a8_tp_create": (I, [P, I, I, I, I, P]),
@@ -83,7 +99,8 @@ EXPORTS = [
     "w8a8_status_string", "w8a8_last_error", "w8a8_create", "w8a8_destroy", "w8a8_workspace_bytes",
     "w8a8_ctx_workspace_bytes", "w8a8_check_device_status", "w8a8_quantize", "w8a8_rms_norm",
     "w8a8_rmsnorm_quantize", "w8a8_silu", "w8a8_mul", "w8a8_residual_add", "w8a8_linear", "w8a8_linear_q",
-    "w8a8_rmsnorm_linear",
+    "w8a8_rmsnorm_linear", "w8a8_decode_stack_workspace_bytes", "w8a8_decode_stack_step",
+    "w8a8_decode_stack_timeline",
     "w8a8_pack_gate_up", "w8a8_qknorm_rope_kvwrite", "w8a8_paged_attention_decode", "w8a8_tp_create", "w8a8_tp_connect",
     "w8a8_tp_allreduce_rmsnorm_quantize", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
     "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch",
@@ -216,6 +233,22 @@ class Context:
                                                  self._opts(act_mode, epilogue, epi_residual, None, kernel, 0),
                                                  _ptr(codes_out), _ptr(scales_out), _stream(stream)),
                     "w8a8_rmsnorm_linear")
+
+    def decode_stack_workspace_bytes(self, desc: DecodeStack) -> int:
+        return self.lib.w8a8_decode_stack_workspace_bytes(C.byref(desc))
+
+    def decode_stack_step(self, desc: DecodeStack, stream=None):
+        self._check(self.lib.w8a8_decode_stack_step(self.handle, C.byref(desc), _stream(stream)),
+                    "w8a8_decode_stack_step")
+
+    def decode_stack_timeline(self, desc: DecodeStack, stream=None):
+        """Nanosecond stamps of the last one-launch step: start, then (phase end, barrier end) x 9 per layer, end."""
+        n = 18 * desc.n_layers + 2
+        buf = (C.c_ulonglong * n)()
+        got = self.lib.w8a8_decode_stack_timeline(self.handle, C.byref(desc), buf, n, _stream(stream))
+        if got < 0:
+            raise W8A8Error(-got, "w8a8_decode_stack_timeline", self.lib.w8a8_last_error().decode())
+        return list(buf)[:got]
 
     def pack_gate_up(self, w_gate, s_gate, w_up, s_up, inter, K, G, W_out, scale_out, stream=None):
         self._check(self.lib.w8a8_pack_gate_up(self.handle, _ptr(w_gate), _ptr(s_gate), _ptr(w_up), _ptr(s_up),

@@ -403,6 +403,24 @@ int w8a8_paged_attention_decode(w8a8_ctx* ctx, const void* q, const void* k_cach
                                          static_cast<float*>(Xs), context_splits, static_cast<cudaStream_t>(stream));
 }
 
+size_t w8a8_decode_stack_workspace_bytes(const w8a8_decode_stack* stack) {
+    return stack ? decode_stack_workspace_bytes(*stack) : 0;
+}
+
+int w8a8_decode_stack_step(w8a8_ctx* ctx, const w8a8_decode_stack* stack, void* stream) {
+    if (!ctx || !stack) return fail(W8A8_ERR_INVALID_ARG, "null context or stack descriptor");
+    return launch_decode_stack(*stack, ctx->workspace, ctx->workspace_bytes, static_cast<float*>(ctx->splitk_partials),
+                               kSplitkPartialBytes, ctx->splitk_counters, kSplitkCounters, ctx->device_status,
+                               static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_decode_stack_timeline(w8a8_ctx* ctx, const w8a8_decode_stack* stack, unsigned long long* stamps_out,
+                               int capacity, void* stream) {
+    if (!ctx || !stack || !stamps_out) return -fail(W8A8_ERR_INVALID_ARG, "null argument");
+    const int n = decode_stack_timeline(*stack, ctx->workspace, stamps_out, capacity, static_cast<cudaStream_t>(stream));
+    return n;
+}
+
 int w8a8_tp_create(w8a8_ctx* ctx, int rank, int world, int max_tokens, int dim, void* ipc_handle_out) {
     if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
     if (ctx->tp) return fail(W8A8_ERR_INVALID_ARG, "this context already has a tensor-parallel exchange");

@@ -36,6 +36,7 @@ constexpr int kStages = 3;
 constexpr int kBlockW = 16 * 256;        // weight bytes of a block
 constexpr int kStagePitch = kBlockW + 128;  // room for the largest scale tail, keeps stages 128-byte aligned
 constexpr int kRingBytes = kStages * kStagePitch;
+constexpr int kLocalTiles = 128;  // row tiles per CTA whose arrival counters live in shared memory
 
 struct GemvPackedParams {
     LinearArgs a;
@@ -91,7 +92,7 @@ __device__ __forceinline__ float ld_cg(const float* p) {
 // (int8_gemm.cu:147-211). One warp per token row, so M <= 8. This replaces a separate launch of a kernel
 // that runs on M CTAs and leaves the rest of the GPU idle.
 template <int MT, int GM, bool FUSED>
-__global__ void __launch_bounds__(kThreads, (MT == 4 || FUSED) ? 1 : 2)
+__global__ void __launch_bounds__(kThreads, 1)
 gemv_packed_kernel(const GemvPackedParams p) {
     static_assert(!FUSED || MT == 1, "the fused prologue handles one row per warp");
     extern __shared__ unsigned char smem_raw[];
@@ -101,8 +102,13 @@ gemv_packed_kernel(const GemvPackedParams p) {
     const int gq = lane >> 2, c = lane & 3;
     constexpr int GPU = GM == 64 ? 4 : GM == 128 ? 2 : 1;  // groups per unit
 
-    // ---- this warp's contiguous range of units; consecutive ranges sit on different SMs ----
-    const unsigned gw = warp * gridDim.x + blockIdx.x;
+    // ---- this warp's contiguous range of units; the eight ranges of a CTA are neighbours, so that most row
+    // tiles cut by a range boundary are cut between warps of ONE CTA and can be added up in shared memory ----
+    __shared__ float red_s[kWarps][2][MT * 4 * 32];
+    __shared__ int cnt_s[kLocalTiles];
+    for (int i = threadIdx.x; i < kLocalTiles; i += kThreads) cnt_s[i] = 0;
+    __syncthreads();
+    const unsigned gw = blockIdx.x * kWarps + warp;
     const unsigned NW = p.NW, U = p.U;
     const unsigned u0 = gw * U / NW, u1 = (gw + 1) * U / NW;
     const int T = gw < NW ? static_cast<int>(u1 - u0) * p.bpu : 0;  // blocks
@@ -336,6 +342,7 @@ gemv_packed_kernel(const GemvPackedParams p) {
     // at after the last block: whichever contributor arrived last adds all partials in ascending-K
     // order and stores. A warp has at most two such tiles (the first and the last of its range).
     constexpr int kSlot = MT * 4 * 32;
+    const int cta_rt0 = static_cast<int>((blockIdx.x * kWarps * U / NW) / p.upt);  // the CTA's first row tile
     int pend_rt[2];
     unsigned pend_old[2];
     int npend = 0;
@@ -345,6 +352,39 @@ gemv_packed_kernel(const GemvPackedParams p) {
         const unsigned t_lo = static_cast<unsigned>(rt) * p.upt, t_hi = t_lo + p.upt;  // [t_lo, t_hi)
         if (u0 <= t_lo && t_hi <= u1) {
             store_tile(rt, acc);
+        } else if (const unsigned first = warp_of_unit(t_lo), last = warp_of_unit(t_hi - 1);
+                   first / kWarps == last / kWarps && rt - cta_rt0 < kLocalTiles) {
+            // every contributor is a warp of this CTA: partials and the arrival counter in shared memory
+            const int my_slot = (static_cast<int>(u0 / p.upt) == rt) ? 0 : 1;
+            float* mine = red_s[warp][my_slot];
+#pragma unroll
+            for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                for (int r = 0; r < 4; ++r) mine[(nt * 4 + r) * 32 + lane] = acc[nt][r];
+            __syncwarp();
+            int old = 0;
+            if (lane == 0) {
+                __threadfence_block();
+                old = atomicAdd(&cnt_s[rt - cta_rt0], 1);
+            }
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old == static_cast<int>(last - first)) {  // the last to arrive adds in ascending-K order
+                __threadfence_block();
+                float sum[MT][4];
+#pragma unroll
+                for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) sum[nt][r] = 0.0f;
+                for (unsigned ww = first; ww <= last; ++ww) {
+                    const int slot = (static_cast<int>((ww * U / NW) / p.upt) == rt) ? 0 : 1;
+                    const float* src = red_s[ww - blockIdx.x * kWarps][slot];
+#pragma unroll
+                    for (int nt = 0; nt < MT; ++nt)
+#pragma unroll
+                        for (int r = 0; r < 4; ++r) sum[nt][r] += src[(nt * 4 + r) * 32 + lane];
+                }
+                store_tile(rt, sum);
+            }
         } else {
             const int my_slot = (static_cast<int>(u0 / p.upt) == rt) ? 0 : 1;
             float* mine = p.partials + (static_cast<size_t>(gw) * 2 + my_slot) * kSlot;
@@ -551,15 +591,6 @@ int num_sms() {
     return n;
 }
 
-int ctas_per_sm() {
-    static int n = [] {
-        const char* v = std::getenv("W8A8_GEMV_CTAS_PER_SM");
-        int k = v ? std::atoi(v) : 2;
-        return k < 1 ? 1 : (k > 2 ? 2 : k);
-    }();
-    return n;
-}
-
 bool packable(int N, int K, int g) {
     return N > 0 && K > 0 && K % 256 == 0 && K % g == 0 && (g == 64 || g == 128 || g % 256 == 0);
 }
@@ -595,9 +626,9 @@ bool make_plan(const LinearArgs& a, Plan& pl) {
     pl.block_bytes = kBlockW + 32 * (a.g >= 256 ? 1 : 256 / a.g);
     pl.tiles = (a.N + 15) / 16;
     pl.U = static_cast<long long>(pl.tiles) * pl.upt;
-    // Two CTAs per SM, both working: the consumer side of each warp's pipeline is a chain of latencies
-    // (barrier, shared loads, MMAs, promote), so twice the warps per SM hides twice as much of it.
-    pl.ctas = (fused ? 1 : ctas_per_sm()) * num_sms();  // the fused form's shared memory leaves room for one
+    // One CTA per SM (two were measured no faster). The warp ranges are then those of the one-launch decode
+    // step, whose results are the same bit for bit.
+    pl.ctas = num_sms();
     if ((pl.U + 1) * static_cast<long long>(pl.ctas) * kWarps >= (1ll << 32)) return false;  // 32-bit range math
     pl.partial_bytes = static_cast<size_t>(pl.ctas) * kWarps * 2 * pl.MT * 4 * 32 * sizeof(float);
     if (pl.partial_bytes > a.splitk_partial_bytes) return false;

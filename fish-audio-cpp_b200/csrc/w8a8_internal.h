@@ -97,6 +97,12 @@ int launch_paged_attention_decode(const __half* q, const __half* k_cache, const 
                                   const int* block_table, const int* seq_lens, int B, int n_q, int n_kv,
                                   int max_blocks, float sm_scale, int layer, int n_layers, __half* out, int g,
                                   int8_t* Xq, float* Xs, int splits, cudaStream_t stream);
+// w8a8_decode_stack.cu : a whole decode step as one persistent cooperative kernel.
+size_t decode_stack_workspace_bytes(const w8a8_decode_stack& d);
+int launch_decode_stack(const w8a8_decode_stack& d, unsigned char* workspace, size_t workspace_bytes, float* partials,
+                        size_t partial_bytes, int* counters, size_t counter_count, int* status, cudaStream_t stream);
+int decode_stack_timeline(const w8a8_decode_stack& d, const unsigned char* workspace, unsigned long long* out, int capacity,
+                          cudaStream_t stream);
 // w8a8_tp.cu : one-shot all-reduce over peer memory fused with residual add + RMSNorm + quantiser.
 struct TpState;
 int tp_create(TpState** out, int rank, int world, int max_tokens, int dim, void* ipc_handle_out64);

@@ -136,6 +136,7 @@ class SlowARStack:
                         ctx.pack_weight(lw[name], lw[sname], n, k, g, P)
                         ctx.register_packed_weight(lw[name], P)
                         self._keep.append(P)
+                        lw[name + "_packed"] = P
             self.layers.append(lw)
         self.final_norm = rand_vec(c.dim, 999983)
         freqs = (1.0 / np.power(np.float32(c.rope_base), (np.float32(2.0) * np.arange(D // 2, dtype=np.float32) /
@@ -237,6 +238,39 @@ class SlowARStack:
         else:
             ctx.residual_add(x, self.delta, B * c.dim)
             ctx.rms_norm(x, self.final_norm, self.out, B, c.dim, c.eps)
+        self.positions.add_(1)
+        self.seq_lens.add_(1)
+        return self.out
+
+    def one_launch_descriptor(self):
+        """The w8a8_decode_stack descriptor of this stack (single GPU, packed weights), built once."""
+        if getattr(self, "_desc", None) is not None:
+            return self._desc
+        assert self.tp_size == 1, "the one-launch step is the single-GPU form"
+        torch, c = self.torch, self.cfg
+        rows = []
+        for lw in self.layers:
+            rows.append([lw["attn_norm"].data_ptr(), lw["ffn_norm"].data_ptr(), lw["q_norm"].data_ptr(),
+                         lw["k_norm"].data_ptr()] + [lw[n + "_packed"].data_ptr() for n in ("wqkv", "wo", "w13", "w2")])
+        table = np.asarray(rows, dtype=np.int64)
+        assert table.shape[1] == capi.DECODE_LAYER_POINTERS
+        self._layer_table = torch.from_numpy(table).to(self.x.device)
+        d = capi.DecodeStack()
+        d.n_layers, d.batch, d.dim, d.n_q_heads, d.n_kv_heads = c.n_layer, self.B, c.dim, self.nq_l, self.nkv_l
+        d.head_dim, d.inter, d.group_size = c.head_dim, self.inter_l, c.group
+        d.eps, d.sm_scale = c.eps, 1.0 / math.sqrt(c.head_dim)
+        d.layers, d.final_norm, d.rope_freqs = self._layer_table.data_ptr(), self.final_norm.data_ptr(), self.freqs.data_ptr()
+        d.positions, d.seq_lens, d.block_table = self.positions.data_ptr(), self.seq_lens.data_ptr(), self.block_table.data_ptr()
+        d.max_blocks_per_seq = self.max_blocks
+        d.k_cache, d.v_cache, d.x, d.out = self.k_cache.data_ptr(), self.v_cache.data_ptr(), self.x.data_ptr(), self.out.data_ptr()
+        self._desc = d
+        return d
+
+    def decode_step_one_launch(self, x_in=None):
+        """The same step as decode_step through w8a8_decode_stack_step: one persistent kernel."""
+        if x_in is not None:
+            self.x.copy_(x_in, non_blocking=True)
+        self.ctx.decode_stack_step(self.one_launch_descriptor())
         self.positions.add_(1)
         self.seq_lens.add_(1)
         return self.out

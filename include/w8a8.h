@@ -207,6 +207,55 @@ W8A8_API int w8a8_paged_attention_decode(w8a8_ctx* ctx, const void* q, const voi
                                 int quant_group_size, void* Xq, void* Xs, int context_splits,
                                 void* stream);
 
+/* ---- one decode step of the whole stack as one launch ------------------------------------------ */
+
+typedef struct w8a8_decode_layer {
+    const void* attn_norm; /* fp16 [dim] */
+    const void* ffn_norm;  /* fp16 [dim] */
+    const void* q_norm;    /* fp16 [head_dim], NULL = no qk-norm */
+    const void* k_norm;
+    const void* packed[4]; /* images made by w8a8_pack_weight of: wqkv [(n_q + 2 n_kv) * head_dim, dim];
+                              wo [dim, n_q * head_dim]; w1/w3 interleaved by w8a8_pack_gate_up
+                              [2 * inter, dim]; w2 [dim, inter] */
+} w8a8_decode_layer;
+
+typedef struct w8a8_decode_stack {
+    int n_layers, batch, dim, n_q_heads, n_kv_heads, head_dim, inter, group_size;
+    float eps, sm_scale;
+    const w8a8_decode_layer* layers; /* DEVICE array [n_layers] */
+    const void* final_norm;          /* fp16 [dim] */
+    const float* rope_freqs;         /* device fp32 [head_dim / 2] */
+    const int* positions;            /* device int32 [batch]: position of the new token */
+    const int* seq_lens;             /* device int32 [batch]: tokens to attend over, the new one included */
+    const int* block_table;          /* device int32 [batch, max_blocks_per_seq] */
+    int max_blocks_per_seq;
+    void* k_cache;                   /* fp16 [blocks, n_layers, n_kv, 16, head_dim] */
+    void* v_cache;
+    void* x;   /* fp16 [batch, dim]: in = embeddings of the new tokens; left holding the residual stream */
+    void* out; /* fp16 [batch, dim]: the final-normed hidden state */
+} w8a8_decode_stack;
+
+/* Scratch the step needs inside the context's workspace (0 = the shape is not supported). */
+W8A8_API size_t w8a8_decode_stack_workspace_bytes(const w8a8_decode_stack* stack);
+
+/* Replaces the layer loop of DualAREngine::decode_step (src/engine/dual_ar_engine.cc:560-665; LM head
+ * and sampling excluded) for batch <= 8 on one GPU: per layer residual add + RMSNorm + quantiser, wqkv,
+ * qk-norm + RoPE + KV write, paged attention, wo, residual add + RMSNorm + quantiser, fused gate/up with
+ * SwiGLU, quantiser, w2 — then the final norm. One persistent cooperative launch (a CTA per SM) whose
+ * warps stream the weights of all linears without interruption; phases are separated by grid
+ * barriers with bounded waits (W8A8_ERR_TIMEOUT through w8a8_check_device_status when one runs out).
+ * Results equal, bit for bit, those of the same step made of this library's separate calls. The
+ * descriptor is read on the host during the call; `layers` must stay valid on the device until the
+ * step has run. */
+W8A8_API int w8a8_decode_stack_step(w8a8_ctx* ctx, const w8a8_decode_stack* stack, void* stream);
+
+/* Diagnostic: the device-side timeline of the last w8a8_decode_stack_step on this context. CTA 0 stamps the
+ * GPU's nanosecond timer at the start, after each of the nine phases of a layer and after each of the nine
+ * grid barriers, and after the final norm: 18 * n_layers + 2 stamps, copied to host memory (synchronises the
+ * stream). Returns the number of stamps, or minus a status code. */
+W8A8_API int w8a8_decode_stack_timeline(w8a8_ctx* ctx, const w8a8_decode_stack* stack,
+                               unsigned long long* stamps_out, int capacity, void* stream);
+
 /* ---- tensor parallelism (no counterpart in the reference, which is single-GPU) ------------- */
 
 /* Row-parallel projections (wo, w2 with K cut at quantisation-group boundaries) leave a partial

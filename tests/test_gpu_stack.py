@@ -82,3 +82,35 @@ def test_stack_matches_oracle_chain(ctx, oracle, group, dim):
     gr.replay(); torch.cuda.synchronize()
     assert np.array_equal(st.out.cpu().numpy().view(np.uint16), out.cpu().numpy().view(np.uint16)) or \
         np.linalg.norm(st.out.cpu().numpy().astype(np.float32) - got) / np.linalg.norm(got) < 1e-3
+
+
+@pytest.mark.parametrize("group,dim,n_kv,inter,layers,B,context", [
+    (256, 512, 1, 512, 2, 3, 37), (64, 1024, 2, 768, 3, 8, 100), (128, 2560, 8, 1024, 2, 8, 530), (256, 2560, 8, 9728, 2, 5, 1024)])
+def test_one_launch_step_equals_the_chain_of_launches(ctx, group, dim, n_kv, inter, layers, B, context):
+    """w8a8_decode_stack_step (one persistent cooperative kernel) against decode_step (nine launches per
+    layer) from the same state: hidden state, residual stream and both KV caches bit for bit, two steps."""
+    cfg = S.SlowARConfig(n_layer=layers, dim=dim, n_head=4 * n_kv, n_kv=n_kv, inter=inter, group=group)
+    st = S.SlowARStack(torch, ctx, cfg, B, context, max_new=8, seed=11)
+    need = ctx.decode_stack_workspace_bytes(st.one_launch_descriptor())
+    assert 0 < need <= ctx.workspace_bytes
+    rng = np.random.default_rng(dim + group)
+    k0, v0 = st.k_cache.clone(), st.v_cache.clone()
+    xs = [torch.from_numpy(rng.standard_normal((B, cfg.dim)).astype(np.float16)).cuda() for _ in range(2)]
+    want = []
+    for x_in in xs:
+        st.decode_step(x_in)
+        torch.cuda.synchronize()
+        want.append((st.out.clone(), st.x.clone() if not st.fuse_norm else None))
+    kw, vw = st.k_cache.clone(), st.v_cache.clone()
+    ctx.check_device_status()
+    st.reset_positions()
+    st.k_cache.copy_(k0); st.v_cache.copy_(v0)
+    for x_in, (out_w, x_w) in zip(xs, want):
+        st.decode_step_one_launch(x_in)
+        torch.cuda.synchronize()
+        ctx.check_device_status()
+        assert torch.equal(st.out.view(torch.int16), out_w.view(torch.int16)), "final-normed hidden state"
+        if x_w is not None:
+            assert torch.equal(st.x.view(torch.int16), x_w.view(torch.int16)), "residual stream"
+    assert torch.equal(st.k_cache.view(torch.int16), kw.view(torch.int16))
+    assert torch.equal(st.v_cache.view(torch.int16), vw.view(torch.int16))
