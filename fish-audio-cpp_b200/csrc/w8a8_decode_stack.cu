@@ -11,7 +11,9 @@
 // arriving. Barriers stall arithmetic, not the HBM stream.
 //
 // The arithmetic of every phase is that of the stand-alone kernels (w8a8_quant.cu, w8a8_gemv_packed.cu,
-// w8a8_attn.cu), operation for operation, so a step gives the same bits as the chain of launches.
+// w8a8_attn.cu), operation for operation. One thing differs: where a linear's K range is cut between warps
+// (whole row tiles per CTA here, one global split there), so its fp32 partial sums are added in a different
+// grouping; int8 codes, scales and int32 group sums are the same.
 //
 //   per layer:  A  x += delta; RMSNorm; quantise            (CTA r = token row r)       | barrier
 //               B  qkv = W8A8 linear(wqkv)                  (all warps, stream-K)        | barrier
@@ -43,6 +45,9 @@ constexpr int kRingBytes = kStages * kStagePitch;
 constexpr int kHeadDim = 128;
 constexpr int kBlockTokens = 16;
 constexpr int kQPerKv = 4;
+// The grid barrier's fence and atomic are issued by a thread other than the one that requests the bulk copies.
+constexpr int kFenceLane = 1;
+constexpr int kLocalTiles = 128;  // row tiles per CTA whose arrival counters live in shared memory
 constexpr int kPartStride = 4 + kHeadDim;  // floats per head of an attention partial: m, l, 2 pad, acc[128]
 
 struct GemvShape {
@@ -79,8 +84,6 @@ struct StackParams {
     float* acts;
     __half* delta;
     float* attn_part;
-    float* partials;
-    int* counters;
     unsigned* barrier;
     int* status;
     unsigned long long* timeline;  // CTA 0 stamps the global nanosecond timer after every phase and barrier
@@ -137,6 +140,23 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// The units of a linear are dealt out in whole 16-row tiles to the CTAs (tile t of T goes to CTA t * C / T) and a
+// CTA's units in equal contiguous runs to its 8 warps. A tile cut by a run boundary is therefore always cut
+// between warps of ONE CTA, and its partial sums meet in shared memory: no global scratch, no atomics on L2.
+__device__ __forceinline__ void warp_range(const GemvShape& sh, unsigned cta, unsigned nctas, unsigned warp, unsigned& cu0,
+                                           unsigned& n, unsigned& nw, unsigned& u0, unsigned& u1) {
+    const unsigned tiles = sh.U / sh.upt;
+    const unsigned t0 = cta * tiles / nctas, t1 = (cta + 1) * tiles / nctas;
+    cu0 = t0 * sh.upt;
+    n = (t1 - t0) * sh.upt;
+    nw = n < kWarps ? n : kWarps;  // warps that take part: none of them with an empty run
+    u0 = u1 = cu0;
+    if (warp < nw) {
+        u0 = cu0 + warp * n / nw;
+        u1 = cu0 + (warp + 1) * n / nw;
+    }
+}
+
 // ---- the weight stream of one warp ------------------------------------------------------------
 struct Stream {
     uint32_t ring;
@@ -163,12 +183,10 @@ __device__ __forceinline__ void stream_issue(Stream& s, const StackParams& p, un
         const GemvShape& sh = p.gs[s.pj & 3];
         const unsigned char* img = s.next_img;
         s.next_img = packed_image(p, s.pj + 1);
-        if (gw < sh.NW) {
-            const unsigned u0 = static_cast<unsigned>(static_cast<unsigned long long>(gw) * sh.U / sh.NW);
-            const unsigned u1 = static_cast<unsigned>(static_cast<unsigned long long>(gw + 1) * sh.U / sh.NW);
-            s.p_left = u1 - u0;
-            s.p_src = img + static_cast<size_t>(u0) * p.block_bytes;
-        }
+        unsigned cu0, n, nw, u0, u1;
+        warp_range(sh, blockIdx.x, gridDim.x, gw % kWarps, cu0, n, nw, u0, u1);
+        s.p_left = u1 - u0;
+        s.p_src = img + static_cast<size_t>(u0) * p.block_bytes;
     }
     const int slot = s.pt % kStages;
     ptx::mbar_arrive_expect_tx(&s.bar[slot], p.block_bytes);
@@ -187,7 +205,7 @@ __device__ __forceinline__ void stream_drain(Stream& s) {
     for (unsigned c = s.ct; c < pt; ++c) ptx::mbar_wait_bounded(&s.bar[c % kStages], (c / kStages) & 1, 1u << 16);
 }
 
-__device__ __forceinline__ void stamp(const StackParams& p, int& slot) {
+__device__ __noinline__ void stamp(const StackParams& p, int& slot) {
     if (blockIdx.x == 0 && threadIdx.x == 0) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
@@ -198,10 +216,10 @@ __device__ __forceinline__ void stamp(const StackParams& p, int& slot) {
 
 // ---- grid barrier -------------------------------------------------------------------------------
 // Monotonic counter, zeroed by the host before the launch. Returns false when the step is being abandoned.
-__device__ __forceinline__ bool grid_barrier(const StackParams& p, unsigned& epoch, int* s_abort) {
+__device__ __noinline__ bool grid_barrier(const StackParams& p, unsigned& epoch, int* s_abort) {
     ++epoch;
     __syncthreads();
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == kFenceLane) {
         __threadfence();
         atomicAdd(p.barrier, 1u);
         const unsigned target = epoch * gridDim.x;
@@ -228,51 +246,54 @@ __device__ __forceinline__ bool grid_barrier(const StackParams& p, unsigned& epo
 }
 
 // ---- phase A / F / final: residual add + RMSNorm (+ quantiser) of one token row by one CTA -----------------
-// 256 threads stand for the reference's T = norm_threads block (rms_norm.cu:69-70): real warp w plays
-// virtual warps w*VW .. w*VW+VW-1, so that thread-strided partial sums, the shuffle-down tree inside each
-// (virtual) warp and the tree over the warp partials happen in the reference's order.
+// The row is staged in shared memory. The sum of squares follows the reference's T = norm_threads launch
+// (rms_norm.cu:23-49, :69-70): real warp w plays virtual warps w*VW .. w*VW+VW-1 — thread-strided partial
+// sums, a shuffle-down tree inside each (virtual) warp, a tree over the warp partials — so the normed values
+// are the reference's. Normalising and quantising then go 8 elements (one 128-bit piece) per thread: the
+// g/8 threads of a group find its absmax with shuffles (int8_gemm.cu:147-211 is order-free there).
+// Written as plain loops on purpose: the code of a phase runs once per layer and must stay small.
+template <int GM>
 __device__ __noinline__ void row_phase(const StackParams& p, int row, const __half* norm_w, bool add_delta,
-                                          bool final_out, float* s_red, unsigned* s_gmax) {
+                                       bool final_out, float* s_red, __half* row_s) {
+    constexpr int LANES = GM / 8;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int K = p.dim, T = p.norm_threads, VW = T / kThreads, g = p.g, G = K / g;
+    const int K = p.dim, T = p.norm_threads, VW = T / kThreads, G = K / GM;
     const size_t base = static_cast<size_t>(row) * K;
-    __half h[4][4], nw[4][4], dl[4][4];
-    for (int j = tid; j < G; j += kThreads) s_gmax[j] = 0u;
-    // every load is requested before any value is used; slots that do not exist read element 0 and are ignored
+    const int pieces = K / 8;
+    uint4 xv[2], dv[2], wv[2];
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
+    for (int i = 0; i < 2; ++i) {  // every load first (K <= 4096: at most two pieces per thread)
+        const int c8 = tid + i * kThreads;
+        const int cc = c8 < pieces ? c8 : 0;
+        xv[i] = ldcg128(p.x + base + cc * 8);
+        dv[i] = ldcg128((add_delta ? p.delta : p.x) + base + cc * 8);
+        wv[i] = __ldg(reinterpret_cast<const uint4*>(norm_w) + cc);
+    }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int e = (warp * VW + k) * 32 + lane + i * T;
-            const int ec = (k < VW && e < K) ? e : 0;
-            nw[k][i] = __ldg(norm_w + ec);
-            h[k][i] = ldcg_h(p.x + base + ec);
-            dl[k][i] = ldcg_h((add_delta ? p.delta : p.x) + base + ec);
-        }
-    float ls[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int i = 0; i < 2; ++i) {
+        const int c8 = tid + i * kThreads;
+        if (c8 < pieces) {
+            if (add_delta) {
+                __half* hx = reinterpret_cast<__half*>(&xv[i]);
+                const __half* hd = reinterpret_cast<const __half*>(&dv[i]);
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int e = (warp * VW + k) * 32 + lane + i * T;
-            if (k < VW && e < K) {
-                __half v = h[k][i];
-                if (add_delta) {
-                    v = __float2half(__half2float(v) + __half2float(dl[k][i]));
-                    p.x[base + e] = v;
-                }
-                h[k][i] = v;
-                float val = __half2float(v);
-                ls[k] += val * val;
+                for (int e = 0; e < 8; ++e) hx[e] = __float2half(__half2float(hx[e]) + __half2float(hd[e]));
+                *reinterpret_cast<uint4*>(p.x + base + c8 * 8) = xv[i];
             }
+            reinterpret_cast<uint4*>(row_s)[c8] = xv[i];
         }
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        if (k < VW) {
-            float local_sum = ls[k];
-            for (int offset = 16; offset > 0; offset /= 2) local_sum += __shfl_down_sync(0xffffffffu, local_sum, offset);
-            if (lane == 0) s_red[warp * VW + k] = local_sum;
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int k = 0; k < VW; ++k) {
+        float local_sum = 0.0f;
+#pragma unroll 1
+        for (int e = (warp * VW + k) * 32 + lane; e < K; e += T) {
+            float val = __half2float(row_s[e]);
+            local_sum += val * val;
         }
+        for (int offset = 16; offset > 0; offset /= 2) local_sum += __shfl_down_sync(0xffffffffu, local_sum, offset);
+        if (lane == 0) s_red[warp * VW + k] = local_sum;
     }
     __syncthreads();
     float total_sum = 0.0f;
@@ -285,49 +306,69 @@ __device__ __noinline__ void row_phase(const StackParams& p, int row, const __ha
     __syncthreads();
     const float rms = s_red[0];
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
+    for (int i = 0; i < 2; ++i) {
+        const int c8 = tid + i * kThreads;
+        const bool live = c8 < pieces;  // whole warps are live or not (pieces is a multiple of 32)
+        __half* hx = reinterpret_cast<__half*>(&xv[i]);
+        const __half* hw = reinterpret_cast<const __half*>(&wv[i]);
+        float v[8], amax = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int e = (warp * VW + k) * 32 + lane + i * T;
-            if (k < VW && e < K) {
-                float val = __half2float(h[k][i]) * rms;
-                h[k][i] = __float2half(val * __half2float(nw[k][i]));
-                if (final_out) p.out[base + e] = h[k][i];
-            }
+        for (int e = 0; e < 8; ++e) {
+            float val = __half2float(hx[e]) * rms;
+            hx[e] = __float2half(val * __half2float(hw[e]));
+            v[e] = __half2float(hx[e]);
+            amax = fmaxf(amax, fabsf(v[e]));
         }
-    if (final_out) return;
-    // quantiser (int8_gemm.cu:147-211): a (virtual) warp's 32 consecutive elements lie in one group
-#pragma unroll
-    for (int k = 0; k < 4; ++k)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int e0 = (warp * VW + k) * 32 + i * T;
-            if (k < VW && e0 < K) {
-                const float m = warp_max(fabsf(__half2float(h[k][i])));
-                if (lane == 0) atomicMax(&s_gmax[e0 / g], __float_as_uint(m));
-            }
+        if (final_out) {
+            if (live) *reinterpret_cast<uint4*>(p.out + base + c8 * 8) = xv[i];
+            continue;
         }
-    __syncthreads();
-    for (int j = tid; j < G; j += kThreads) {
-        float sc = __uint_as_float(s_gmax[j]) / 127.0f;
-        if (sc < 1e-8f) sc = 1e-8f;
-        p.xs[static_cast<size_t>(row) * G + j] = sc;
+#pragma unroll
+        for (int o = LANES / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (!live) continue;
+        float scale = amax / 127.0f;
+        if (scale < 1e-8f) scale = 1e-8f;
+        if ((lane & (LANES - 1)) == 0) p.xs[static_cast<size_t>(row) * G + (c8 * 8) / GM] = scale;
+        const float inv_scale = 1.0f / scale;
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            int q = __float2int_rn(v[e] * inv_scale);
+            q = max(-127, min(127, q));
+            if (e < 4) lo |= (static_cast<uint32_t>(q) & 0xffu) << (8 * e);
+            else hi |= (static_cast<uint32_t>(q) & 0xffu) << (8 * (e - 4));
+        }
+        *reinterpret_cast<uint2*>(p.xq + base + c8 * 8) = make_uint2(lo, hi);
     }
+    __syncthreads();  // s_red and the staged row may be reused
+}
+
+// Stores a finished 16-row tile held in MMA fragment layout (rows gq / gq+8, tokens 2c / 2c+1), with the
+// SwiGLU epilogue for the gate/up linear. Kept out of line: it is called from several places of a phase
+// and the phases must stay small enough for the instruction cache.
+__device__ __noinline__ void store_tile_fn(const GemvShape& sh, __half* Y, int M, int rt, int gq, int c, float v0, float v1,
+                                           float v2, float v3) {
+    const float v[4] = {v0, v1, v2, v3};
+    const int rA = rt * 16 + gq;
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
+    for (int e = 0; e < 2; ++e) {
+        const int tok = 2 * c + e;
+        if (tok >= M) continue;
+        if (sh.epilogue == W8A8_EPI_SWIGLU) {
+            if (rA + 8 < sh.N) {
+                const float g16 = __half2float(__float2half(v[e]));
+                const __half s16 = __float2half(g16 / (1.0f + expf(-g16)));
+                const float u16 = __half2float(__float2half(v[2 + e]));
+                Y[static_cast<size_t>(tok) * (sh.N / 2) + rt * 8 + gq] = __float2half(__half2float(s16) * u16);
+            }
+        } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int e = (warp * VW + k) * 32 + lane + i * T;
-            if (k < VW && e < K) {
-                float sc = __uint_as_float(s_gmax[e / g]) / 127.0f;
-                if (sc < 1e-8f) sc = 1e-8f;
-                const float inv_scale = 1.0f / sc;
-                int q = __float2int_rn(__half2float(h[k][i]) * inv_scale);
-                q = max(-127, min(127, q));
-                p.xq[base + e] = static_cast<int8_t>(q);
+            for (int hrow = 0; hrow < 2; ++hrow) {
+                const int row = rA + 8 * hrow;
+                if (row < sh.N) Y[static_cast<size_t>(tok) * sh.N + row] = __float2half(v[2 * hrow + e]);
             }
         }
-    __syncthreads();  // s_red / s_gmax may be reused
+    }
 }
 
 // ---- phases B / E / G / I: one W8A8 linear over the packed stream, M <= 8 ------------------------------------
@@ -336,17 +377,15 @@ __device__ __noinline__ void row_phase(const StackParams& p, int row, const __ha
 // all of K over its range, and a read from L2 per block would put a memory round trip on each step);
 // rows are K + 64 bytes apart so that a quarter-warp's eight 16-byte reads fall into different banks.
 template <int GM>
-__device__ __noinline__ bool gemv_phase(const StackParams& p, Stream& s, const GemvShape& sh, const int8_t* Xq,
-                                           const float* Xs, __half* Y, unsigned gw, int lane, unsigned char* stage) {
+__device__ __noinline__ bool gemv_phase(const StackParams& p, Stream& s_ref, const GemvShape& sh, const int8_t* Xq,
+                                           const float* Xs, __half* Y, unsigned gw, int lane, unsigned char* stage,
+                                           float (*red_s)[2][4 * 32], int* cnt_s) {
+    Stream s = s_ref;  // in registers for the length of the phase
     constexpr int GPU = GM == 64 ? 4 : GM == 128 ? 2 : 1;
-    constexpr int kSlot = 4 * 32;
     const int gq = lane >> 2, c = lane & 3;
-    const unsigned NW = sh.NW, U = sh.U;
-    unsigned u0 = 0, u1 = 0;
-    if (gw < NW) {
-        u0 = static_cast<unsigned>(static_cast<unsigned long long>(gw) * U / NW);
-        u1 = static_cast<unsigned>(static_cast<unsigned long long>(gw + 1) * U / NW);
-    }
+    const unsigned warp = gw % kWarps;
+    unsigned cu0, n_cta, nw_cta, u0, u1;
+    warp_range(sh, blockIdx.x, gridDim.x, warp, cu0, n_cta, nw_cta, u0, u1);
     const int T = static_cast<int>(u1 - u0);
     const int M = p.B, upt = sh.upt;
     const int pitch = sh.K + 64;
@@ -359,9 +398,7 @@ __device__ __noinline__ bool gemv_phase(const StackParams& p, Stream& s, const G
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst0 + row * pitch + piece * 16),
                          "l"(Xq + static_cast<size_t>(row) * sh.K + piece * 16) : "memory");
         }
-        const uint32_t sdst = ptx::smem_u32(scales_s);
-        for (int i = threadIdx.x; i < M * sh.G; i += kThreads)
-            asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(sdst + i * 4), "l"(Xs + i) : "memory");
+        for (int i = threadIdx.x; i < M * sh.G; i += kThreads) scales_s[i] = ldcg_f(Xs + i);  // past L1, like the codes
         asm volatile("cp.async.wait_all;" ::: "memory");
         __syncthreads();
     }
@@ -372,80 +409,46 @@ __device__ __noinline__ bool gemv_phase(const StackParams& p, Stream& s, const G
     int P[4] = {0, 0, 0, 0}, Q[4] = {0, 0, 0, 0};
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 
-    auto store_tile = [&](int rt, const float (&v)[4]) {
-        const int rA = rt * 16 + gq;
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            const int tok = 2 * c + e;
-            if (tok >= M) continue;
-            if (sh.epilogue == W8A8_EPI_SWIGLU) {
-                if (rA + 8 < sh.N) {
-                    const float g16 = __half2float(__float2half(v[e]));
-                    const __half s16 = __float2half(g16 / (1.0f + expf(-g16)));
-                    const float u16 = __half2float(__float2half(v[2 + e]));
-                    Y[static_cast<size_t>(tok) * (sh.N / 2) + rt * 8 + gq] = __float2half(__half2float(s16) * u16);
-                }
-            } else {
-#pragma unroll
-                for (int hrow = 0; hrow < 2; ++hrow) {
-                    const int row = rA + 8 * hrow;
-                    if (row < sh.N) Y[static_cast<size_t>(tok) * sh.N + row] = __float2half(v[2 * hrow + e]);
-                }
-            }
-        }
+    auto store_tile = [&](int rt, const float (&v)[4]) { store_tile_fn(sh, Y, M, rt, gq, c, v[0], v[1], v[2], v[3]); };
+    auto warp_of_unit = [&](unsigned u) -> unsigned {  // the warp of this CTA whose run holds unit u
+        return ((u - cu0 + 1) * nw_cta - 1) / n_cta;
     };
-    auto warp_of_unit = [&](unsigned u) -> unsigned {
-        return static_cast<unsigned>((static_cast<unsigned long long>(u + 1) * NW - 1) / U);
-    };
-    int pend_rt[2];
-    unsigned pend_old[2];
-    int npend = 0;
+    const int cta_rt0 = static_cast<int>(cu0 / upt);
+    // Called when the warp has added its last unit of row tile rt into acc. A cut tile: the partial goes to the
+    // warp's slot, the arrival is counted, and whichever warp arrives last adds the partials in ascending-K
+    // order and stores. Nothing waits.
     auto finish_tile = [&](int rt) {
         const unsigned t_lo = static_cast<unsigned>(rt) * upt, t_hi = t_lo + upt;
         if (u0 <= t_lo && t_hi <= u1) {
             store_tile(rt, acc);
         } else {
+            const unsigned first = warp_of_unit(t_lo), last = warp_of_unit(t_hi - 1);
             const int my_slot = (static_cast<int>(u0 / upt) == rt) ? 0 : 1;
-            float* mine = p.partials + (static_cast<size_t>(gw) * 2 + my_slot) * kSlot;
+            float* mine = red_s[warp][my_slot];
 #pragma unroll
             for (int r = 0; r < 4; ++r) mine[r * 32 + lane] = acc[r];
             __syncwarp();
-            unsigned old = 0;
-            if (lane == 0)
-                asm volatile("atom.add.release.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + rt) : "memory");
-            if (npend == 0) { pend_rt[0] = rt; pend_old[0] = old; } else { pend_rt[1] = rt; pend_old[1] = old; }
-            ++npend;
+            int old = 0;
+            if (lane == 0) {
+                __threadfence_block();
+                old = atomicAdd(&cnt_s[rt - cta_rt0], 1);
+            }
+            old = __shfl_sync(0xffffffffu, old, 0);
+            if (old == static_cast<int>(last - first)) {
+                __threadfence_block();
+                float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                for (unsigned ww = first; ww <= last; ++ww) {
+                    const unsigned wu0 = cu0 + ww * n_cta / nw_cta;
+                    const float* src = red_s[ww][(static_cast<int>(wu0 / upt) == rt) ? 0 : 1];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) sum[r] += src[r * 32 + lane];
+                }
+                store_tile(rt, sum);
+                if (lane == 0) cnt_s[rt - cta_rt0] = 0;  // the next linear starts from zero again
+            }
         }
 #pragma unroll
         for (int r = 0; r < 4; ++r) acc[r] = 0.0f;
-    };
-    auto resolve_pending = [&](int rt, unsigned old_lane0) {
-        const unsigned t_lo = static_cast<unsigned>(rt) * upt, t_hi = t_lo + upt;
-        const unsigned first = warp_of_unit(t_lo), last = warp_of_unit(t_hi - 1);
-        const unsigned old = __shfl_sync(0xffffffffu, old_lane0, 0);
-        if (old != last - first) return;
-        __threadfence();
-        float sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (unsigned w = first; w <= last; w += 4) {
-            float v[4][4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const unsigned ww = w + q <= last ? w + q : last;
-                const unsigned wu0 = static_cast<unsigned>(static_cast<unsigned long long>(ww) * U / NW);
-                const int slot = (static_cast<int>(wu0 / upt) == rt) ? 0 : 1;
-                const float* src = p.partials + (static_cast<size_t>(ww) * 2 + slot) * kSlot;
-#pragma unroll
-                for (int r = 0; r < 4; ++r) v[q][r] = ldcg_f(src + r * 32 + lane);
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-                if (w + q <= last) {
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) sum[r] += v[q][r];
-                }
-        }
-        store_tile(rt, sum);
-        if (lane == 0) p.counters[rt] = 0;
     };
     auto promote = [&](__half hsa, __half hsb, float x0, float x1) {
         const float fa = __half2float(hsa), fb = __half2float(hsb);
@@ -497,17 +500,14 @@ __device__ __noinline__ bool gemv_phase(const StackParams& p, Stream& s, const G
         ++s.ct;
         if (lane == 0) stream_issue(s, p, gw);
         if (GM == 256) promote(sa[0], sb[0], xsc[0][0], xsc[0][1]);
-        if (++ub == upt) {
+        // one call site for the tile end: the row tile is complete, or the range ends inside it
+        ++ub;
+        if (ub == upt || t + 1 == T) {
             finish_tile(rt);
-            ub = 0;
-            ++rt;
+            if (ub == upt) { ub = 0; ++rt; }
         }
     }
-    if (ok && T > 0 && ub != 0) finish_tile(rt);
-    if (ok) {
-        if (npend > 0) resolve_pending(pend_rt[0], pend_old[0]);
-        if (npend > 1) resolve_pending(pend_rt[1], pend_old[1]);
-    }
+    s_ref = s;
     return ok;
 }
 
@@ -519,9 +519,9 @@ struct KvFrag {
 
 // One warp, one head of the new token: per-head RMSNorm in the reference's order (rms_norm.cu:23-49 with
 // a 128-thread block) and interleaved-pair RoPE (rope.cu:36-45). h: elements lane, 32+lane, 64+lane, 96+lane.
-__device__ __forceinline__ void head_norm_rope(__half (&h)[4], const __half* w, float eps, const float* freqs, int pos,
-                                               int lane) {
-    if (w) {
+__device__ __forceinline__ void head_norm_rope(__half (&h)[4], bool with_norm, const __half (&w)[4], float eps,
+                                               const float (&fr)[4], int pos, int lane) {
+    if (with_norm) {
         float part[4];
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
@@ -536,13 +536,12 @@ __device__ __forceinline__ void head_norm_rope(__half (&h)[4], const __half* w, 
 #pragma unroll
         for (int v = 0; v < 4; ++v) {
             float val = __half2float(h[v]) * rms;
-            h[v] = __float2half(val * __half2float(__ldg(w + v * 32 + lane)));
+            h[v] = __float2half(val * __half2float(w[v]));
         }
     }
 #pragma unroll
     for (int v = 0; v < 4; ++v) {
-        const float freq = __ldg(freqs + ((v * 32 + lane) >> 1));
-        float angle = freq * static_cast<float>(pos);
+        float angle = fr[v] * static_cast<float>(pos);
         float cos_a = cosf(angle), sin_a = sinf(angle);
         const float mine = __half2float(h[v]);
         const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
@@ -559,58 +558,51 @@ struct AttnSmem {
     __half out_s[kQPerKv * kHeadDim];
 };
 
+// Physical numbers of the warp's first 32 KV blocks (lane i: its i-th block). They depend on the sequence and on
+// the context slice only, not on the layer, so the kernel reads them once and keeps them in a register.
+__device__ __forceinline__ int first_phys(const StackParams& p, int item, int warp, int lane, int seq_len) {
+    const int S = p.S, s = item % S, b = item / (S * p.n_kv);
+    const int n_blocks = (seq_len + kBlockTokens - 1) / kBlockTokens;
+    const int bi = s + warp * S + lane * S * kWarps;
+    return bi < n_blocks ? __ldg(p.block_table + static_cast<size_t>(b) * p.max_blocks + bi) : 0;
+}
+
 __device__ __noinline__ void attn_phase(const StackParams& p, const w8a8_decode_layer& L, int layer, int item,
-                                           AttnSmem& sm) {
+                                           AttnSmem& sm, int pos, int seq_len, int phys_first) {
     const int S = p.S;
     const int s = item % S, kvh = (item / S) % p.n_kv, b = item / (S * p.n_kv);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int total_heads = p.n_q + 2 * p.n_kv;
-    const int pos = __ldg(p.positions + b), seq_len = __ldg(p.seq_lens + b);
-    const int n_blocks = (seq_len + kBlockTokens - 1) / kBlockTokens;
+    // Everything the prologue reads is requested here, before the first value is used: each dependent read
+    // is a round trip to L2, and a chain of five of them was longer than the attention loop itself.
     const __half* qkv_row = p.qkv + static_cast<size_t>(b) * total_heads * kHeadDim;
-    const bool owner = ((pos / kBlockTokens) % S) == s;  // this CTA attends over the block the new token joins
-
-    if (warp < kQPerKv) {
-        __half h[4];
-        const __half* src = qkv_row + (kvh * kQPerKv + warp) * kHeadDim;
+    const bool role_q = warp < kQPerKv, is_k = warp == kQPerKv, is_v = warp == kQPerKv + 1;
+    __half hq[4], wq[4];
+    float fr[4];
+    const __half* norm_w = static_cast<const __half*>(role_q ? L.q_norm : L.k_norm);
+    {
+        const __half* src = qkv_row + (role_q ? kvh * kQPerKv + warp : p.n_q + (is_k ? 0 : p.n_kv) + kvh) * kHeadDim;
 #pragma unroll
-        for (int v = 0; v < 4; ++v) h[v] = ldcg_h(src + v * 32 + lane);
-        head_norm_rope(h, static_cast<const __half*>(L.q_norm), p.eps, p.freqs, pos, lane);
-#pragma unroll
-        for (int v = 0; v < 4; ++v) sm.q_s[warp][v * 32 + lane] = h[v];
-    } else if (warp < kQPerKv + 2 && owner) {
-        const bool is_k = warp == kQPerKv;
-        __half h[4];
-        const __half* src = qkv_row + (p.n_q + (is_k ? 0 : p.n_kv) + kvh) * kHeadDim;
-#pragma unroll
-        for (int v = 0; v < 4; ++v) h[v] = ldcg_h(src + v * 32 + lane);
-        if (is_k) head_norm_rope(h, static_cast<const __half*>(L.k_norm), p.eps, p.freqs, pos, lane);
-        const int phys = __ldg(p.block_table + static_cast<size_t>(b) * p.max_blocks + pos / kBlockTokens);
-        if (phys >= 0) {
-            __half* dst = (is_k ? p.k_cache : p.v_cache) +
-                          ((((static_cast<size_t>(phys) * p.n_layers + layer) * p.n_kv + kvh) * kBlockTokens) +
-                           pos % kBlockTokens) * kHeadDim;
-#pragma unroll
-            for (int v = 0; v < 4; ++v) dst[v * 32 + lane] = h[v];
+        for (int v = 0; v < 4; ++v) {
+            hq[v] = (role_q || is_k || is_v) ? ldcg_h(src + v * 32 + lane) : __float2half(0.0f);
+            wq[v] = norm_w ? __ldg(norm_w + v * 32 + lane) : __float2half(1.0f);
+            fr[v] = __ldg(p.freqs + ((v * 32 + lane) >> 1));
         }
     }
-    __syncthreads();  // q in shared memory; the new token's k and v row written (read back past L1 below)
+    const int n_blocks = (seq_len + kBlockTokens - 1) / kBlockTokens;
+    const bool owner = ((pos / kBlockTokens) % S) == s;  // this CTA attends over the block the new token joins
 
-    uint32_t qa[4][4];
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (g < kQPerKv) v = *reinterpret_cast<const uint4*>(&sm.q_s[g][(i * 4 + t) * 8]);
-        qa[i][0] = v.x; qa[i][1] = v.y; qa[i][2] = v.z; qa[i][3] = v.w;
-    }
+    // The K and V blocks do not depend on this step's q: the first two are requested before the new token's
+    // q / k / v rows are normalised and rotated, so that the two latencies overlap. The one block that does
+    // depend on this step (the block the new token joins, attended over by the owner) waits for the write.
     const int stride = S * kWarps, first = s + warp * S;
     const int n_mine = first < n_blocks ? (n_blocks - first + stride - 1) / stride : 0;
     auto fetch_phys = [&](int it0) -> int {
         const int bi = first + (it0 + lane) * stride;
         return bi < n_blocks ? __ldg(p.block_table + static_cast<size_t>(b) * p.max_blocks + bi) : 0;
     };
-    int phys_mine = fetch_phys(0);
+    int phys_mine = phys_first;
     auto load = [&](KvFrag& f, int it) {
         if ((it & 31) == 0 && it > 0) phys_mine = fetch_phys(it);
         const int phys = __shfl_sync(0xffffffffu, phys_mine, it & 31);
@@ -632,6 +624,41 @@ __device__ __noinline__ void attn_phase(const StackParams& p, const w8a8_decode_
             for (int h = 0; h < 2; ++h) f.v[q][h] = ldcg128(row + (g + 8 * h) * 8);
         }
     };
+    KvFrag fa, fb;
+    const int new_bi = pos / kBlockTokens;
+    const bool pre0 = n_mine > 0 && !(owner && first == new_bi);
+    const bool pre1 = n_mine > 1 && !(owner && first + stride == new_bi);
+    if (pre0) load(fa, 0);
+    if (pre1) load(fb, 1);
+
+    // warps 0..3: a query head each; in the owner CTA warp 4: the new k row, warp 5: the new v row
+    if (role_q || ((is_k || is_v) && owner)) {
+        if (!is_v) head_norm_rope(hq, norm_w != nullptr, wq, p.eps, fr, pos, lane);
+        if (role_q) {
+#pragma unroll
+            for (int v = 0; v < 4; ++v) sm.q_s[warp][v * 32 + lane] = hq[v];
+        } else {
+            const int phys = __ldg(p.block_table + static_cast<size_t>(b) * p.max_blocks + new_bi);
+            if (phys >= 0) {
+                __half* dst = (is_k ? p.k_cache : p.v_cache) +
+                              ((((static_cast<size_t>(phys) * p.n_layers + layer) * p.n_kv + kvh) * kBlockTokens) +
+                               pos % kBlockTokens) * kHeadDim;
+#pragma unroll
+                for (int v = 0; v < 4; ++v) dst[v * 32 + lane] = hq[v];
+            }
+        }
+    }
+    __syncthreads();  // q in shared memory; the new token's k and v row written (read back past L1 below)
+    if (n_mine > 0 && !pre0) load(fa, 0);
+    if (n_mine > 1 && !pre1) load(fb, 1);
+
+    uint32_t qa[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (g < kQPerKv) v = *reinterpret_cast<const uint4*>(&sm.q_s[g][(i * 4 + t) * 8]);
+        qa[i][0] = v.x; qa[i][1] = v.y; qa[i][2] = v.z; qa[i][3] = v.w;
+    }
     float m_run = -1e30f, l_run = 0.0f;
     float o[16][2];
 #pragma unroll
@@ -682,18 +709,13 @@ __device__ __noinline__ void attn_phase(const StackParams& p, const w8a8_decode_
                 mma_top_rows(o[n][0], o[n][1], pa0, pa2, b0, b1);
             }
     };
-    {
-        KvFrag fa, fb;
-        int it = 0;
-        if (n_mine > 0) load(fa, 0);
-        while (it < n_mine) {
-            if (it + 1 < n_mine) load(fb, it + 1);
-            compute(fa, it);
-            if (++it >= n_mine) break;
-            if (it + 1 < n_mine) load(fa, it + 1);
-            compute(fb, it);
-            ++it;
-        }
+    for (int it = 0; it < n_mine;) {  // fa holds block `it`, fb block `it + 1`
+        compute(fa, it);
+        if (it + 2 < n_mine) load(fa, it + 2);
+        if (++it >= n_mine) break;
+        compute(fb, it);
+        if (it + 2 < n_mine) load(fb, it + 2);
+        ++it;
     }
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
@@ -734,16 +756,25 @@ __device__ __noinline__ void merge_phase(const StackParams& p, int pair, AttnSme
     if (threadIdx.x < kQPerKv * 32) {
         const int hh = threadIdx.x >> 5, d0 = (threadIdx.x & 31) * 4;
         const float* src0 = p.attn_part + (static_cast<size_t>(pair) * S * kQPerKv + hh) * kPartStride;
-        float m = -1e30f;
-        for (int r = 0; r < S; ++r) m = fmaxf(m, ldcg_f(src0 + static_cast<size_t>(r) * kQPerKv * kPartStride));
-        float l = 0.0f, a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int r = 0; r < S; ++r) {
-            const float* src = src0 + static_cast<size_t>(r) * kQPerKv * kPartStride;
-            const float scr = __expf(ldcg_f(src) - m);
-            l += ldcg_f(src + 1) * scr;
-            const float4 v4 = ldcg_f4(src + 4 + d0);
-            a[0] += v4.x * scr; a[1] += v4.y * scr; a[2] += v4.z * scr; a[3] += v4.w * scr;
+        float4 ml[8], v4s[8];  // S <= 8; every load is requested before the first value is used
+#pragma unroll
+        for (int r = 0; r < 8; ++r) {
+            const float* src = src0 + static_cast<size_t>(r < S ? r : 0) * kQPerKv * kPartStride;
+            ml[r] = ldcg_f4(src);
+            v4s[r] = ldcg_f4(src + 4 + d0);
         }
+        float m = -1e30f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < S) m = fmaxf(m, ml[r].x);
+        float l = 0.0f, a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int r = 0; r < 8; ++r)
+            if (r < S) {
+                const float scr = __expf(ml[r].x - m);
+                l += ml[r].y * scr;
+                a[0] += v4s[r].x * scr; a[1] += v4s[r].y * scr; a[2] += v4s[r].z * scr; a[3] += v4s[r].w * scr;
+            }
         const float inv = seq_len > 0 ? 1.0f / l : 0.0f;
 #pragma unroll
         for (int i = 0; i < 4; ++i) sm.out_s[hh * kHeadDim + d0 + i] = __float2half(seq_len > 0 ? a[i] * inv : 0.0f);
@@ -808,10 +839,12 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const __grid_
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bars[kWarps][kStages];
     __shared__ float s_red[32];
-    __shared__ unsigned s_gmax[64];
     __shared__ int s_abort;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const unsigned gw = warp * gridDim.x + blockIdx.x, total_warps = gridDim.x * kWarps;
+    __shared__ float red_s[kWarps][2][4 * 32];
+    __shared__ int cnt_s[kLocalTiles];
+    for (int i = threadIdx.x; i < kLocalTiles; i += kThreads) cnt_s[i] = 0;
+    const unsigned gw = blockIdx.x * kWarps + warp, total_warps = gridDim.x * kWarps;
     const uint32_t base_u32 = (ptx::smem_u32(smem_raw) + 127u) & ~127u;
     // after the ring: one region used by turns for the attention scratch and for the staged activation codes
     unsigned char* stage = smem_raw + (base_u32 - ptx::smem_u32(smem_raw)) + kWarps * kRingBytes;
@@ -832,6 +865,15 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const __grid_
     __syncwarp();
     __syncthreads();
 
+    // layer-invariant inputs of the attention phase, read once
+    const int n_items = p.B * p.n_kv * p.S;
+    int a_pos = 0, a_len = 0, a_phys = 0;
+    if (static_cast<int>(blockIdx.x) < n_items) {
+        const int b = blockIdx.x / (p.S * p.n_kv);
+        a_pos = __ldg(p.positions + b);
+        a_len = __ldg(p.seq_lens + b);
+        a_phys = first_phys(p, blockIdx.x, warp, lane, a_len);
+    }
     unsigned epoch = 0;
     int ts = 0;  // 19 stamps per layer: after each of the 9 phases and each of the 9 barriers, +1 at the top
     bool ok = true;
@@ -840,17 +882,32 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const __grid_
         const w8a8_decode_layer& L = p.layers[l];
         // A
         if (static_cast<int>(blockIdx.x) < p.B)
-            row_phase(p, blockIdx.x, static_cast<const __half*>(L.attn_norm), l > 0, false, s_red, s_gmax);
+            row_phase<GM>(p, blockIdx.x, static_cast<const __half*>(L.attn_norm), l > 0, false, s_red,
+                          reinterpret_cast<__half*>(stage));
         stamp(p, ts);
         if (!(ok = grid_barrier(p, epoch, &s_abort))) break;
         stamp(p, ts);
         // B
-        ok = gemv_phase<GM>(p, s, p.gs[0], p.xq, p.xs, p.qkv, gw, lane, stage);
+        ok = gemv_phase<GM>(p, s, p.gs[0], p.xq, p.xs, p.qkv, gw, lane, stage, red_s, cnt_s);
         stamp(p, ts);
         if (!grid_barrier(p, epoch, &s_abort) || !ok) { ok = false; break; }
         stamp(p, ts);
         // C
-        for (int item = blockIdx.x; item < p.B * p.n_kv * p.S; item += gridDim.x) attn_phase(p, L, l, item, asm_);
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x) {
+            if (item != static_cast<int>(blockIdx.x)) {  // a CTA with more than one item looks the later ones up again
+                const int b = item / (p.S * p.n_kv);
+                a_pos = __ldg(p.positions + b);
+                a_len = __ldg(p.seq_lens + b);
+                a_phys = first_phys(p, item, warp, lane, a_len);
+            }
+            attn_phase(p, L, l, item, asm_, a_pos, a_len, a_phys);
+        }
+        if (n_items > static_cast<int>(gridDim.x)) {  // back to the first item's values for the next layer
+            const int b = blockIdx.x / (p.S * p.n_kv);
+            a_pos = __ldg(p.positions + b);
+            a_len = __ldg(p.seq_lens + b);
+            a_phys = first_phys(p, blockIdx.x, warp, lane, a_len);
+        }
         stamp(p, ts);
         if (!(ok = grid_barrier(p, epoch, &s_abort))) break;
         stamp(p, ts);
@@ -860,18 +917,19 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const __grid_
         if (!(ok = grid_barrier(p, epoch, &s_abort))) break;
         stamp(p, ts);
         // E
-        ok = gemv_phase<GM>(p, s, p.gs[1], p.aq, p.as_, p.delta, gw, lane, stage);
+        ok = gemv_phase<GM>(p, s, p.gs[1], p.aq, p.as_, p.delta, gw, lane, stage, red_s, cnt_s);
         stamp(p, ts);
         if (!grid_barrier(p, epoch, &s_abort) || !ok) { ok = false; break; }
         stamp(p, ts);
         // F
         if (static_cast<int>(blockIdx.x) < p.B)
-            row_phase(p, blockIdx.x, static_cast<const __half*>(L.ffn_norm), true, false, s_red, s_gmax);
+            row_phase<GM>(p, blockIdx.x, static_cast<const __half*>(L.ffn_norm), true, false, s_red,
+                          reinterpret_cast<__half*>(stage));
         stamp(p, ts);
         if (!(ok = grid_barrier(p, epoch, &s_abort))) break;
         stamp(p, ts);
         // G
-        ok = gemv_phase<GM>(p, s, p.gs[2], p.xq, p.xs, p.act, gw, lane, stage);
+        ok = gemv_phase<GM>(p, s, p.gs[2], p.xq, p.xs, p.act, gw, lane, stage, red_s, cnt_s);
         stamp(p, ts);
         if (!grid_barrier(p, epoch, &s_abort) || !ok) { ok = false; break; }
         stamp(p, ts);
@@ -881,13 +939,14 @@ __global__ void __launch_bounds__(kThreads, 1) decode_stack_kernel(const __grid_
         if (!(ok = grid_barrier(p, epoch, &s_abort))) break;
         stamp(p, ts);
         // I
-        ok = gemv_phase<GM>(p, s, p.gs[3], p.actq, p.acts, p.delta, gw, lane, stage);
+        ok = gemv_phase<GM>(p, s, p.gs[3], p.actq, p.acts, p.delta, gw, lane, stage, red_s, cnt_s);
         stamp(p, ts);
         if (!grid_barrier(p, epoch, &s_abort) || !ok) { ok = false; break; }
         stamp(p, ts);
     }
     if (ok) {
-        if (static_cast<int>(blockIdx.x) < p.B) row_phase(p, blockIdx.x, p.final_norm, true, true, s_red, s_gmax);
+        if (static_cast<int>(blockIdx.x) < p.B)
+            row_phase<GM>(p, blockIdx.x, p.final_norm, true, true, s_red, reinterpret_cast<__half*>(stage));
         stamp(p, ts);
     } else {
         stream_drain(s);
@@ -1002,7 +1061,8 @@ int launch_decode_stack(const w8a8_decode_stack& d, unsigned char* workspace, si
     p.attn_part = reinterpret_cast<float*>(workspace + sc.attn_part);
     p.barrier = reinterpret_cast<unsigned*>(workspace + sc.barrier);
     p.timeline = reinterpret_cast<unsigned long long*>(workspace + sc.timeline);
-    p.partials = partials; p.counters = counters; p.status = status;
+    p.status = status;
+    (void)partials; (void)partial_bytes; (void)counters; (void)counter_count;  // the step adds cut tiles in shared memory
     const int Ns[4] = {(d.n_q_heads + 2 * d.n_kv_heads) * kHeadDim, d.dim, 2 * d.inter, d.dim};
     const int Ks[4] = {d.dim, d.n_q_heads * kHeadDim, d.dim, d.inter};
     const unsigned warps = static_cast<unsigned>(sms) * kWarps;
@@ -1012,13 +1072,11 @@ int launch_decode_stack(const w8a8_decode_stack& d, unsigned char* workspace, si
         sh.epilogue = i == 2 ? W8A8_EPI_SWIGLU : W8A8_EPI_NONE;
         if (Ks[i] % 256 != 0 || Ns[i] % 16 != 0) return fail(W8A8_ERR_UNSUPPORTED, "decode stack: linear %d is %d x %d", i, Ns[i], Ks[i]);
         const unsigned long long U = static_cast<unsigned long long>(Ns[i] / 16) * sh.upt;
-        if (U >= (1ull << 31)) return fail(W8A8_ERR_UNSUPPORTED, "decode stack: linear %d too large", i);
+        if ((U + 1) * warps >= (1ull << 32)) return fail(W8A8_ERR_UNSUPPORTED, "decode stack: linear %d too large", i);
         sh.U = static_cast<unsigned>(U);
-        sh.NW = sh.U < warps ? sh.U : warps;
-        if (static_cast<size_t>(Ns[i] / 16) > counter_count) return fail(W8A8_ERR_WORKSPACE, "decode stack: too many row tiles");
+        sh.NW = warps;
+        if (Ns[i] / 16 / sms + 2 > kLocalTiles) return fail(W8A8_ERR_UNSUPPORTED, "decode stack: linear %d has too many row tiles per CTA", i);
     }
-    if (static_cast<size_t>(warps) * 2 * 4 * 32 * sizeof(float) > partial_bytes)
-        return fail(W8A8_ERR_WORKSPACE, "decode stack: split-K scratch too small");
 
     cudaError_t e = cudaMemsetAsync(p.barrier, 0, 256, stream);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "decode stack: memset: %s", cudaGetErrorString(e));
