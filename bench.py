@@ -388,6 +388,23 @@ class DecodeStack:
         if e2e:
             self.host_out.copy_(self.st.out, non_blocking=True)
 
+    def timeline(self):
+        """Median microseconds per phase and per barrier of one layer in the last one-launch step (CTA 0's
+        device clock; layer 0 left out: its first phase has no residual to add)."""
+        t = np.asarray(self.ctx.decode_stack_timeline(self.st.one_launch_descriptor()), dtype=np.int64)
+        L = self.cfg.n_layer
+        per = np.diff(t)[:18 * L].reshape(L, 18)[1:] if L > 1 else np.diff(t)[:18].reshape(1, 18)
+        med = np.median(per, axis=0) / 1e3
+        names = ["A norm+quant", "B wqkv", "C rope+kv+attention", "D merge+quant", "E wo", "F norm+quant", "G w13+swiglu",
+                 "H quant", "I w2"]
+        out = {}
+        for i, n in enumerate(names):
+            out[n] = round(float(med[2 * i]), 2)
+            out[n + " | barrier"] = round(float(med[2 * i + 1]), 2)
+        out["layer"] = round(float(med.sum()), 2)
+        out["step"] = round(float(t[-1] - t[0]) / 1e3, 1)
+        return out
+
     def time_linears(self, reps=20):
         """(average seconds per launch, algorithmic bytes per launch) of the four linears of every layer,
         replayed alone from a graph: the dominant kernel on its own, timed with CUDA events."""
@@ -580,6 +597,8 @@ def main():
     ap.add_argument("--split-k", type=int, default=0, help="force the GEMV's K-slice count (tuning aid)")
     ap.add_argument("--no-pack", action="store_true", help="leave weights row-major (skip the loader-side pack)")
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a graph")
+    ap.add_argument("--timeline", action="store_true",
+                    help="with --step-form one-launch: add the device-side per-phase medians of one step to the line")
     ap.add_argument("--step-form", choices=["one-launch", "chain"], default="chain",
                     help="decode_stack on one GPU: the whole step as one persistent kernel (w8a8_decode_stack_step) "
                          "or as nine launches per layer")
@@ -745,6 +764,8 @@ def main():
             "clocks": clocks,
             "gpu_launches": wl.launches_per_step * args.steps,
         }
+        if args.timeline and getattr(wl, "one_launch", False):
+            line["config"]["timeline_us"] = wl.timeline()
         if lin:
             ach = lin[1] / lin_s / 1e9
             line["roofline"] = {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",

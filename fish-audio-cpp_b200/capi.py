@@ -78,6 +78,7 @@ def load_library() -> C.CDLL:
         "w8a8_decode_stack_timeline": (I, [P, C.POINTER(DecodeStack), P, I, P]),
         "w8a8_qknorm_rope_kvwrite": (I, [P, P, P, P, F, P, P, P, I, P, P, I, I, I, I, I, I, P, P]),
         "w8a8_paged_attention_decode": (I, [P, P, P, P, P, P, P, I, I, I, I, F, I, I, I, I, P, P, I, P]),
+        "w8a8_qkv_attention_decode": (I, [P, P, P, P, F, P, P, P, P, P, P, P, I, I, I, I, F, I, I, I, I, P, P, I, P]),
         "w8a8_tp_create": (I, [P, I, I, I, I, P]),
         "w8a8_tp_connect": (I, [P, P]),
         "w8a8_tp_allreduce_rmsnorm_quantize": (I, [P, P, P, P, F, P, P, I, I, I, I, P, P, P, P]),
@@ -101,7 +102,7 @@ EXPORTS = [
     "w8a8_rmsnorm_quantize", "w8a8_silu", "w8a8_mul", "w8a8_residual_add", "w8a8_linear", "w8a8_linear_q",
     "w8a8_rmsnorm_linear", "w8a8_decode_stack_workspace_bytes", "w8a8_decode_stack_step",
     "w8a8_decode_stack_timeline",
-    "w8a8_pack_gate_up", "w8a8_qknorm_rope_kvwrite", "w8a8_paged_attention_decode", "w8a8_tp_create", "w8a8_tp_connect",
+    "w8a8_pack_gate_up", "w8a8_qknorm_rope_kvwrite", "w8a8_paged_attention_decode", "w8a8_qkv_attention_decode", "w8a8_tp_create", "w8a8_tp_connect",
     "w8a8_tp_allreduce_rmsnorm_quantize", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
     "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch",
 ]
@@ -271,6 +272,16 @@ class Context:
                                                          head_dim, max_blocks, sm_scale, layer, n_layers, n_kv,
                                                          quant_group_size, _ptr(Xq), _ptr(Xs), context_splits,
                                                          _stream(stream)), "w8a8_paged_attention_decode")
+
+    def qkv_attention_decode(self, qkv, q_norm_w, k_norm_w, eps, freqs, positions, k_cache, v_cache, block_table,
+                             seq_lens, out, batch, n_heads, head_dim, max_blocks, sm_scale, layer, n_layers, n_kv,
+                             quant_group_size=0, Xq=None, Xs=None, context_splits=0, stream=None):
+        self._check(self.lib.w8a8_qkv_attention_decode(self.handle, _ptr(qkv), _ptr(q_norm_w), _ptr(k_norm_w), eps,
+                                                       _ptr(freqs), _ptr(positions), _ptr(k_cache), _ptr(v_cache),
+                                                       _ptr(block_table), _ptr(seq_lens), _ptr(out), batch, n_heads,
+                                                       head_dim, max_blocks, sm_scale, layer, n_layers, n_kv,
+                                                       quant_group_size, _ptr(Xq), _ptr(Xs), context_splits,
+                                                       _stream(stream)), "w8a8_qkv_attention_decode")
 
     def tp_create(self, rank, world, max_tokens, dim) -> bytes:
         """Allocates this rank's exchange buffer; returns its 64-byte IPC handle."""

@@ -403,6 +403,25 @@ int w8a8_paged_attention_decode(w8a8_ctx* ctx, const void* q, const void* k_cach
                                          static_cast<float*>(Xs), context_splits, static_cast<cudaStream_t>(stream));
 }
 
+int w8a8_qkv_attention_decode(w8a8_ctx* ctx, const void* qkv, const void* q_norm_w, const void* k_norm_w, float eps,
+                              const float* freqs, const int* positions, void* k_cache, void* v_cache,
+                              const int* block_table, const int* seq_lens, void* out, int batch, int n_heads,
+                              int head_dim, int max_blocks_per_seq, float sm_scale, int layer, int n_layers,
+                              int n_kv_heads, int quant_group_size, void* Xq, void* Xs, int context_splits,
+                              void* stream) {
+    if (!ctx) return fail(W8A8_ERR_INVALID_ARG, "null context");
+    if (batch < 0 || head_dim != 128) return fail(W8A8_ERR_UNSUPPORTED, "head_dim must be 128 (got %d)", head_dim);
+    if (batch > 0 && (!qkv || !freqs || !positions || !k_cache || !v_cache || !block_table || !seq_lens || (!out && !Xq)))
+        return fail(W8A8_ERR_INVALID_ARG, "qkv_attention_decode: null argument");
+    if ((Xq == nullptr) != (Xs == nullptr)) return fail(W8A8_ERR_INVALID_ARG, "Xq and Xs go together");
+    return launch_qkv_attention_decode(static_cast<const __half*>(qkv), static_cast<const __half*>(q_norm_w),
+                                       static_cast<const __half*>(k_norm_w), eps, freqs, positions,
+                                       static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), block_table, seq_lens,
+                                       batch, n_heads, n_kv_heads, max_blocks_per_seq, sm_scale, layer, n_layers,
+                                       static_cast<__half*>(out), quant_group_size, static_cast<int8_t*>(Xq),
+                                       static_cast<float*>(Xs), context_splits, static_cast<cudaStream_t>(stream));
+}
+
 size_t w8a8_decode_stack_workspace_bytes(const w8a8_decode_stack* stack) {
     return stack ? decode_stack_workspace_bytes(*stack) : 0;
 }

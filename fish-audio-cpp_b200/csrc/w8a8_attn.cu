@@ -132,6 +132,15 @@ struct AttnParams {
     float* Xs;                // [B, n_q*128/g]
     int g;
     int S;                    // context slices = cluster size
+    // fused prologue (ROPE form): q, k, v of the new token come from the qkv projection's output
+    const __half* qkv;        // [B, (n_q + 2 n_kv) * 128]
+    const __half* q_norm_w;   // [128] or null
+    const __half* k_norm_w;
+    float eps;
+    const float* freqs;       // [64]
+    const int* positions;     // [B]
+    __half* k_cache_w;        // the caches again, writable
+    __half* v_cache_w;
 };
 
 constexpr int kAttnWarps = 8;
@@ -150,6 +159,46 @@ __device__ __forceinline__ uint4 ld_stream16(const __half* ptr) {
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(ptr));
     return r;
+}
+
+__device__ __forceinline__ uint4 ld_cg16(const __half* ptr) {
+    uint4 r;
+    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(ptr));
+    return r;
+}
+
+// One warp, one head of the new token: per-head RMSNorm in the reference's order (rms_norm.cu:23-49 with a
+// 128-thread block) and interleaved-pair RoPE (rope.cu:36-45) — the arithmetic of qknorm_rope_kvwrite_kernel.
+// h: elements lane, 32+lane, 64+lane, 96+lane; w, fr: norm weights and frequencies of the same elements.
+__device__ __forceinline__ void head_norm_rope(__half (&h)[4], bool with_norm, const __half (&w)[4], float eps,
+                                               const float (&fr)[4], int pos, int lane) {
+    if (with_norm) {
+        float part[4];
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            float val = __half2float(h[v]);
+            float local_sum = 0.0f;
+            local_sum += val * val;
+            for (int offset = 16; offset > 0; offset /= 2) local_sum += __shfl_down_sync(0xffffffffu, local_sum, offset);
+            part[v] = __shfl_sync(0xffffffffu, local_sum, 0);
+        }
+        float total_sum = (part[0] + part[2]) + (part[1] + part[3]);
+        const float rms = rsqrtf(total_sum / kHeadDim + eps);
+#pragma unroll
+        for (int v = 0; v < 4; ++v) {
+            float val = __half2float(h[v]) * rms;
+            h[v] = __float2half(val * __half2float(w[v]));
+        }
+    }
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+        float angle = fr[v] * static_cast<float>(pos);
+        float cos_a = cosf(angle), sin_a = sinf(angle);
+        const float mine = __half2float(h[v]);
+        const float other = __shfl_xor_sync(0xffffffffu, mine, 1);
+        float q0 = (lane & 1) ? other : mine, q1 = (lane & 1) ? mine : other;
+        h[v] = (lane & 1) ? __float2half(q0 * sin_a + q1 * cos_a) : __float2half(q0 * cos_a - q1 * sin_a);
+    }
 }
 
 // D(16x8, fp32) += A(16x16 fp16, rows 8..15 zero) x B(16x8 fp16). Only rows 0..7 of D are kept.
@@ -172,9 +221,16 @@ __device__ __forceinline__ uint32_t reg_of(const uint4& v, int i) {
 // "k index" of an MMA is a permutation of the real one, applied to q alike; V's token pairs are put
 // side by side with one byte-permute per register. Nothing is staged in shared memory. Each warp
 // keeps the next block's 8 KB in flight while it works on the current one.
+//
+// ROPE form: the launch also does what qknorm_rope_kvwrite_kernel does. Warps 0..3 norm and rotate the four
+// query heads into shared memory; in the CTA that attends over the block the new token joins, warps 4 and 5
+// write the new k and v rows into the cache first. The first two KV blocks of every warp are requested
+// before that work, so its latency hides under theirs.
+template <bool ROPE>
 __global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_kernel(const AttnParams p) {
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
+    __shared__ __align__(16) __half q_s[ROPE ? kQPerKv : 1][kHeadDim];
     __shared__ float red_m[kAttnWarps][kQPerKv], red_l[kAttnWarps][kQPerKv];
     __shared__ float red_acc[kAttnWarps][kQPerKv][kHeadDim];
     __shared__ float cta_m[kQPerKv], cta_l[kQPerKv];
@@ -188,15 +244,26 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_ker
     const int n_blocks = (seq_len + kBlockTokens - 1) / kBlockTokens;
     const int heads_here = p.n_q / p.n_kv;  // == kQPerKv (checked on the host)
 
-    // q of head g (rows 4..15 of the tile are zero), in the same piece order as K
-    uint32_t qa[4][4];
+    // ROPE: everything the prologue reads is requested here, before the first value is used
+    int pos = 0;
+    bool owner = false;
+    const bool role_q = warp < kQPerKv, is_k = warp == kQPerKv, is_v = warp == kQPerKv + 1;
+    __half hq[4], wq[4];
+    float fr[4];
+    const __half* norm_w = nullptr;
+    if constexpr (ROPE) {
+        pos = p.positions[b];
+        norm_w = role_q ? p.q_norm_w : p.k_norm_w;
+        const int total_heads = p.n_q + 2 * p.n_kv;
+        const __half* src = p.qkv + (static_cast<size_t>(b) * total_heads +
+                                     (role_q ? kvh * heads_here + warp : p.n_q + (is_k ? 0 : p.n_kv) + kvh)) * kHeadDim;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (g < kQPerKv)
-            v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(b) * p.n_q + kvh * heads_here + g) * kHeadDim +
-                                                (i * 4 + t) * 8);
-        qa[i][0] = v.x; qa[i][1] = v.y; qa[i][2] = v.z; qa[i][3] = v.w;
+        for (int v = 0; v < 4; ++v) {
+            hq[v] = (role_q || is_k || is_v) ? src[v * 32 + lane] : __float2half(0.0f);
+            wq[v] = norm_w ? norm_w[v * 32 + lane] : __float2half(1.0f);
+            fr[v] = p.freqs[(v * 32 + lane) >> 1];
+        }
+        owner = ((pos / kBlockTokens) % S) == s;  // this CTA attends over the block the new token joins
     }
 
     // 16-token blocks are dealt round-robin: first over the cluster's CTAs, then over the warps.
@@ -220,16 +287,56 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_ker
             const int tok = j * 8 + g;
             const __half* row = p.k_cache + base + static_cast<size_t>(tok < tokens ? tok : 0) * kHeadDim;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) f.k[j][i] = ld_stream16(row + (i * 4 + t) * 8);
+            for (int i = 0; i < 4; ++i) f.k[j][i] = ROPE ? ld_cg16(row + (i * 4 + t) * 8) : ld_stream16(row + (i * 4 + t) * 8);
         }
 #pragma unroll
         for (int q = 0; q < 4; ++q) {
             const int tok = 2 * t + (q & 1) + 8 * (q >> 1);
             const __half* row = p.v_cache + base + static_cast<size_t>(tok < tokens ? tok : 0) * kHeadDim;
 #pragma unroll
-            for (int h = 0; h < 2; ++h) f.v[q][h] = ld_stream16(row + (g + 8 * h) * 8);
+            for (int h = 0; h < 2; ++h) f.v[q][h] = ROPE ? ld_cg16(row + (g + 8 * h) * 8) : ld_stream16(row + (g + 8 * h) * 8);
         }
     };
+
+    KvFrag fa, fb;
+    const int new_bi = pos / kBlockTokens;
+    const bool pre0 = n_mine > 0 && !(ROPE && owner && first == new_bi);
+    const bool pre1 = n_mine > 1 && !(ROPE && owner && first + stride == new_bi);
+    if (pre0) load(fa, 0);
+    if (pre1) load(fb, 1);
+    if constexpr (ROPE) {
+        if (role_q || ((is_k || is_v) && owner)) {
+            if (!is_v) head_norm_rope(hq, norm_w != nullptr, wq, p.eps, fr, pos, lane);
+            if (role_q) {
+#pragma unroll
+                for (int v = 0; v < 4; ++v) q_s[warp][v * 32 + lane] = hq[v];
+            } else {
+                const int phys = p.block_table[static_cast<size_t>(b) * p.max_blocks + new_bi];
+                if (phys >= 0) {
+                    __half* dst = (is_k ? p.k_cache_w : p.v_cache_w) +
+                                  ((((static_cast<size_t>(phys) * p.n_layers + p.layer) * p.n_kv + kvh) * kBlockTokens) +
+                                   pos % kBlockTokens) * kHeadDim;
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) dst[v * 32 + lane] = hq[v];
+                }
+            }
+        }
+        __syncthreads();  // q in shared memory; the new k and v rows written (read back past L1)
+        if (n_mine > 0 && !pre0) load(fa, 0);
+        if (n_mine > 1 && !pre1) load(fb, 1);
+    }
+    // q of head g (rows 4..15 of the tile are zero), in the same piece order as K
+    uint32_t qa[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (g < kQPerKv) {
+            if constexpr (ROPE) v = *reinterpret_cast<const uint4*>(&q_s[g][(i * 4 + t) * 8]);
+            else v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(b) * p.n_q + kvh * heads_here + g) * kHeadDim +
+                                                     (i * 4 + t) * 8);
+        }
+        qa[i][0] = v.x; qa[i][1] = v.y; qa[i][2] = v.z; qa[i][3] = v.w;
+    }
 
     float m_run = -1e30f, l_run = 0.0f;
     float o[16][2];  // head g; tile n = 8h + e holds dims (2t + 8h)*8 + e and (2t + 1 + 8h)*8 + e
@@ -284,18 +391,13 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_ker
             }
     };
 
-    {
-        KvFrag fa, fb;
-        int it = 0;
-        if (n_mine > 0) load(fa, 0);
-        while (it < n_mine) {
-            if (it + 1 < n_mine) load(fb, it + 1);
-            compute(fa, it);
-            if (++it >= n_mine) break;
-            if (it + 1 < n_mine) load(fa, it + 1);
-            compute(fb, it);
-            ++it;
-        }
+    for (int it = 0; it < n_mine;) {  // fa holds block `it`, fb block `it + 1`
+        compute(fa, it);
+        if (it + 2 < n_mine) load(fa, it + 2);
+        if (++it >= n_mine) break;
+        compute(fb, it);
+        if (it + 2 < n_mine) load(fb, it + 2);
+        ++it;
     }
     // the four lanes of a quad hold the same head: their partial denominators add up
     l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
@@ -399,10 +501,39 @@ int launch_qknorm_rope_kvwrite(const __half* qkv, const __half* q_norm_w, const 
     return W8A8_OK;
 }
 
+namespace {
+int launch_attention(const AttnParams& base, int B, int splits, cudaStream_t stream);
+}
+
 int launch_paged_attention_decode(const __half* q, const __half* k_cache, const __half* v_cache,
                                   const int* block_table, const int* seq_lens, int B, int n_q, int n_kv,
                                   int max_blocks, float sm_scale, int layer, int n_layers, __half* out, int g,
                                   int8_t* Xq, float* Xs, int splits, cudaStream_t stream) {
+    AttnParams p = {};
+    p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.block_table = block_table; p.seq_lens = seq_lens;
+    p.max_blocks = max_blocks; p.n_q = n_q; p.n_kv = n_kv; p.layer = layer; p.n_layers = n_layers; p.sm_scale = sm_scale;
+    p.out = out; p.Xq = Xq; p.Xs = Xs; p.g = g;
+    return launch_attention(p, B, splits, stream);
+}
+
+int launch_qkv_attention_decode(const __half* qkv, const __half* q_norm_w, const __half* k_norm_w, float eps,
+                                const float* freqs, const int* positions, __half* k_cache, __half* v_cache,
+                                const int* block_table, const int* seq_lens, int B, int n_q, int n_kv, int max_blocks,
+                                float sm_scale, int layer, int n_layers, __half* out, int g, int8_t* Xq, float* Xs,
+                                int splits, cudaStream_t stream) {
+    AttnParams p = {};
+    p.k_cache = k_cache; p.v_cache = v_cache; p.block_table = block_table; p.seq_lens = seq_lens;
+    p.max_blocks = max_blocks; p.n_q = n_q; p.n_kv = n_kv; p.layer = layer; p.n_layers = n_layers; p.sm_scale = sm_scale;
+    p.out = out; p.Xq = Xq; p.Xs = Xs; p.g = g;
+    p.qkv = qkv; p.q_norm_w = q_norm_w; p.k_norm_w = k_norm_w; p.eps = eps; p.freqs = freqs; p.positions = positions;
+    p.k_cache_w = k_cache; p.v_cache_w = v_cache;
+    return launch_attention(p, B, splits, stream);
+}
+
+namespace {
+int launch_attention(const AttnParams& base, int B, int splits, cudaStream_t stream) {
+    const int n_q = base.n_q, n_kv = base.n_kv, g = base.g;
+    const int8_t* Xq = base.Xq;
     if (B == 0) return W8A8_OK;
     if (n_kv <= 0 || n_q != n_kv * kQPerKv)
         return fail(W8A8_ERR_UNSUPPORTED, "paged attention here handles 4 query heads per kv head (got %d / %d)", n_q, n_kv);
@@ -417,8 +548,8 @@ int launch_paged_attention_decode(const __half* q, const __half* k_cache, const 
         splits = want >= 8 ? 8 : want >= 4 ? 4 : want >= 2 ? 2 : 1;
     }
     if (splits > 8) splits = 8;
-    AttnParams p = {q, k_cache, v_cache, block_table, seq_lens, max_blocks, n_q, n_kv, layer, n_layers, sm_scale,
-                    out, Xq, Xs, g, splits};
+    AttnParams p = base;
+    p.S = splits;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(splits, n_kv, B);
     cfg.blockDim = dim3(kAttnWarps * 32, 1, 1);
@@ -432,9 +563,11 @@ int launch_paged_attention_decode(const __half* q, const __half* k_cache, const 
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled(kPdlAttn) ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, paged_attention_decode_kernel, p);
+    cudaError_t e = p.qkv ? cudaLaunchKernelEx(&cfg, paged_attention_decode_kernel<true>, p)
+                          : cudaLaunchKernelEx(&cfg, paged_attention_decode_kernel<false>, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "paged_attention_decode launch: %s", cudaGetErrorString(e));
     return W8A8_OK;
 }
+}  // namespace
 
 }  // namespace w8a8

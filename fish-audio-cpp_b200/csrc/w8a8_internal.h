@@ -97,6 +97,11 @@ int launch_paged_attention_decode(const __half* q, const __half* k_cache, const 
                                   const int* block_table, const int* seq_lens, int B, int n_q, int n_kv,
                                   int max_blocks, float sm_scale, int layer, int n_layers, __half* out, int g,
                                   int8_t* Xq, float* Xs, int splits, cudaStream_t stream);
+int launch_qkv_attention_decode(const __half* qkv, const __half* q_norm_w, const __half* k_norm_w, float eps,
+                                const float* freqs, const int* positions, __half* k_cache, __half* v_cache,
+                                const int* block_table, const int* seq_lens, int B, int n_q, int n_kv, int max_blocks,
+                                float sm_scale, int layer, int n_layers, __half* out, int g, int8_t* Xq, float* Xs,
+                                int splits, cudaStream_t stream);
 // w8a8_decode_stack.cu : a whole decode step as one persistent cooperative kernel.
 size_t decode_stack_workspace_bytes(const w8a8_decode_stack& d);
 int launch_decode_stack(const w8a8_decode_stack& d, unsigned char* workspace, size_t workspace_bytes, float* partials,

@@ -8,6 +8,8 @@
 // value that the reference would have rounded to fp16 on its way through global
 // memory is rounded to fp16 here too, so the int8 codes and the fp32 scales are
 // bit-identical to those of the unfused reference chain.
+#include <cstdlib>
+
 #include "w8a8_internal.h"
 
 namespace w8a8 {
@@ -307,6 +309,107 @@ __global__ void __launch_bounds__(1024) rowquant_fast_kernel(const RowQuantParam
     }
 }
 
+// residual add + RMSNorm + group quantiser for the decode step, in little code: 256 threads per row, the row
+// staged in shared memory, g in {64, 128, 256}, K a multiple of 256 up to 4096. The sum of squares follows the
+// reference's T-thread launch (rms_norm.cu:23-49, :69-70): real warp w plays virtual warps w*VW .. w*VW+VW-1
+// (VW = T / 256), so the normed values are the reference's; normalising and quantising then go 8 elements (one
+// 128-bit piece) per thread, the g/8 threads of a group finding its absmax with shuffles. Plain loops on purpose:
+// a launch runs this code once, and what it costs is the instruction fetch as much as the arithmetic.
+template <int GM>
+__global__ void __launch_bounds__(256) rowquant_compact_kernel(const RowQuantParams p, int T) {
+    constexpr int LANES = GM / 8, kThreads = 256;
+    __shared__ float s_red[32];
+    __shared__ __align__(16) __half row_s[4096];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int K = p.K, VW = T / kThreads, G = p.G, row = blockIdx.x;
+    const size_t base = static_cast<size_t>(row) * K;
+    const int pieces = K / 8;
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    uint4 xv[2], dv[2], wv[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int c8 = tid + i * kThreads;
+        wv[i] = __ldg(reinterpret_cast<const uint4*>(p.norm_weight) + (c8 < pieces ? c8 : 0));
+    }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {  // every load first (at most two pieces per thread)
+        const int c8 = tid + i * kThreads;
+        const int cc = c8 < pieces ? c8 : 0;
+        xv[i] = *reinterpret_cast<const uint4*>(p.x_in + base + cc * 8);
+        dv[i] = *reinterpret_cast<const uint4*>((p.residual ? p.residual : p.x_in) + base + cc * 8);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int c8 = tid + i * kThreads;
+        if (c8 < pieces) {
+            if (p.residual) {
+                __half* hx = reinterpret_cast<__half*>(&xv[i]);
+                const __half* hd = reinterpret_cast<const __half*>(&dv[i]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) hx[e] = __float2half(__half2float(hx[e]) + __half2float(hd[e]));
+                if (p.x_out) *reinterpret_cast<uint4*>(p.x_out + base + c8 * 8) = xv[i];
+            }
+            reinterpret_cast<uint4*>(row_s)[c8] = xv[i];
+        }
+    }
+    __syncthreads();
+#pragma unroll 1
+    for (int k = 0; k < VW; ++k) {
+        float local_sum = 0.0f;
+#pragma unroll 1
+        for (int e = (warp * VW + k) * 32 + lane; e < K; e += T) {
+            float val = __half2float(row_s[e]);
+            local_sum += val * val;
+        }
+        for (int offset = 16; offset > 0; offset /= 2) local_sum += __shfl_down_sync(0xffffffffu, local_sum, offset);
+        if (lane == 0) s_red[warp * VW + k] = local_sum;
+    }
+    __syncthreads();
+    float total_sum = 0.0f;
+    if (warp == 0) {
+        if (lane < T / 32) total_sum = s_red[lane];
+        for (int offset = 16; offset > 0; offset /= 2) total_sum += __shfl_down_sync(0xffffffffu, total_sum, offset);
+    }
+    __syncthreads();
+    if (tid == 0) s_red[0] = rsqrtf(total_sum / K + p.eps);
+    __syncthreads();
+    const float rms = s_red[0];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int c8 = tid + i * kThreads;
+        const bool live = c8 < pieces;  // whole warps are live or not (pieces is a multiple of 32)
+        __half* hx = reinterpret_cast<__half*>(&xv[i]);
+        const __half* hw = reinterpret_cast<const __half*>(&wv[i]);
+        float v[8], amax = 0.0f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            float val = __half2float(hx[e]) * rms;
+            hx[e] = __float2half(val * __half2float(hw[e]));
+            v[e] = __half2float(hx[e]);
+            amax = fmaxf(amax, fabsf(v[e]));
+        }
+        if (live && p.normed_out) *reinterpret_cast<uint4*>(p.normed_out + base + c8 * 8) = xv[i];
+        if (!p.Xq) continue;
+#pragma unroll
+        for (int o = LANES / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+        if (!live) continue;
+        float scale = amax / 127.0f;
+        if (scale < 1e-8f) scale = 1e-8f;
+        if ((lane & (LANES - 1)) == 0) p.Xs[static_cast<size_t>(row) * G + (c8 * 8) / GM] = scale;
+        const float inv_scale = 1.0f / scale;
+        uint32_t lo = 0, hi = 0;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+            int q = __float2int_rn(v[e] * inv_scale);
+            q = max(-127, min(127, q));
+            if (e < 4) lo |= (static_cast<uint32_t>(q) & 0xffu) << (8 * e);
+            else hi |= (static_cast<uint32_t>(q) & 0xffu) << (8 * (e - 4));
+        }
+        *reinterpret_cast<uint2*>(p.Xq + base + c8 * 8) = make_uint2(lo, hi);
+    }
+}
+
 // The quantiser alone (int8_gemm.cu:147-211) for g in {64, 128, 256}: no shared memory, no block
 // barrier. A thread owns 8 consecutive activations (one 128-bit load), the g/8 threads of a group
 // find the absmax with shuffles, and each thread stores its 8 codes as one 64-bit word. At decode
@@ -418,6 +521,28 @@ int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
         if (threads < 32) threads = 32;  // shuffles need whole warps; lanes past K add 0.0f
     } else if (K >= 4096) {
         threads = 512;
+    }
+    static const bool compact_ok = [] {
+        const char* v = std::getenv("W8A8_ROW_COMPACT");
+        return v ? (*v && *v != '0') : true;
+    }();
+    if (compact_ok && norm_weight && threads >= 256 && K % 256 == 0 && K <= 4096 && !smooth_inv && !act_scale && !p.per_token &&
+        (p.g == 64 || p.g == 128 || p.g == 256) && p.vec_ok && aligned16(norm_weight) &&
+        (!normed_out || aligned16(normed_out)) && (!Xq || (reinterpret_cast<uintptr_t>(Xq) & 7u) == 0)) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(M, 1, 1);
+        cfg.blockDim = dim3(256, 1, 1);
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = pdl_enabled(kPdlRow) ? 1 : 0;
+        cudaError_t e = p.g == 64    ? cudaLaunchKernelEx(&cfg, rowquant_compact_kernel<64>, p, threads)
+                        : p.g == 128 ? cudaLaunchKernelEx(&cfg, rowquant_compact_kernel<128>, p, threads)
+                                     : cudaLaunchKernelEx(&cfg, rowquant_compact_kernel<256>, p, threads);
+        if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "rowquant_compact launch: %s", cudaGetErrorString(e));
+        return W8A8_OK;
     }
     if (norm_weight && threads >= 32 && K <= kFastElems * threads && p.g % 32 == 0 && p.G <= 160) {
         cudaLaunchConfig_t cfg = {};

@@ -72,6 +72,8 @@ class SlowARStack:
         # On one GPU the residual add + RMSNorm + quantiser before wqkv and w13 run inside the linear's own
         # launch (w8a8_rmsnorm_linear); with TP the exchange sits in that place instead.
         self.fuse_norm = fuse_norm and tp_size == 1 and pack and os.environ.get("W8A8_STACK_FUSE_NORM", "0") == "1"
+        # qk-norm + RoPE + KV write inside the attention launch (W8A8_STACK_FUSE_ROPE=0: as two launches)
+        self.fuse_rope = os.environ.get("W8A8_STACK_FUSE_ROPE", "1") == "1"
         c = cfg
         assert c.n_kv % tp_size == 0 and c.n_head == 4 * c.n_kv and c.head_dim == 128
         g = c.group
@@ -173,7 +175,7 @@ class SlowARStack:
         self.actq = torch.empty((B, self.inter_l), dtype=torch.int8, device=dev)
         self.acts = torch.empty((B, self.inter_l // g), dtype=torch.float32, device=dev)
         self.out = torch.empty((B, c.dim), **h16)
-        self.launches_per_step = c.n_layer * (7 if self.fuse_norm else 9) + 2
+        self.launches_per_step = c.n_layer * ((7 if self.fuse_norm else 9) - (1 if self.fuse_rope else 0)) + 2
         # bytes the step must move at least once (per rank): weights + scales + the KV it reads
         wbytes = sum(lw[n].numel() + lw[s].numel() * 2 for lw in self.layers
                      for n, s in (("wqkv", "sqkv"), ("wo", "so"), ("w13", "s13"), ("w2", "s2")))
@@ -205,12 +207,19 @@ class SlowARStack:
                                      residual=self.delta if pending else None)
             if not self.fuse_norm:
                 ctx.linear_q(lw["wqkv"], lw["sqkv"], g, self.xq, self.xs, self.qkv, B, self.qkv_n, c.dim)
-            ctx.qknorm_rope_kvwrite(self.qkv, lw["q_norm"], lw["k_norm"], c.eps, self.freqs, self.positions,
-                                    self.block_table, self.max_blocks, self.k_cache, self.v_cache, l, c.n_layer, B,
-                                    self.nq_l, self.nkv_l, D, self.q)
-            ctx.paged_attention_decode(self.q, self.k_cache, self.v_cache, self.block_table, self.seq_lens, None, B,
-                                       self.nq_l, D, self.max_blocks, sm_scale, l, c.n_layer, self.nkv_l,
-                                       quant_group_size=g, Xq=self.aq, Xs=self.as_, context_splits=self.attn_splits)
+            if self.fuse_rope:
+                ctx.qkv_attention_decode(self.qkv, lw["q_norm"], lw["k_norm"], c.eps, self.freqs, self.positions,
+                                         self.k_cache, self.v_cache, self.block_table, self.seq_lens, None, B, self.nq_l,
+                                         D, self.max_blocks, sm_scale, l, c.n_layer, self.nkv_l, quant_group_size=g,
+                                         Xq=self.aq, Xs=self.as_, context_splits=self.attn_splits)
+            else:
+                ctx.qknorm_rope_kvwrite(self.qkv, lw["q_norm"], lw["k_norm"], c.eps, self.freqs, self.positions,
+                                        self.block_table, self.max_blocks, self.k_cache, self.v_cache, l, c.n_layer, B,
+                                        self.nq_l, self.nkv_l, D, self.q)
+                ctx.paged_attention_decode(self.q, self.k_cache, self.v_cache, self.block_table, self.seq_lens, None, B,
+                                           self.nq_l, D, self.max_blocks, sm_scale, l, c.n_layer, self.nkv_l,
+                                           quant_group_size=g, Xq=self.aq, Xs=self.as_,
+                                           context_splits=self.attn_splits)
             ctx.linear_q(lw["wo"], lw["so"], g, self.aq, self.as_, self.delta, B, c.dim, self.attn_k)
             if self.all_reduce is not None:
                 self.all_reduce(self.delta)

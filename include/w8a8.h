@@ -207,6 +207,18 @@ W8A8_API int w8a8_paged_attention_decode(w8a8_ctx* ctx, const void* q, const voi
                                 int quant_group_size, void* Xq, void* Xs, int context_splits,
                                 void* stream);
 
+/* w8a8_qknorm_rope_kvwrite and w8a8_paged_attention_decode as ONE launch (same arguments, q never leaves the
+ * chip): each (sequence, kv head) CTA group norms and rotates its four query heads itself, the CTA that attends
+ * over the block the new token joins writes the new k and v rows first. Same arithmetic and rounding points as
+ * the two calls, so outputs, codes, scales and cache contents are theirs bit for bit. seq_lens must count the
+ * new token (positions[b] + 1 in a plain decode step). */
+W8A8_API int w8a8_qkv_attention_decode(w8a8_ctx* ctx, const void* qkv, const void* q_norm_w,
+                              const void* k_norm_w, float eps, const float* freqs, const int* positions,
+                              void* k_cache, void* v_cache, const int* block_table, const int* seq_lens,
+                              void* out, int batch, int n_heads, int head_dim, int max_blocks_per_seq,
+                              float sm_scale, int layer, int n_layers, int n_kv_heads, int quant_group_size,
+                              void* Xq, void* Xs, int context_splits, void* stream);
+
 /* ---- one decode step of the whole stack as one launch ------------------------------------------ */
 
 typedef struct w8a8_decode_layer {

@@ -95,3 +95,44 @@ def test_paged_attention_decode(ctx, oracle, B, lens, splits):
                                        rout.data_ptr(), B, N_Q, D, max_blocks, sm, layer, LAYERS, N_KV)
         torch.cuda.synchronize()
         assert (rout.float() - dout.float()).abs().max().item() <= 2e-3 * max(1.0, rout.float().abs().max().item())
+
+
+@pytest.mark.parametrize("B,positions", [(1, [0]), (3, [15, 16, 40]), (8, [1024] * 8), (4, [4, 299, 31, 999])])
+@pytest.mark.parametrize("splits", [0, 1, 2, 3])
+def test_qkv_attention_decode_equals_the_two_calls(ctx, B, positions, splits):
+    """qk-norm + RoPE + KV write + attention (+ quantiser) as one launch against the two launches: attention
+    output, codes, scales and both caches bit for bit."""
+    rng = np.random.default_rng(B + sum(positions))
+    layer, max_blocks, g = 1, 128, 256
+    kc, vc, bt = make_cache(rng, B, max(positions) + 1, max_blocks)
+    qkv = rng.standard_normal((B, (N_Q + 2 * N_KV) * D)).astype(np.float16)
+    qw = rng.uniform(0.5, 1.5, D).astype(np.float16)
+    kw = rng.uniform(0.5, 1.5, D).astype(np.float16)
+    freqs = (1.0 / np.power(np.float32(1e6), np.float32(2.0) * np.arange(D // 2, dtype=np.float32) / np.float32(D))
+             ).astype(np.float32)
+    pos = np.array(positions, np.int32)
+    dqkv, dqw, dkw, dfr, dpos, dbt = dev(qkv), dev(qw), dev(kw), dev(freqs), dev(pos), dev(bt)
+    dseq = dev(pos + 1)
+    sm = 1.0 / np.sqrt(D)
+
+    def run(fused):
+        dk, dv = dev(kc), dev(vc)
+        out = torch.full((B, N_Q, D), 7.0, dtype=torch.float16, device="cuda")
+        xq = torch.full((B, N_Q * D), 99, dtype=torch.int8, device="cuda")
+        xs = torch.full((B, N_Q * D // g), -1.0, dtype=torch.float32, device="cuda")
+        if fused:
+            ctx.qkv_attention_decode(dqkv, dqw, dkw, 1e-6, dfr, dpos, dk, dv, dbt, dseq, out, B, N_Q, D, max_blocks, sm,
+                                     layer, LAYERS, N_KV, quant_group_size=g, Xq=xq, Xs=xs, context_splits=splits)
+        else:
+            dq = torch.empty((B, N_Q, D), dtype=torch.float16, device="cuda")
+            ctx.qknorm_rope_kvwrite(dqkv, dqw, dkw, 1e-6, dfr, dpos, dbt, max_blocks, dk, dv, layer, LAYERS, B, N_Q, N_KV,
+                                    D, dq)
+            ctx.paged_attention_decode(dq, dk, dv, dbt, dseq, out, B, N_Q, D, max_blocks, sm, layer, LAYERS, N_KV,
+                                       quant_group_size=g, Xq=xq, Xs=xs, context_splits=splits)
+        torch.cuda.synchronize()
+        return out, xq, xs, dk, dv
+
+    want, got = run(False), run(True)
+    for w, gt, what in zip(want, got, ("attention output", "codes", "scales", "k cache", "v cache")):
+        assert torch.equal(w.view(torch.uint8) if w.dtype != torch.int8 else w, gt.view(torch.uint8) if gt.dtype != torch.int8 else gt), what
+    assert not torch.equal(got[3], dev(kc)), "the new k rows were written"
