@@ -14,11 +14,17 @@
 //     [16 rows][groups per block] fp16              the block's weight scales (32, 64 or 128 bytes)
 //   blocks ordered rt-major, kb ascending, one after another with no gaps.
 //
-// The stream-K range of a warp (w*U/W .. (w+1)*U/W units) is then ONE contiguous byte range: the warp
+// Work split: whole 16-row tiles per CTA (tile t of T goes to CTA t * C / T), the CTA's units of 256 K-bytes
+// in equal contiguous runs to its eight warps. A warp's run is then ONE contiguous byte range: the warp
 // pulls it through a private ring of shared-memory stages with 1-D bulk copies (cp.async.bulk, one
 // block per copy, completion on an mbarrier), reads its fragments back with conflict-free 128-bit
 // shared loads, and finds the scales in the same stage — no strided access, no separate scale
 // traffic, no tensor map. Rows past N are stored as zeros, so no tail handling is needed on loads.
+// A row tile cut by a run boundary is always cut between warps of one CTA: its fp32 partial tiles meet in
+// shared memory and the warp that arrives last adds them in ascending-K order. (An earlier form cut one
+// global range over all warps of the grid and fixed cut tiles up through global scratch and L2 atomics:
+// perfectly balanced, but two to three L2 round trips at the tail of every launch; measured 2 us slower
+// per launch on the decode shapes than the at most one-tile imbalance of this form.)
 //
 // Launched with programmatic dependent launch: the first kStages blocks are requested before
 // griddepcontrol.wait. Every mbarrier wait is bounded; on expiry the warp records an error word.
@@ -45,9 +51,6 @@ struct GemvPackedParams {
     int upt;          // units per 16-row tile
     int bpu;          // blocks per unit (1, or g / 256 when g > 256)
     unsigned U;       // units in all
-    int NW;           // warps that take part
-    float* partials;
-    int* counters;
     int* status;
 };
 
@@ -108,10 +111,19 @@ gemv_packed_kernel(const GemvPackedParams p) {
     __shared__ int cnt_s[kLocalTiles];
     for (int i = threadIdx.x; i < kLocalTiles; i += kThreads) cnt_s[i] = 0;
     __syncthreads();
-    const unsigned gw = blockIdx.x * kWarps + warp;
-    const unsigned NW = p.NW, U = p.U;
-    const unsigned u0 = gw * U / NW, u1 = (gw + 1) * U / NW;
-    const int T = gw < NW ? static_cast<int>(u1 - u0) * p.bpu : 0;  // blocks
+    // Whole 16-row tiles per CTA (tile t of `tiles` goes to CTA t * C / tiles), the CTA's units in equal contiguous
+    // runs to its warps (none with an empty run): a tile cut by a run boundary is always cut between warps of
+    // this CTA.
+    const unsigned tiles = p.U / p.upt;
+    const unsigned ct0 = blockIdx.x * tiles / gridDim.x, ct1 = (blockIdx.x + 1) * tiles / gridDim.x;
+    const unsigned cu0 = ct0 * p.upt, n_cta = (ct1 - ct0) * p.upt;
+    const unsigned nw_cta = n_cta < kWarps ? n_cta : kWarps;
+    unsigned u0 = cu0, u1 = cu0;
+    if (static_cast<unsigned>(warp) < nw_cta) {
+        u0 = cu0 + warp * n_cta / nw_cta;
+        u1 = cu0 + (warp + 1) * n_cta / nw_cta;
+    }
+    const int T = static_cast<int>(u1 - u0) * p.bpu;  // blocks
 
     const uint32_t ring = ((ptx::smem_u32(smem_raw) + 127u) & ~127u) + warp * kRingBytes;
     uint64_t* bar = bars[warp];
@@ -332,29 +344,20 @@ gemv_packed_kernel(const GemvPackedParams p) {
         }
     };
 
-    auto warp_of_unit = [&](unsigned u) -> unsigned {  // the warp whose range holds unit u
-        return ((u + 1) * NW - 1) / U;
+    auto warp_of_unit = [&](unsigned u) -> unsigned {  // the warp of this CTA whose run holds unit u
+        return ((u - cu0 + 1) * nw_cta - 1) / n_cta;
     };
+    const int cta_rt0 = static_cast<int>(ct0);
 
-    // A tile cut by a range boundary: the warp parks its fp32 partial in scratch and bumps the tile's
-    // arrival counter with a release atomic WITHOUT waiting for the answer (a wait here would stall
-    // the warp's stream for two memory round trips in the middle of its range). The answer is looked
-    // at after the last block: whichever contributor arrived last adds all partials in ascending-K
-    // order and stores. A warp has at most two such tiles (the first and the last of its range).
-    constexpr int kSlot = MT * 4 * 32;
-    const int cta_rt0 = static_cast<int>((blockIdx.x * kWarps * U / NW) / p.upt);  // the CTA's first row tile
-    int pend_rt[2];
-    unsigned pend_old[2];
-    int npend = 0;
-
-    // Called when the warp has added its last unit of row tile rt into acc.
+    // Called when the warp has added its last unit of row tile rt into acc. A cut tile: the fp32 partial goes to
+    // the warp's slot in shared memory, the arrival is counted, and whichever warp arrives last adds the
+    // partials in ascending-K order and stores. Nothing waits; nothing leaves the SM.
     auto finish_tile = [&](int rt) {
         const unsigned t_lo = static_cast<unsigned>(rt) * p.upt, t_hi = t_lo + p.upt;  // [t_lo, t_hi)
         if (u0 <= t_lo && t_hi <= u1) {
             store_tile(rt, acc);
-        } else if (const unsigned first = warp_of_unit(t_lo), last = warp_of_unit(t_hi - 1);
-                   first / kWarps == last / kWarps && rt - cta_rt0 < kLocalTiles) {
-            // every contributor is a warp of this CTA: partials and the arrival counter in shared memory
+        } else {
+            const unsigned first = warp_of_unit(t_lo), last = warp_of_unit(t_hi - 1);
             const int my_slot = (static_cast<int>(u0 / p.upt) == rt) ? 0 : 1;
             float* mine = red_s[warp][my_slot];
 #pragma unroll
@@ -368,7 +371,7 @@ gemv_packed_kernel(const GemvPackedParams p) {
                 old = atomicAdd(&cnt_s[rt - cta_rt0], 1);
             }
             old = __shfl_sync(0xffffffffu, old, 0);
-            if (old == static_cast<int>(last - first)) {  // the last to arrive adds in ascending-K order
+            if (old == static_cast<int>(last - first)) {
                 __threadfence_block();
                 float sum[MT][4];
 #pragma unroll
@@ -376,8 +379,8 @@ gemv_packed_kernel(const GemvPackedParams p) {
 #pragma unroll
                     for (int r = 0; r < 4; ++r) sum[nt][r] = 0.0f;
                 for (unsigned ww = first; ww <= last; ++ww) {
-                    const int slot = (static_cast<int>((ww * U / NW) / p.upt) == rt) ? 0 : 1;
-                    const float* src = red_s[ww - blockIdx.x * kWarps][slot];
+                    const unsigned wu0 = cu0 + ww * n_cta / nw_cta;
+                    const float* src = red_s[ww][(static_cast<int>(wu0 / p.upt) == rt) ? 0 : 1];
 #pragma unroll
                     for (int nt = 0; nt < MT; ++nt)
 #pragma unroll
@@ -385,61 +388,11 @@ gemv_packed_kernel(const GemvPackedParams p) {
                 }
                 store_tile(rt, sum);
             }
-        } else {
-            const int my_slot = (static_cast<int>(u0 / p.upt) == rt) ? 0 : 1;
-            float* mine = p.partials + (static_cast<size_t>(gw) * 2 + my_slot) * kSlot;
-#pragma unroll
-            for (int nt = 0; nt < MT; ++nt)
-#pragma unroll
-                for (int r = 0; r < 4; ++r) mine[(nt * 4 + r) * 32 + lane] = acc[nt][r];
-            __syncwarp();  // orders the other lanes' stores before lane 0's release
-            unsigned old = 0;
-            if (lane == 0)
-                asm volatile("atom.add.release.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(p.counters + rt) : "memory");
-            if (npend == 0) { pend_rt[0] = rt; pend_old[0] = old; } else { pend_rt[1] = rt; pend_old[1] = old; }
-            ++npend;
         }
 #pragma unroll
         for (int nt = 0; nt < MT; ++nt)
 #pragma unroll
             for (int r = 0; r < 4; ++r) acc[nt][r] = 0.0f;
-    };
-
-    auto resolve_pending = [&](int rt, unsigned old_lane0) {
-        const unsigned t_lo = static_cast<unsigned>(rt) * p.upt, t_hi = t_lo + p.upt;
-        const unsigned first = warp_of_unit(t_lo), last = warp_of_unit(t_hi - 1);
-        const unsigned old = __shfl_sync(0xffffffffu, old_lane0, 0);
-        if (old != last - first) return;  // somebody else arrives later and does it
-        __threadfence();                  // acquire: the other contributors' partials
-        float sum[MT][4];
-#pragma unroll
-        for (int nt = 0; nt < MT; ++nt)
-#pragma unroll
-            for (int r = 0; r < 4; ++r) sum[nt][r] = 0.0f;
-        // four contributors' loads are in flight at a time; the adds stay in ascending-K order
-        for (unsigned w = first; w <= last; w += 4) {
-            float v[4][MT][4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-                const unsigned ww = w + q <= last ? w + q : last;
-                const int slot = (static_cast<int>((ww * U / NW) / p.upt) == rt) ? 0 : 1;
-                const float* src = p.partials + (static_cast<size_t>(ww) * 2 + slot) * kSlot;
-#pragma unroll
-                for (int nt = 0; nt < MT; ++nt)
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) v[q][nt][r] = ld_cg(src + (nt * 4 + r) * 32 + lane);
-            }
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-                if (w + q <= last) {
-#pragma unroll
-                    for (int nt = 0; nt < MT; ++nt)
-#pragma unroll
-                        for (int r = 0; r < 4; ++r) sum[nt][r] += v[q][nt][r];
-                }
-        }
-        store_tile(rt, sum);
-        if (lane == 0) p.counters[rt] = 0;  // ready for the next launch
     };
 
     auto promote = [&](int rt, int j, __half hsa, __half hsb, const float (&xsv)[MT][2]) {
@@ -545,10 +498,11 @@ gemv_packed_kernel(const GemvPackedParams p) {
         if (++si == p.bpu) {
             si = 0;
             if (GM == 256) promote(rt, ub, sa[0], sb[0], xsc[0]);
-            if (++ub == p.upt) {
+            // one call site for the tile end: the row tile is complete, or the range ends inside it
+            ++ub;
+            if (ub == p.upt || t + 1 == T) {
                 finish_tile(rt);
-                ub = 0;
-                ++rt;
+                if (ub == p.upt) { ub = 0; ++rt; }
             }
 #pragma unroll
             for (int q = 0; q < GPU; ++q)
@@ -559,11 +513,6 @@ gemv_packed_kernel(const GemvPackedParams p) {
         for (int ch = 0; ch < 4; ++ch)
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt) xc[ch][nt] = xn[ch][nt];
-    }
-    if (ok && T > 0 && ub != 0) finish_tile(rt);  // the range ended inside a tile
-    if (ok) {
-        if (npend > 0) resolve_pending(pend_rt[0], pend_old[0]);
-        if (npend > 1) resolve_pending(pend_rt[1], pend_old[1]);
     }
     if (!ok) {
         // Leave only once every requested block has landed (or a second bounded wait ran out): a TMA write
@@ -577,7 +526,6 @@ gemv_packed_kernel(const GemvPackedParams p) {
 struct Plan {
     int MT, GM, upt, bpu, block_bytes, tiles, ctas;
     long long U;
-    size_t partial_bytes;
 };
 
 int num_sms() {
@@ -618,7 +566,6 @@ bool make_plan(const LinearArgs& a, Plan& pl) {
         if (reinterpret_cast<uintptr_t>(a.Xq) & 15u) return false;
     }
     if (a.epilogue == W8A8_EPI_SWIGLU && a.N % 16 != 0) return false;
-    if (!a.splitk_partials || !a.splitk_counters) return false;
     pl.MT = a.M <= 8 ? 1 : (a.M <= 16 ? 2 : 4);
     pl.GM = a.g == 64 ? 64 : a.g == 128 ? 128 : 256;
     pl.bpu = a.g > 256 ? a.g / 256 : 1;
@@ -626,13 +573,11 @@ bool make_plan(const LinearArgs& a, Plan& pl) {
     pl.block_bytes = kBlockW + 32 * (a.g >= 256 ? 1 : 256 / a.g);
     pl.tiles = (a.N + 15) / 16;
     pl.U = static_cast<long long>(pl.tiles) * pl.upt;
-    // One CTA per SM (two were measured no faster). The warp ranges are then those of the one-launch decode
-    // step, whose results are the same bit for bit.
-    pl.ctas = num_sms();
+    // One CTA per SM (two were measured no faster), never more CTAs than row tiles. The warp runs are then those
+    // of the one-launch decode step, whose results are the same bit for bit.
+    pl.ctas = pl.tiles < num_sms() ? pl.tiles : num_sms();
     if ((pl.U + 1) * static_cast<long long>(pl.ctas) * kWarps >= (1ll << 32)) return false;  // 32-bit range math
-    pl.partial_bytes = static_cast<size_t>(pl.ctas) * kWarps * 2 * pl.MT * 4 * 32 * sizeof(float);
-    if (pl.partial_bytes > a.splitk_partial_bytes) return false;
-    if (static_cast<size_t>(pl.tiles) > a.splitk_counter_count) return false;
+    if (pl.tiles / pl.ctas + 2 > kLocalTiles) return false;  // arrival counters of a CTA's tiles sit in shared memory
     return true;
 }
 
@@ -645,9 +590,6 @@ int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_
     p.upt = pl.upt;
     p.bpu = pl.bpu;
     p.U = static_cast<unsigned>(pl.U);
-    p.NW = static_cast<int>(pl.U < static_cast<long long>(pl.ctas) * kWarps ? pl.U : pl.ctas * kWarps);
-    p.partials = static_cast<float*>(a.splitk_partials);
-    p.counters = a.splitk_counters;
     p.status = status;
     auto kern = gemv_packed_kernel<MT, GM, FUSED>;
     const size_t smem = static_cast<size_t>(kWarps) * kRingBytes + 128 + (FUSED ? fused_smem_bytes(a.K, a.G) : 0);
