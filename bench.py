@@ -37,11 +37,11 @@ def peaks():
 
 # DRAM traffic / algorithmic bytes of the dominant kernels, from one ncu capture each (dram__bytes_read.sum +
 # dram__bytes_write.sum of a launch, summaries under profiles/): gemv_packed_kernel on gate_up M=1 g=256 moved
-# 50.274 MB against 50.241 MB; gemm_i8_kernel on gate_up M=2048 g=256 moved 130.8 MB against 135.2 MB (weights,
+# 50.249 MB against 50.241 MB; gemm_i8_kernel on gate_up M=2048 g=256 moved 130.8 MB against 135.2 MB (weights,
 # scales, codes and activation scales in, fp16 out; part of the output was still in L2 when the kernel ended).
 # Traffic of both grows in proportion to the bytes a launch touches, so a launch's traffic is that ratio times
 # its own algorithmic bytes.
-GEMV_TRAFFIC_RATIO = 50.274 / 50.241
+GEMV_TRAFFIC_RATIO = 50.249 / 50.241
 GEMM_TRAFFIC_RATIO = 130.8 / 135.2
 
 
@@ -779,7 +779,7 @@ def main():
                                 "frac": round(ach / pk["hbm_gbs"], 4),
                                 "traffic": int(GEMV_TRAFFIC_RATIO * lin[1]),
                                 "traffic_source": "algorithmic bytes per launch scaled by the DRAM/algorithmic ratio of "
-                                                  "one ncu capture (gate_up M=1 g=256)",
+                                                  "one ncu capture (w1|w3 at M=8 g=256)",
                                 "peak_source": pk["source"],
                                 "kernel": "gemv_packed_kernel (the 4 linears of each layer, timed alone)",
                                 "algorithmic_bytes_per_launch": int(lin[1]), "us_per_launch": round(lin_s * 1e6, 2)}
