@@ -11,9 +11,9 @@
 // arriving. Barriers stall arithmetic, not the HBM stream.
 //
 // The arithmetic of every phase is that of the stand-alone kernels (w8a8_quant.cu, w8a8_gemv_packed.cu,
-// w8a8_attn.cu), operation for operation. One thing differs: where a linear's K range is cut between warps
-// (whole row tiles per CTA here, one global split there), so its fp32 partial sums are added in a different
-// grouping; int8 codes, scales and int32 group sums are the same.
+// w8a8_attn.cu), operation for operation. One thing differs: how many CTAs share a linear's row tiles (one per
+// SM here, up to two per SM there), hence where its K range is cut between warps and how its fp32 partial sums
+// are grouped; int8 codes, scales and int32 group sums are the same.
 //
 //   per layer:  A  x += delta; RMSNorm; quantise            (CTA r = token row r)       | barrier
 //               B  qkv = W8A8 linear(wqkv)                  (all warps, stream-K)        | barrier

@@ -86,6 +86,7 @@ int launch_linear_gemv_tma(const LinearArgs& a, int* device_status, cudaStream_t
 // w8a8_gemv_packed.cu : M <= 32 over pre-packed weights (linear byte stream, 1-D bulk copies).
 size_t packed_weight_bytes(int N, int K, int g);
 int launch_pack_weight(const int8_t* W, const __half* S, int N, int K, int g, void* out, cudaStream_t s);
+int gemv_packed_ctas(int tiles, int sms, bool two_per_sm);  // CTAs that share a linear's row tiles
 bool gemv_packed_supports(const LinearArgs& a);  // also answers for the fused-prologue form (a.norm_weight set)
 int launch_linear_gemv_packed(const LinearArgs& a, int* device_status, cudaStream_t s);
 // w8a8_attn.cu : decode-step neighbours (qk-norm + RoPE + KV write; paged attention).

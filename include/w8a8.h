@@ -257,8 +257,9 @@ W8A8_API size_t w8a8_decode_stack_workspace_bytes(const w8a8_decode_stack* stack
  * warps stream the weights of all linears without interruption; phases are separated by grid
  * barriers with bounded waits (W8A8_ERR_TIMEOUT through w8a8_check_device_status when one runs out).
  * The arithmetic is that of this library's separate calls: int8 codes, scales and int32 group sums are
- * the same; a linear's fp32 partial sums are grouped differently (whole row tiles per CTA), so its fp16
- * outputs may differ from the separate calls' in the last bit. The
+ * the same; a linear's fp32 partial sums are grouped differently (its row tiles are shared by one CTA per
+ * SM here, by up to two in a separate call), so its fp16 outputs may differ from the separate calls' in
+ * the last bit. The
  * descriptor is read on the host during the call; `layers` must stay valid on the device until the
  * step has run. */
 W8A8_API int w8a8_decode_stack_step(w8a8_ctx* ctx, const w8a8_decode_stack* stack, void* stream);

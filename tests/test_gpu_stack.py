@@ -89,8 +89,13 @@ def test_stack_matches_oracle_chain(ctx, oracle, group, dim):
     (256, 2560, 8, 9728, 1, 8, 1024)])
 def test_one_launch_step_matches_the_chain_of_launches(ctx, group, dim, n_kv, inter, layers, B, context):
     """w8a8_decode_stack_step (one persistent cooperative kernel) against decode_step (eight launches per
-    layer) from the same state, two steps: both deal a linear's row tiles and K runs to warps in the same way
-    and run the same arithmetic, so the hidden state and both KV caches agree bit for bit."""
+    layer) from the same state, two steps. Both run the same arithmetic; the one difference is how many CTAs
+    share a linear's row tiles (148 there, up to 296 in the separate launches), hence where its K range is cut
+    between warps, i.e. the grouping of its fp32 partial sums, so outputs of a
+    linear may differ in the last fp16 bit and, now and then, a quantiser after it flips a code. The bars:
+    hidden state within 2e-2 in relative L2 norm after several layers; the KV rows written by layer 0 within
+    3 fp16 ulp for at least 99 % of the elements and never beyond 1e-2 of the largest value; all KV rows
+    within 2e-2 in relative L2 norm."""
     cfg = S.SlowARConfig(n_layer=layers, dim=dim, n_head=4 * n_kv, n_kv=n_kv, inter=inter, group=group)
     st = S.SlowARStack(torch, ctx, cfg, B, context, max_new=8, seed=11)
     need = ctx.decode_stack_workspace_bytes(st.one_launch_descriptor())
@@ -112,11 +117,19 @@ def test_one_launch_step_matches_the_chain_of_launches(ctx, group, dim, n_kv, in
         st.decode_step_one_launch(x_in)
         torch.cuda.synchronize()
         ctx.check_device_status()
-        assert torch.equal(st.out.float(), out_w), "final-normed hidden state"
+        got = st.out.float()
+        rel = ((got - out_w).norm() / out_w.norm()).item()
+        assert rel < 2e-2, rel
         outs.append(st.out.clone())
-    assert torch.equal(st.k_cache.view(torch.int16), kw.view(torch.int16))
-    assert torch.equal(st.v_cache.view(torch.int16), vw.view(torch.int16))
-    assert not torch.equal(kw, k0)
+    for got_c, want_c, before in ((st.k_cache, kw, k0), (st.v_cache, vw, v0)):
+        assert (want_c != before).any()
+        # layer 0 sees the same hidden state in both forms: its new rows differ by last-bit effects only
+        g0, w0 = got_c[:, 0].float(), want_c[:, 0].float()
+        assert (g0 - w0).abs().max().item() <= 1e-2 * w0.abs().max().item()
+        ulp = (got_c[:, 0].contiguous().view(torch.int16).int() - want_c[:, 0].contiguous().view(torch.int16).int()).abs()
+        assert (ulp <= 3).float().mean().item() >= 0.99
+        # deeper layers inherit the hidden state's difference
+        assert ((got_c.float() - want_c.float()).norm() / want_c.float().norm()).item() < 2e-2
     # the step is deterministic: the same inputs from the same state give the same bits
     st.reset_positions()
     st.k_cache.copy_(k0); st.v_cache.copy_(v0)
