@@ -61,7 +61,7 @@ class SlowARStack:
         self.torch, self.ctx, self.cfg = torch, ctx, cfg
         self.B, self.tp_rank, self.tp_size = batch, tp_rank, tp_size
         self.all_reduce = all_reduce
-        self.attn_splits = attn_splits
+        self.attn_splits = int(os.environ.get("W8A8_STACK_ATTN_SPLITS", attn_splits))
         # "fused": the exchange happens inside the residual+norm+quant kernel over peer memory;
         # "nccl": a library all-reduce between the projection and that kernel (the baseline).
         self.tp_fused = tp_size > 1 and tp_mode == "fused"
