@@ -241,7 +241,15 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_ker
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
     const int seq_len = p.seq_lens[b];
-    const int n_blocks = (seq_len + kBlockTokens - 1) / kBlockTokens;
+    // 16-token blocks are dealt round-robin: first over the cluster's CTAs, then over the warps. The physical
+    // numbers of this warp's next 32 blocks, one per lane, are requested before seq_len is used anywhere (the
+    // read is bounded by the table's width), so that the two reads are one round trip, not two.
+    const int stride = S * kAttnWarps, first = s + warp * S;
+    auto fetch_phys = [&](int it0) -> int {
+        const int bi = first + (it0 + lane) * stride;
+        return bi < p.max_blocks ? p.block_table[static_cast<size_t>(b) * p.max_blocks + bi] : 0;
+    };
+    int phys_mine = fetch_phys(0);
     const int heads_here = p.n_q / p.n_kv;  // == kQPerKv (checked on the host)
 
     // ROPE: everything the prologue reads is requested here, before the first value is used
@@ -266,15 +274,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_ker
         owner = ((pos / kBlockTokens) % S) == s;  // this CTA attends over the block the new token joins
     }
 
-    // 16-token blocks are dealt round-robin: first over the cluster's CTAs, then over the warps.
-    const int stride = S * kAttnWarps, first = s + warp * S;
+    const int n_blocks = (seq_len + kBlockTokens - 1) / kBlockTokens;
     const int n_mine = first < n_blocks ? (n_blocks - first + stride - 1) / stride : 0;
-    // physical block numbers of this warp's next 32 blocks, one per lane
-    auto fetch_phys = [&](int it0) -> int {
-        const int bi = first + (it0 + lane) * stride;
-        return bi < n_blocks ? p.block_table[static_cast<size_t>(b) * p.max_blocks + bi] : 0;
-    };
-    int phys_mine = fetch_phys(0);
 
     auto load = [&](KvFrag& f, int it) {
         if ((it & 31) == 0 && it > 0) phys_mine = fetch_phys(it);
