@@ -820,7 +820,7 @@ def main():
                      "frac": round(achieved / pk["hbm_gbs"], 4),
                      "traffic": None if reference else int(GEMV_TRAFFIC_RATIO * per_launch_bytes),
                      "peak_source": pk["source"],
-                     "kernel": "gemv_kernel" if not reference else "reference kernels",
+                     "kernel": "gemv_packed_kernel" if not reference else "reference kernels",
                      "algorithmic_bytes_per_launch": int(per_launch_bytes)},
         "clocks": clocks,
         "gpu_launches": wl.launches_per_step * args.steps,
