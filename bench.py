@@ -457,6 +457,99 @@ class DecodeStack:
         return []
 
 
+class FastARFrame:
+    """configs[4]: the fast-AR codebook decoder. One step = one frame: 10 codebook steps, each a 4-layer stack
+    (hidden 2560, 32q/8kv x128, SwiGLU 9728, no qk-norm, W8A8 g64) at batch 8 over the codebooks decoded so far
+    (the mirror of DualAREngine::fast_codebook_decode_device, src/engine/dual_ar_engine.cc:769-844), then the final
+    norm and the codebook head 2560 -> 4096 (g64). Sampling and the embedding lookup of the sampled code are left
+    out: every codebook step gets the same synthetic input rows. The frame is replayed from one CUDA graph.
+    `lm_head()` times the slow AR's int8 LM head 2560 -> 155776 (g256) at M = 1 and 8 on the side."""
+
+    def __init__(self, torch, ctx, batch=8, codebooks=10):
+        from fish_audio_cpp_b200 import stack as S, synth
+
+        self.torch, self.ctx, self.batch, self.codebooks = torch, ctx, batch, codebooks
+        cfg = S.SlowARConfig(n_layer=4, group=64, qk_norm=False)
+        self.cfg = cfg
+        self.st = S.SlowARStack(torch, ctx, cfg, batch, 0, max_new=32, seed=17)
+        gen = torch.Generator(device="cuda").manual_seed(5)
+        self.head_w = torch.randint(-127, 128, (4096, cfg.dim), dtype=torch.int8, device="cuda", generator=gen)
+        self.head_s = torch.empty((4096, cfg.dim // 64), dtype=torch.float32, device="cuda").uniform_(
+            1e-3, 5e-3, generator=gen).half()
+        P = torch.empty((ctx.packed_weight_bytes(4096, cfg.dim, 64),), dtype=torch.uint8, device="cuda")
+        ctx.pack_weight(self.head_w, self.head_s, 4096, cfg.dim, 64, P)
+        ctx.register_packed_weight(self.head_w, P)
+        self._keep = [P]
+        self.logits = torch.empty((batch, 4096), dtype=torch.float16, device="cuda")
+        self.host_x = (torch.randn((batch, cfg.dim), generator=torch.Generator().manual_seed(3)) * 0.5).half().pin_memory()
+        self.dev_x = self.host_x.cuda()
+        self.host_logits = torch.empty((batch, 4096), dtype=torch.float16).pin_memory()
+        self.graphs, self.eager, self.split_k, self.cases = {}, False, 0, []
+        self.launches_per_step = codebooks * (self.st.launches_per_step + 2)
+        self.h2d, self.d2h = self.host_x.numel() * 2, self.host_logits.numel() * 2
+        head_bytes = self.head_w.numel() + self.head_s.numel() * 2
+        kv = sum(2 * batch * (t + 1) * cfg.n_layer * cfg.n_kv * cfg.head_dim * 2 for t in range(codebooks))
+        self.bytes_per_step = codebooks * (self.st.weight_bytes + head_bytes) + kv
+        self.ops_per_step = codebooks * 2 * batch * (sum(lw[n].numel() for lw in self.st.layers
+                                                           for n in ("wqkv", "wo", "w13", "w2")) + self.head_w.numel())
+
+    def body(self, e2e):
+        if e2e:
+            self.dev_x.copy_(self.host_x, non_blocking=True)
+        for _ in range(self.codebooks):
+            out = self.st.decode_step(self.dev_x)
+            self.ctx.linear(self.head_w, self.head_s, 64, out, self.logits, self.batch, 4096, self.cfg.dim)
+        self.st.reset_positions()
+        if e2e:
+            self.host_logits.copy_(self.logits, non_blocking=True)
+
+    def step(self, e2e=False):
+        t = self.torch
+        if self.eager:
+            self.body(e2e)
+        else:
+            if e2e not in self.graphs:
+                self.body(e2e)
+                t.cuda.synchronize()
+                gr = t.cuda.CUDAGraph()
+                with t.cuda.graph(gr):
+                    self.body(e2e)
+                self.graphs[e2e] = gr
+            self.graphs[e2e].replay()
+        if e2e:
+            t.cuda.current_stream().synchronize()
+
+    def per_case(self, min_ms=3.0):
+        return []
+
+    def lm_head(self, vocab=155776, reps=20):
+        """The slow AR's LM head as an int8 linear (the reference keeps it fp16: tools/quant_utils.py:37-52), M = 1
+        and 8, g256, packed: microseconds and GB/s of algorithmic bytes, weights (399 MB) larger than L2."""
+        t, ctx, K = self.torch, self.ctx, self.cfg.dim
+        gen = t.Generator(device="cuda").manual_seed(9)
+        W = t.randint(-127, 128, (vocab, K), dtype=t.int8, device="cuda", generator=gen)
+        Sc = t.empty((vocab, K // 256), dtype=t.float32, device="cuda").uniform_(1e-3, 5e-3, generator=gen).half()
+        P = t.empty((ctx.packed_weight_bytes(vocab, K, 256),), dtype=t.uint8, device="cuda")
+        ctx.pack_weight(W, Sc, vocab, K, 256, P)
+        ctx.register_packed_weight(W, P)
+        out = {}
+        for M in (1, 8):
+            X = (t.randn((M, K), device="cuda", generator=gen) * 0.5).half()
+            Y = t.empty((M, vocab), dtype=t.float16, device="cuda")
+            for _ in range(3):
+                ctx.linear(W, Sc, 256, X, Y, M, vocab, K)
+            e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                ctx.linear(W, Sc, 256, X, Y, M, vocab, K)
+            e1.record()
+            t.cuda.synchronize()
+            us = e0.elapsed_time(e1) * 1e3 / reps
+            out[f"M{M}"] = {"us": round(us, 1), "gbs": round(algorithmic_bytes(M, vocab, K, 256) / us / 1e3, 1)}
+        ctx.register_packed_weight(W, None)
+        return out
+
+
 class ReferenceStack:
     """configs[3] with the reference's own CUDA kernels (oracle/_ref, stock entry points) chained in the
     order of DualAREngine::decode_step (src/engine/dual_ar_engine.cc:576-657) at batch 8: rms_norm,
@@ -593,7 +686,7 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["decode_stack", "decode_sweep", "prefill"], default="decode_stack")
+    ap.add_argument("--workload", choices=["decode_stack", "decode_sweep", "prefill", "fast_ar"], default="decode_stack")
     ap.add_argument("--tp-mode", choices=["fused", "nccl"], default="fused",
                     help="N > 1: all-reduce inside the norm kernel over peer memory (fused) or NCCL (baseline)")
     ap.add_argument("--layers", type=int, default=36, help="decode_stack: number of layers (36 = the named config)")
@@ -664,6 +757,8 @@ def main():
             wl = DecodeStack(torch, ctx, world, rank, dist, layers=args.layers, tp_mode=args.tp_mode)
         elif args.workload == "prefill":
             wl = PrefillSweep(torch, ctx)
+        elif args.workload == "fast_ar":
+            wl = FastARFrame(torch, ctx)
         else:
             wl = DecodeSweep(torch, ctx, pack=not args.no_pack)
 
@@ -746,6 +841,32 @@ def main():
             "e2e": {"value": None, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "prefill activations are produced on the device by the embedding / previous layer; "
                             "the end-to-end figure of this repository is the decode_stack workload's"},
+        }
+        print(json.dumps(line), flush=True)
+        finish(dist, wl)
+        return
+    if args.workload == "fast_ar":
+        ms_per_step = dev_ms / args.steps
+        tok_s = wl.batch * wl.codebooks / (ms_per_step * 1e-3)
+        gbs = wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9
+        line = {
+            "metric": "fast_ar_codebook_tokens_per_s", "value": round(tok_s * world, 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
+            "config": {"workload": "configs[4]: fast-AR codebook decoder, one frame per step = 10 codebook steps x (4 layers, "
+                                   "hidden 2560, 32q/8kv x128, SwiGLU 9728, no qk-norm, W8A8 g64) + codebook head 2560->4096, "
+                                   "batch 8; sampling and embedding lookup outside; one CUDA graph per frame",
+                       "global_batch": wl.batch, "codebooks": wl.codebooks,
+                       "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+                       "l2": "a frame streams 10 x 0.42 GB of weights: each codebook step's weights exceed L2",
+                       "lm_head_int8_155776": None if args.no_detail else wl.lm_head()},
+            "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(gbs / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"],
+                         "kernel": "the whole frame (weights + scales + KV read, algorithmic bytes over frame time)",
+                         "algorithmic_bytes_per_launch": int(wl.bytes_per_step / wl.launches_per_step)},
+            "clocks": clocks, "gpu_launches": wl.launches_per_step * args.steps,
+            "e2e": {"value": round(wl.batch * wl.codebooks / (e2e_ms_max / args.steps * 1e-3), 1), "unit": "tokens/s",
+                    "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h},
         }
         print(json.dumps(line), flush=True)
         finish(dist, wl)

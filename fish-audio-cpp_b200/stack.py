@@ -42,6 +42,7 @@ class SlowARConfig:
     eps: float = 1e-6
     group: int = 256
     block_tokens: int = 16
+    qk_norm: bool = True   # per-head RMSNorm of q and k before RoPE (slow AR: yes, fast AR: no; dual_ar_config.h:19,28)
 
 
 def shard_bounds(total_groups: int, world: int):
@@ -127,8 +128,8 @@ class SlowARStack:
             s2 = s2_f[:, self.inter_lo // g:self.inter_hi // g].contiguous()
             torch.cuda.synchronize()
             del wqkv_f, sqkv_f, wo_f, so_f, w1_f, s1_f, w3_f, s3_f, w2_f, s2_f, w1, w3, s1, s3
-            lw = dict(attn_norm=rand_vec(c.dim, t + 6), ffn_norm=rand_vec(c.dim, t + 7), q_norm=rand_vec(D, t + 8),
-                      k_norm=rand_vec(D, t + 9), wqkv=wqkv, sqkv=sqkv, wo=wo, so=so, w13=w13, s13=s13, w2=w2, s2=s2)
+            lw = dict(attn_norm=rand_vec(c.dim, t + 6), ffn_norm=rand_vec(c.dim, t + 7),
+                      q_norm=rand_vec(D, t + 8) if c.qk_norm else None, k_norm=rand_vec(D, t + 9) if c.qk_norm else None, wqkv=wqkv, sqkv=sqkv, wo=wo, so=so, w13=w13, s13=s13, w2=w2, s2=s2)
             if pack:  # what the loader does once per weight: pack for the decode kernel and register the pair
                 for name, sname, n, k in (("wqkv", "sqkv", self.qkv_n, c.dim), ("wo", "so", c.dim, self.attn_k),
                                           ("w13", "s13", 2 * self.inter_l, c.dim), ("w2", "s2", c.dim, self.inter_l)):
@@ -259,8 +260,8 @@ class SlowARStack:
         torch, c = self.torch, self.cfg
         rows = []
         for lw in self.layers:
-            rows.append([lw["attn_norm"].data_ptr(), lw["ffn_norm"].data_ptr(), lw["q_norm"].data_ptr(),
-                         lw["k_norm"].data_ptr()] + [lw[n + "_packed"].data_ptr() for n in ("wqkv", "wo", "w13", "w2")])
+            rows.append([lw["attn_norm"].data_ptr(), lw["ffn_norm"].data_ptr(),
+                         lw["q_norm"].data_ptr() if c.qk_norm else 0, lw["k_norm"].data_ptr() if c.qk_norm else 0] + [lw[n + "_packed"].data_ptr() for n in ("wqkv", "wo", "w13", "w2")])
         table = np.asarray(rows, dtype=np.int64)
         assert table.shape[1] == capi.DECODE_LAYER_POINTERS
         self._layer_table = torch.from_numpy(table).to(self.x.device)

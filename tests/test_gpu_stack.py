@@ -25,8 +25,10 @@ def oracle_step(oracle, st, x_in, k_cache, v_cache, bt, positions, jitter=None):
         q = np.empty((B, st.nq_l, D), np.float16)
         for b in range(B):
             pos = int(positions[b])
-            q[b] = oracle.qknorm_rope(qkv[b, :st.nq_l], cpu(lw["q_norm"]), c.eps, freqs, pos)
-            kk = oracle.qknorm_rope(qkv[b, st.nq_l:st.nq_l + st.nkv_l], cpu(lw["k_norm"]), c.eps, freqs, pos)
+            qn = cpu(lw["q_norm"]) if c.qk_norm else None
+            kn = cpu(lw["k_norm"]) if c.qk_norm else None
+            q[b] = oracle.qknorm_rope(qkv[b, :st.nq_l], qn, c.eps, freqs, pos)
+            kk = oracle.qknorm_rope(qkv[b, st.nq_l:st.nq_l + st.nkv_l], kn, c.eps, freqs, pos)
             phys = bt[b, pos // 16]
             k_cache[phys, l, :, pos % 16] = kk
             v_cache[phys, l, :, pos % 16] = qkv[b, st.nq_l + st.nkv_l:]
@@ -44,10 +46,11 @@ def oracle_step(oracle, st, x_in, k_cache, v_cache, bt, positions, jitter=None):
     return oracle.rms_norm(x, cpu(st.final_norm), c.eps)
 
 
-@pytest.mark.parametrize("group,dim", [(64, 512), (256, 512), (256, 1024)])  # dim 1024: the one-launch norm+linear
-def test_stack_matches_oracle_chain(ctx, oracle, group, dim):
-    cfg = S.SlowARConfig(n_layer=2, dim=dim, n_head=4, n_kv=1, inter=512, group=group)
-    B, context = 3, 37
+@pytest.mark.parametrize("group,dim,qk_norm,context", [(64, 512, True, 37), (256, 512, True, 37), (256, 1024, True, 37),
+                                                        (64, 1024, False, 3)])  # the last: the fast AR's form
+def test_stack_matches_oracle_chain(ctx, oracle, group, dim, qk_norm, context):
+    cfg = S.SlowARConfig(n_layer=2, dim=dim, n_head=4, n_kv=1, inter=512, group=group, qk_norm=qk_norm)
+    B = 3
     st = S.SlowARStack(torch, ctx, cfg, B, context, max_new=8, seed=5)
     rng = np.random.default_rng(group)
     x_in = rng.standard_normal((B, cfg.dim)).astype(np.float16)
