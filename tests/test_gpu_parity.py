@@ -622,3 +622,39 @@ def test_decode_shapes_full_size(ctx, oracle, name, g, M):
     assert np.array_equal(dP.cpu().numpy(), P)
     assert_close_fp16(oracle, dY.cpu().numpy(), oracle.linear_q(W, ws, Xq, Xs, g), f"{name} M={M} g={g}",
                       abs_terms=abs_term_sum(P, ws, Xs))
+
+
+@pytest.mark.parametrize("name,g,M", [("qkv", 256, 8), ("o", 256, 8), ("gate_up", 256, 8), ("down", 256, 8), ("qkv", 64, 1),
+                                      ("o", 64, 5), ("gate_up", 64, 8), ("down", 64, 3), ("gate_up", 256, 16), ("down", 64, 32),
+                                      ("lm_head", 256, 8), ("codebook_head", 64, 8)])
+def test_packed_decode_shapes_full_size(ctx, oracle, pkg, name, g, M):
+    """The decode kernel proper (weights packed and registered, as the loader does) at the sizes of the
+    benchmarks, the int8 LM head (2560 -> 155776) and the fast AR's codebook head included: int32 group sums
+    bit-exact, fp16 within the bars, two runs bitwise equal."""
+    K, N = {"lm_head": (2560, 155776), "codebook_head": (2560, 4096)}.get(name) or synth.PROJECTIONS[name]
+    X, W, ws = synth.linear_case(2000 + M + g, M, N, K, g)
+    G = oracle.num_groups(K, g)
+    dW, dS, dX = dev(W), dev(ws), dev(X)
+    dPk = torch.empty((ctx.packed_weight_bytes(N, K, g),), dtype=torch.uint8, device="cuda")
+    ctx.pack_weight(dW, dS, N, K, g, dPk)
+    ctx.register_packed_weight(dW, dPk)
+    try:
+        dump = N * G * M <= (1 << 27)  # the LM head's sums would be 190 MB: checked through the fp16 output only
+        dP = torch.empty((M, N, G), dtype=torch.int32, device="cuda") if dump else None
+        outs = []
+        for _ in range(2):
+            ybuf, dY = guarded((M, N), torch.float16, 33.0)
+            ctx.linear(dW, dS, g, dX, dY, M, N, K, dump=dP, kernel=pkg.KERNEL_GEMV_PACKED)
+            torch.cuda.synchronize()
+            ctx.check_device_status()
+            assert guards_intact(ybuf, 33.0)
+            outs.append(dY.cpu().numpy())
+        assert np.array_equal(outs[0].view(np.uint16), outs[1].view(np.uint16))
+        Xq, Xs = oracle.quantize(X, g)
+        P = oracle.group_sums(W, Xq, g)
+        if dump:
+            assert np.array_equal(dP.cpu().numpy(), P)
+        assert_close_fp16(oracle, outs[0], oracle.linear_q(W, ws, Xq, Xs, g), f"{name} M={M} g={g}",
+                          abs_terms=abs_term_sum(P, ws, Xs))
+    finally:
+        ctx.register_packed_weight(dW, None)
