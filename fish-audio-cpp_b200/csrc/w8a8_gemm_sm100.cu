@@ -239,6 +239,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const bool magic = a.g <= 256;           // |P| <= 127 * 127 * 256 < 2^22
         int jrun = 0;                            // running group counter over all the tiles of this CTA
         bool ok = true;
+        // The first weight scales and the first activation scale of a tile are requested while the tile before it
+        // is being stored (two L2 round trips that would otherwise sit between the tiles).
+        float wpre[kWsGroups], xs_pre = 0.0f;
+        auto preload = [&](int tile) {
+            const int pm = (tile % p.tiles_m) * BM + row, pn0 = (tile / p.tiles_m) * BN;
+            const int pcol = min(pn0 + (et & (BN - 1)), a.N - 1);
+#pragma unroll
+            for (int q = 0; q < kWsGroups; ++q)
+                wpre[q] = (et < BN && q < G) ? __half2float(a.w_scale[static_cast<size_t>(pcol) * G + q]) : 0.0f;
+            xs_pre = a.Xs[static_cast<size_t>(pm < a.M ? pm : 0) * G];
+        };
+        if (static_cast<int>(blockIdx.x) < p.tiles_total) preload(blockIdx.x);
         for (int tile = blockIdx.x; tile < p.tiles_total && ok; tile += gridDim.x) {
         const int m0 = (tile % p.tiles_m) * BM, n0 = (tile / p.tiles_m) * BN;
         const int m = m0 + row;
@@ -255,9 +267,11 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             for (int q = 0; q < kWsGroups; ++q)
                 if (et < BN && j0 + q < G) ws_s[buf][q][et] = __half2float(a.w_scale[static_cast<size_t>(ncol) * G + j0 + q]);
         };
-        stage_ws(0, 0);
+#pragma unroll
+        for (int q = 0; q < kWsGroups; ++q)
+            if (et < BN && q < G) ws_s[0][q][et] = wpre[q];
         asm volatile("bar.sync 1, 256;" ::: "memory");
-        float xs_next = xs_row[0];
+        float xs_next = xs_pre;
         for (int j = 0; j < G && ok; ++j, ++jrun) {
             const int as = jrun % kAccStages, buf = (j / kWsGroups) & 1, q = j % kWsGroups;
             const float xs = xs_next;
@@ -305,50 +319,74 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             if (lane == 0) ptx::mbar_arrive(&acc_empty[as]);
             if (q == kWsGroups - 1) asm volatile("bar.sync 1, 256;" ::: "memory");
         }
+        if (tile + static_cast<int>(gridDim.x) < p.tiles_total) preload(tile + gridDim.x);
         // ---- final store: fp16, optional residual add or SwiGLU, 16 bytes at a time ----
         if (ok && m_ok) {
             const int nb = n0 + half * HC;  // first column of this thread
             auto accf = [&](int c) -> float { return (c & 1) ? hi2(acc2[c >> 1]) : lo2(acc2[c >> 1]); };
+            // A thread owns HC consecutive columns of one row, i.e. a contiguous run of the output: it is written
+            // 32 bytes (one whole sector) per store where the row allows it, 16 bytes or element-wise otherwise.
+            auto st32 = [](__half* dst, const __half* o16) {
+                const uint4 lo = *reinterpret_cast<const uint4*>(o16), hi = *reinterpret_cast<const uint4*>(o16 + 8);
+                asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(lo.x), "r"(lo.y), "r"(lo.z),
+                             "r"(lo.w), "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+            };
             if (a.epilogue == W8A8_EPI_SWIGLU) {
                 __half* yrow = a.Y + static_cast<size_t>(m) * (a.N / 2) + nb / 2;
+                const bool wide = (a.N % 64) == 0 && (reinterpret_cast<uintptr_t>(a.Y) & 31u) == 0;
 #pragma unroll
-                for (int b = 0; b < HC / 16; ++b) {
-                    if (nb + b * 16 + 16 > a.N) break;
-                    __align__(16) __half o[8];
+                for (int b = 0; b < HC / 32; ++b) {  // 32 columns -> 16 outputs
+                    __align__(16) __half o[16];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const float g16 = __half2float(__float2half(accf(b * 16 + i)));
-                        const __half s16 = __float2half(g16 / (1.0f + expf(-g16)));
-                        const float u16 = __half2float(__float2half(accf(b * 16 + 8 + i)));
-                        o[i] = __float2half(__half2float(s16) * u16);
+                    for (int hb = 0; hb < 2; ++hb)
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const float g16 = __half2float(__float2half(accf(b * 32 + hb * 16 + i)));
+                            const __half s16 = __float2half(g16 / (1.0f + expf(-g16)));
+                            const float u16 = __half2float(__float2half(accf(b * 32 + hb * 16 + 8 + i)));
+                            o[hb * 8 + i] = __float2half(__half2float(s16) * u16);
+                        }
+                    if (wide && nb + b * 32 + 32 <= a.N) {
+                        st32(yrow + b * 16, o);
+                    } else {
+                        if (nb + b * 32 + 16 <= a.N) *reinterpret_cast<uint4*>(yrow + b * 16) = *reinterpret_cast<const uint4*>(o);
+                        if (nb + b * 32 + 32 <= a.N) *reinterpret_cast<uint4*>(yrow + b * 16 + 8) = *reinterpret_cast<const uint4*>(o + 8);
                     }
-                    *reinterpret_cast<uint4*>(yrow + b * 8) = *reinterpret_cast<const uint4*>(o);
                 }
             } else {
                 __half* yrow = a.Y + static_cast<size_t>(m) * a.N + nb;
                 const __half* rrow = a.residual ? a.residual + static_cast<size_t>(m) * a.N + nb : nullptr;
                 const bool vec = (a.N % 8) == 0;
+                const bool wide = (a.N % 16) == 0 && (reinterpret_cast<uintptr_t>(a.Y) & 31u) == 0;
 #pragma unroll
-                for (int b = 0; b < HC / 8; ++b) {
-                    if (nb + b * 8 >= a.N) break;
-                    __align__(16) __half o[8];
-                    __align__(16) __half rr[8];
-                    const bool full = vec && nb + b * 8 + 8 <= a.N;
+                for (int b = 0; b < HC / 16; ++b) {  // 16 columns per step
+                    if (nb + b * 16 >= a.N) break;
+                    __align__(16) __half o[16];
+                    __align__(16) __half rr[16];
+                    const bool full = vec && nb + b * 16 + 16 <= a.N;
                     if (a.epilogue == W8A8_EPI_RESIDUAL) {
-                        if (full) *reinterpret_cast<uint4*>(rr) = *reinterpret_cast<const uint4*>(rrow + b * 8);
-                        else
-                            for (int i = 0; i < 8; ++i) rr[i] = nb + b * 8 + i < a.N ? rrow[b * 8 + i] : __float2half(0.f);
+                        if (full) {
+                            *reinterpret_cast<uint4*>(rr) = *reinterpret_cast<const uint4*>(rrow + b * 16);
+                            *reinterpret_cast<uint4*>(rr + 8) = *reinterpret_cast<const uint4*>(rrow + b * 16 + 8);
+                        } else {
+                            for (int i = 0; i < 16; ++i) rr[i] = nb + b * 16 + i < a.N ? rrow[b * 16 + i] : __float2half(0.f);
+                        }
                     }
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        __half y = __float2half(accf(b * 8 + i));
+                    for (int i = 0; i < 16; ++i) {
+                        __half y = __float2half(accf(b * 16 + i));
                         if (a.epilogue == W8A8_EPI_RESIDUAL) y = __float2half(__half2float(y) + __half2float(rr[i]));
                         o[i] = y;
                     }
-                    if (full) *reinterpret_cast<uint4*>(yrow + b * 8) = *reinterpret_cast<const uint4*>(o);
-                    else
-                        for (int i = 0; i < 8; ++i)
-                            if (nb + b * 8 + i < a.N) yrow[b * 8 + i] = o[i];
+                    if (full && wide) {
+                        st32(yrow + b * 16, o);
+                    } else if (full) {
+                        *reinterpret_cast<uint4*>(yrow + b * 16) = *reinterpret_cast<const uint4*>(o);
+                        *reinterpret_cast<uint4*>(yrow + b * 16 + 8) = *reinterpret_cast<const uint4*>(o + 8);
+                    } else {
+                        for (int i = 0; i < 16; ++i)
+                            if (nb + b * 16 + i < a.N) yrow[b * 16 + i] = o[i];
+                    }
                 }
             }
         }
