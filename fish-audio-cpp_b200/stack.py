@@ -55,6 +55,25 @@ def shard_bounds(total_groups: int, world: int):
     return b
 
 
+def shard_plan(cfg: SlowARConfig, tp_size: int, tp_rank: int):
+    """Shapes of one rank's shard: (q heads, kv heads, rows of wqkv, K of wo, first and last intermediate channel).
+    Column-parallel wqkv / w1|w3 by heads and intermediate channels, row-parallel wo / w2 with K cut at quantisation
+    group boundaries (so every per-group int32 sum stays on one rank)."""
+    c, g = cfg, cfg.group
+    assert c.n_kv % tp_size == 0 and c.n_head == 4 * c.n_kv and c.head_dim == 128
+    nq_l, nkv_l = c.n_head // tp_size, c.n_kv // tp_size
+    qkv_n, attn_k = (nq_l + 2 * nkv_l) * c.head_dim, nq_l * c.head_dim
+    assert attn_k % g == 0, "attention shard must hold whole quantisation groups"
+    assert c.inter % g == 0
+    # cut in units of 256 channels when the group size divides 256: the decode kernel's packed weight format
+    # wants K in multiples of 256, and a multiple of 256 is a multiple of the group size too
+    unit = 256 if (256 % g == 0 and c.inter % 256 == 0) else g
+    gb = shard_bounds(c.inter // unit, tp_size)
+    lo, hi = gb[tp_rank] * unit, gb[tp_rank + 1] * unit
+    assert hi > lo and (hi - lo) % 8 == 0
+    return nq_l, nkv_l, qkv_n, attn_k, lo, hi
+
+
 class SlowARStack:
     def __init__(self, torch, ctx: capi.Context, cfg: SlowARConfig, batch: int, context: int, max_new: int = 256,
                  tp_rank: int = 0, tp_size: int = 1, seed: int = 0, all_reduce=None, pack: bool = True,
@@ -76,17 +95,9 @@ class SlowARStack:
         # qk-norm + RoPE + KV write inside the attention launch (W8A8_STACK_FUSE_ROPE=0: as two launches)
         self.fuse_rope = os.environ.get("W8A8_STACK_FUSE_ROPE", "1") == "1"
         c = cfg
-        assert c.n_kv % tp_size == 0 and c.n_head == 4 * c.n_kv and c.head_dim == 128
         g = c.group
-        self.nq_l, self.nkv_l = c.n_head // tp_size, c.n_kv // tp_size
-        self.qkv_n = (self.nq_l + 2 * self.nkv_l) * c.head_dim
-        self.attn_k = self.nq_l * c.head_dim
-        assert self.attn_k % g == 0, "attention shard must hold whole quantisation groups"
-        assert c.inter % g == 0
-        gb = shard_bounds(c.inter // g, tp_size)
-        self.inter_lo, self.inter_hi = gb[tp_rank] * g, gb[tp_rank + 1] * g
+        self.nq_l, self.nkv_l, self.qkv_n, self.attn_k, self.inter_lo, self.inter_hi = shard_plan(cfg, tp_size, tp_rank)
         self.inter_l = self.inter_hi - self.inter_lo
-        assert self.inter_l > 0 and self.inter_l % 8 == 0
         dev = "cuda"
         gen = torch.Generator(device=dev)
 

@@ -22,6 +22,25 @@ def test_shard_bounds():
     assert S.shard_bounds(152, 8)[-1] == 152 and S.shard_bounds(16, 2) == [0, 8, 16]
 
 
+@pytest.mark.parametrize("tp", [1, 2, 4, 8])
+@pytest.mark.parametrize("group", [256, 64])
+def test_shard_plan_of_the_benchmark_stack(tp, group):
+    """Every rank's shard of the 36-layer config keeps the shapes the decode kernels take: K of each linear a
+    multiple of 256 (packable), whole quantisation groups, four query heads per kv head; the shards tile the
+    intermediate channels without gap or overlap."""
+    cfg = S.SlowARConfig(group=group)
+    edges = []
+    for r in range(tp):
+        nq, nkv, qkv_n, attn_k, lo, hi = S.shard_plan(cfg, tp, r)
+        assert nq == 4 * nkv and nkv >= 1 and qkv_n == (nq + 2 * nkv) * 128 and qkv_n % 16 == 0
+        assert attn_k % 256 == 0 and attn_k % group == 0            # K of wo
+        assert (hi - lo) % 256 == 0 and (hi - lo) % group == 0      # K of w2, and rows of w1 | w3 (x2, % 16)
+        assert cfg.dim % 256 == 0                                   # K of wqkv and w1 | w3
+        edges.append((lo, hi))
+    assert edges[0][0] == 0 and edges[-1][1] == cfg.inter
+    assert all(edges[i][1] == edges[i + 1][0] for i in range(tp - 1))
+
+
 def _free_port():
     with socket.socket() as s:
         s.bind(("127.0.0.1", 0))
