@@ -140,3 +140,21 @@ def test_one_launch_step_matches_the_chain_of_launches(ctx, group, dim, n_kv, in
         st.decode_step_one_launch(x_in)
         torch.cuda.synchronize()
         assert torch.equal(st.out.view(torch.int16), first.view(torch.int16))
+
+
+@pytest.mark.parametrize("tp,rank", [(2, 1), (4, 0), (4, 3), (8, 0), (8, 7)])
+@pytest.mark.parametrize("group", [256, 64])
+def test_every_tensor_parallel_shard_shape_runs(ctx, tp, rank, group):
+    """One rank's shard of the benchmark stack at TP 2 / 4 / 8 (uneven w2 shards included), run alone on one GPU
+    with no exchange: the decode kernels must take every shard shape (packed weights, attention with 16 / 8 / 4
+    query heads) and give finite numbers. The exchange itself is tested in test_gpu_tp.py."""
+    cfg = S.SlowARConfig(n_layer=1, group=group)
+    st = S.SlowARStack(torch, ctx, cfg, 8, 100, max_new=4, tp_rank=rank, tp_size=tp, seed=3, all_reduce=None,
+                       tp_mode="nccl")
+    x = torch.from_numpy(np.random.default_rng(tp + rank).standard_normal((8, cfg.dim)).astype(np.float16)).cuda()
+    out = st.decode_step(x)
+    torch.cuda.synchronize()
+    ctx.check_device_status()
+    assert torch.isfinite(out.float()).all()
+    for name in ("wqkv", "wo", "w13", "w2"):
+        assert name + "_packed" in st.layers[0], f"{name} shard of TP{tp} rank {rank} was not packable"
