@@ -115,6 +115,10 @@ __device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
     return d;
 }
+// Four consecutive floats of shared memory as two packed pairs, in one 16-byte load.
+__device__ __forceinline__ void lds_pairs(const float* p, uint64_t& lo, uint64_t& hi) {
+    asm volatile("ld.shared.v2.u64 {%0, %1}, [%2];" : "=l"(lo), "=l"(hi) : "r"(ptx::smem_u32(p)));
+}
 // Exact int32 -> fp32 for |v| < 2^22: the integer lands in the mantissa of 1.5 * 2^23, which is then removed.
 __device__ __forceinline__ uint64_t ints_to_floats_magic(uint32_t a, uint32_t b) {
     const uint64_t biased = static_cast<uint64_t>(a + 0x4B400000u) | (static_cast<uint64_t>(b + 0x4B400000u) << 32);
@@ -131,6 +135,9 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr) {
 constexpr uint32_t kIdesc = (2u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) |
                             (static_cast<uint32_t>(BM >> 4) << 24);
 
+// MAGIC: groups of at most 256, whose sums convert to fp32 by integer add + float subtract. A template
+// parameter, not a run-time flag: the flag cost a branch per four sums in the promote loop.
+template <bool MAGIC>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                const GemmParams p) {
@@ -236,7 +243,7 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         const int half = (warp - 4) >> 2;        // which HC columns
         const int row = quad * 32 + lane;        // row inside the tile
         const int et = (warp - 4) * 32 + lane;   // 0..255: stages the weight scale of tile column et
-        const bool magic = a.g <= 256;           // |P| <= 127 * 127 * 256 < 2^22
+        constexpr bool magic = MAGIC;            // |P| <= 128 * 128 * 256 = 2^22
         int jrun = 0;                            // running group counter over all the tiles of this CTA
         bool ok = true;
         // The first weight scales and the first activation scale of a tile are requested while the tile before it
@@ -294,17 +301,18 @@ gemm_i8_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                 const uint32_t (&rr)[CH] = r[ci & 1];
 #pragma unroll
                 for (int c = 0; c < CH; c += 4) {
-                    const float4 w4 = *reinterpret_cast<const float4*>(&ws_s[buf][q][half * HC + c0 + c]);
+                    uint64_t w01, w23;
+                    lds_pairs(&ws_s[buf][q][half * HC + c0 + c], w01, w23);
                     uint64_t f01, f23;
-                    if (magic) {
+                    if constexpr (magic) {
                         f01 = ints_to_floats_magic(rr[c + 0], rr[c + 1]);
                         f23 = ints_to_floats_magic(rr[c + 2], rr[c + 3]);
                     } else {
                         f01 = pack2(static_cast<float>(static_cast<int>(rr[c + 0])), static_cast<float>(static_cast<int>(rr[c + 1])));
                         f23 = pack2(static_cast<float>(static_cast<int>(rr[c + 2])), static_cast<float>(static_cast<int>(rr[c + 3])));
                     }
-                    acc2[(c0 + c) / 2] = fma2(mul2(f01, pack2(w4.x, w4.y)), xs2, acc2[(c0 + c) / 2]);
-                    acc2[(c0 + c) / 2 + 1] = fma2(mul2(f23, pack2(w4.z, w4.w)), xs2, acc2[(c0 + c) / 2 + 1]);
+                    acc2[(c0 + c) / 2] = fma2(mul2(f01, w01), xs2, acc2[(c0 + c) / 2]);
+                    acc2[(c0 + c) / 2 + 1] = fma2(mul2(f23, w23), xs2, acc2[(c0 + c) / 2 + 1]);
                 }
                 if (a.dump && m_ok) {
 #pragma unroll
@@ -431,12 +439,13 @@ int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t str
     p.tiles_m = (a.M + BM - 1) / BM;
     p.tiles_total = p.tiles_m * ((a.N + BN - 1) / BN);
     const size_t smem = static_cast<size_t>(kStages) * kStageBytes + 1024;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_i8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(smem));
+    const bool magic = a.g <= 256;
+    auto kernel = magic ? gemm_i8_kernel<true> : gemm_i8_kernel<false>;
+    static bool attr_set[2] = {false, false};
+    if (!attr_set[magic]) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        attr_set = true;
+        attr_set[magic] = true;
     }
     cudaLaunchConfig_t cfg = {};
     int sms = 148, dev = 0;
@@ -451,7 +460,7 @@ int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t str
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled(kPdlLinear) ? 1 : 0;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_i8_kernel, map_x, map_w, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, map_x, map_w, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "gemm launch: %s", cudaGetErrorString(e));
     return W8A8_OK;
 }
