@@ -605,6 +605,31 @@ def test_linear_against_reference_kernel(ctx, oracle, M, N, K, g):
         assert exact or exact_alt, "oracle promote order matches neither fma nor mul+add of the reference"
 
 
+@pytest.mark.parametrize("g", [256, 64])
+@pytest.mark.parametrize("wval,qval", [(-128, 127), (127, 127), (-128, -127), (127, -127)])
+def test_gemm_tcgen05_extreme_codes(ctx, oracle, pkg, g, wval, qval):
+    """Every product at its largest magnitude: a group of 256 sums to 128 * 127 * 256 = 4 161 536, just under the
+    2^22 up to which the kernel's integer-add int32 -> fp32 conversion is exact. Sums and fp16 bits must match."""
+    M, N, K = 130, 264, 512
+    G = oracle.num_groups(K, g)
+    rng = np.random.default_rng(7)
+    W = np.full((N, K), wval, dtype=np.int8)
+    W[::3, ::5] = -wval if wval != -128 else 127  # mixed signs in some rows
+    ws = synth.weight_scales(rng, N, G)
+    Xq = np.full((M, K), qval, dtype=np.int8)
+    Xq[1::2, 7::11] = -qval
+    Xs = rng.uniform(1e-3, 4e-2, size=(M, G)).astype(np.float32)
+    dP = torch.full((M, N, G), -1, dtype=torch.int32, device="cuda")
+    dY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+    ctx.linear_q(dev(W), dev(ws), g, dev(Xq), dev(Xs), dY, M, N, K, dump=dP, kernel=pkg.KERNEL_GEMM)
+    torch.cuda.synchronize()
+    ctx.check_device_status()
+    P = oracle.group_sums(W, Xq, g)
+    assert np.abs(P).max() >= 127 * 127 * g
+    assert np.array_equal(dP.cpu().numpy(), P)
+    assert np.array_equal(dY.cpu().numpy().view(np.uint16), oracle.linear_q(W, ws, Xq, Xs, g).view(np.uint16))
+
+
 # ---------------------------------------------------------------- headline shapes at full size
 @pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
 @pytest.mark.parametrize("g", [256, 64])
