@@ -212,7 +212,7 @@ def write_packed_sidecar(ctx, c: Container, out_path) -> Dict[str, Tuple[int, in
     import torch
 
     def dev(a):
-        return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        return torch.from_numpy(np.array(a, order="C")).cuda()  # a copy: container views are read-only
 
     fused = {w1: (prefix, w3) for prefix, w1, w3 in fused_gate_up_names(c)}
     second = {w3 for _, w3 in fused.values()}
