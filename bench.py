@@ -547,6 +547,34 @@ class FastARFrame:
             us = e0.elapsed_time(e1) * 1e3 / reps
             out[f"M{M}"] = {"us": round(us, 1), "gbs": round(algorithmic_bytes(M, vocab, K, 256) / us / 1e3, 1)}
         ctx.register_packed_weight(W, None)
+        # the rows the decode sampler reads (semantic range + end of sequence) as a table of their own
+        from fish_audio_cpp_b200 import lm_head as lmh
+
+        rows = lmh.sampled_rows()
+        Wc, Scc = lmh.compact_head(W, Sc, rows)
+        n = len(rows)
+        Pc = t.empty((ctx.packed_weight_bytes(n, K, 256),), dtype=t.uint8, device="cuda")
+        ctx.pack_weight(Wc, Scc, n, K, 256, Pc)
+        ctx.register_packed_weight(Wc, Pc)
+        flush = t.empty((256 << 20,), dtype=t.uint8, device="cuda")
+        for M in (1, 8):
+            X = (t.randn((M, K), device="cuda", generator=gen) * 0.5).half()
+            Y = t.empty((M, n), dtype=t.float16, device="cuda")
+            for _ in range(3):
+                ctx.linear(Wc, Scc, 256, X, Y, M, n, K)
+            total = 0.0
+            for _ in range(reps):  # 10.5 MB of weights would sit in L2: flush it between the timed launches
+                flush.fill_(1)
+                e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+                e0.record()
+                ctx.linear(Wc, Scc, 256, X, Y, M, n, K)
+                e1.record()
+                t.cuda.synchronize()
+                total += e0.elapsed_time(e1) * 1e3
+            us = total / reps
+            out[f"sampled_rows_M{M}"] = {"rows": n, "us": round(us, 1),
+                                         "gbs": round(algorithmic_bytes(M, n, K, 256) / us / 1e3, 1)}
+        ctx.register_packed_weight(Wc, None)
         return out
 
 

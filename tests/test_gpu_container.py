@@ -90,3 +90,36 @@ def test_gate_and_up_with_two_smooth_vectors_stay_apart(ctx, tmp_path):
     done = ct.write_packed_sidecar(ctx, ct.Container(tmp_path / "model.bin"), tmp_path / "model.packed.bin")
     assert P0 + "feed_forward.w13.weight" not in done
     assert done[P0 + "feed_forward.w1.weight"] == (40, 512, 256) and done[P0 + "feed_forward.w3.weight"] == (40, 512, 256)
+
+
+def test_sampled_rows_lm_head_equals_the_rows_of_the_full_head(ctx, oracle, pkg):
+    """The compact LM head (semantic range + end of sequence, gathered and packed at load) against the oracle on
+    those rows, and against the same rows of the full head's output."""
+    from fish_audio_cpp_b200 import lm_head as lmh
+
+    vocab, K, g, M = 2048, 512, 256, 8
+    rng = np.random.default_rng(5)
+    W, S = synth.weights(rng, vocab, K), synth.weight_scales(rng, vocab, K // g)
+    X = synth.activations(rng, M, K)
+    rows = lmh.sampled_rows(1500, 1999, 77)
+    dW, dS, dX = dev(W), dev(S), dev(X)
+    dWc, dSc = lmh.compact_head(dW, dS, rows)
+    n = len(rows)
+    img = torch.empty(ctx.packed_weight_bytes(n, K, g), dtype=torch.uint8, device="cuda")
+    ctx.pack_weight(dWc, dSc, n, K, g, img)
+    ctx.register_packed_weight(dWc, img)
+    try:
+        dYc = torch.empty((M, n), dtype=torch.float16, device="cuda")
+        ctx.linear(dWc, dSc, g, dX, dYc, M, n, K, kernel=pkg.KERNEL_GEMV_PACKED)
+        dY = torch.empty((M, vocab), dtype=torch.float16, device="cuda")
+        ctx.linear(dW, dS, g, dX, dY, M, vocab, K)
+        torch.cuda.synchronize()
+        ctx.check_device_status()
+    finally:
+        ctx.register_packed_weight(dWc, None)
+    Xq, Xs = oracle.quantize(X, g)
+    Wc, Sc = lmh.compact_head(W, S, rows)
+    P = oracle.group_sums(Wc, Xq, g)
+    terms = abs_term_sum(P, Sc, Xs)
+    assert_close_fp16(oracle, dYc.cpu().numpy(), oracle.linear_q(Wc, Sc, Xq, Xs, g), "compact head", abs_terms=terms)
+    assert_close_fp16(oracle, dYc.cpu().numpy(), dY.cpu().numpy()[:, rows], "compact vs full head", abs_terms=terms)
