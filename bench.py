@@ -37,12 +37,13 @@ def peaks():
 
 # DRAM traffic / algorithmic bytes of the dominant kernels, from one ncu capture each (dram__bytes_read.sum +
 # dram__bytes_write.sum of a launch, summaries under profiles/): gemv_packed_kernel on gate_up M=1 g=256 moved
-# 50.249 MB against 50.241 MB; gemm_i8_kernel on gate_up M=2048 g=256 moved 130.8 MB against 135.2 MB (weights,
-# scales, codes and activation scales in, fp16 out; part of the output was still in L2 when the kernel ended).
+# 50.249 MB against 50.241 MB; gemm_i8_kernel on gate_up M=2048 g=256 moved 91.8 MB against 135.2 MB (weights,
+# scales, codes and activation scales in: 55.7 MB read for 55.5; fp16 out: 36.2 MB of the 79.7 MB had been written
+# back when the kernel ended, the rest was still in L2).
 # Traffic of both grows in proportion to the bytes a launch touches, so a launch's traffic is that ratio times
 # its own algorithmic bytes.
 GEMV_TRAFFIC_RATIO = 50.249 / 50.241
-GEMM_TRAFFIC_RATIO = 130.8 / 135.2
+GEMM_TRAFFIC_RATIO = 91.8 / 135.2
 
 
 def algorithmic_bytes(M, N, K, g):
