@@ -3,8 +3,8 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
 
-Prints ONE JSON line (rank 0). See DESIGN.md for what each key means and how the roofline
-figures are derived.
+Prints ONE JSON line (rank 0): the headline metric of the chosen workload, its roofline figure, the
+end-to-end figure with host buffers, the CPU baseline and the clocks seen while it ran.
 """
 from __future__ import annotations
 

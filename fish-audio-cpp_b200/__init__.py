@@ -24,4 +24,5 @@ from .capi import (  # noqa: F401
     load_library,
     num_groups,
     static_scratch_bytes,
+    static_scratch_check_status,
 )

@@ -84,10 +84,15 @@ def load_library() -> C.CDLL:
         "w8a8_tp_allreduce_rmsnorm_quantize": (I, [P, P, P, P, F, P, P, I, I, I, I, P, P, P, P]),
         "w8a8_packed_weight_bytes": (Z, [I, I, I]),
         "w8a8_pack_weight": (I, [P, P, P, I, I, I, P, P]),
-        "w8a8_register_packed_weight": (I, [P, P, P]),
+        "w8a8_register_packed_weight": (I, [P, P, P, I, I, I]),
+        "w8a8_static_scratch_check_status": (I, [P]),
         "w8a8_static_scratch_bytes": (Z, []),
         "w8a8_linear_static_scratch": (I, [P, P, I, P, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "fish_shim_int8_dequant_gemm_fp16": (I, [P, P, I, P, P, P, P, I, I, I, P, C.c_char_p, I]),
+        "fish_shim_rms_norm": (I, [P, P, P, I, I, F, P, C.c_char_p, I]),
+        "fish_shim_silu_forward": (I, [P, I, P, C.c_char_p, I]),
+        "fish_shim_mul_forward": (I, [P, P, I, P, C.c_char_p, I]),
+        "fish_shim_residual_add": (I, [P, P, I, P, C.c_char_p, I]),
     }
     for name, (res, args) in sigs.items():
         fn = getattr(lib, name)
@@ -104,7 +109,7 @@ EXPORTS = [
     "w8a8_decode_stack_timeline",
     "w8a8_pack_gate_up", "w8a8_qknorm_rope_kvwrite", "w8a8_paged_attention_decode", "w8a8_qkv_attention_decode", "w8a8_tp_create", "w8a8_tp_connect",
     "w8a8_tp_allreduce_rmsnorm_quantize", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
-    "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch",
+    "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch", "w8a8_static_scratch_check_status",
 ]
 
 
@@ -145,6 +150,15 @@ def linear_static_scratch(W, w_scale, group_size, X, Y, M, N, K, act_scale=None,
                                         _stream(stream))
     if rc != 0:
         raise W8A8Error(rc, "w8a8_linear_static_scratch", lib.w8a8_last_error().decode())
+
+
+def static_scratch_check_status(stream=None):
+    """Raises W8A8Error(status 4) if a kernel launched by linear_static_scratch on the current device gave up a
+    bounded wait since the last check; synchronises the stream."""
+    lib = load_library()
+    rc = lib.w8a8_static_scratch_check_status(_stream(stream))
+    if rc != 0:
+        raise W8A8Error(rc, "w8a8_static_scratch_check_status", lib.w8a8_last_error().decode())
 
 
 class Context:
@@ -307,9 +321,29 @@ class Context:
         self._check(self.lib.w8a8_pack_weight(self.handle, _ptr(W), _ptr(w_scale), N, K, group_size,
                                               _ptr(packed_out), _stream(stream)), "w8a8_pack_weight")
 
-    def register_packed_weight(self, W, packed):
-        self._check(self.lib.w8a8_register_packed_weight(self.handle, _ptr(W), _ptr(packed)),
+    def register_packed_weight(self, W, packed, N=0, K=0, group_size=0):
+        """packed=None removes the entry; otherwise N, K, group_size are the shape the image was packed for."""
+        self._check(self.lib.w8a8_register_packed_weight(self.handle, _ptr(W), _ptr(packed), N, K, group_size),
                     "w8a8_register_packed_weight")
+
+    def _shim(self, name, *args, stream=None):
+        buf = C.create_string_buffer(512)
+        rc = getattr(self.lib, name)(*args, _stream(stream), buf, 512)
+        if rc:
+            raise RuntimeError(buf.value.decode())
+
+    def shim_rms_norm(self, x, weight, out, n_tokens, dim, eps, stream=None):
+        """fish::kernels::rms_norm with the reference's signature (src/kernels/kernels.h:10-19)."""
+        self._shim("fish_shim_rms_norm", _ptr(x), _ptr(weight), _ptr(out), n_tokens, dim, eps, stream=stream)
+
+    def shim_silu_forward(self, x, n, stream=None):
+        self._shim("fish_shim_silu_forward", _ptr(x), n, stream=stream)
+
+    def shim_mul_forward(self, a, b, n, stream=None):
+        self._shim("fish_shim_mul_forward", _ptr(a), _ptr(b), n, stream=stream)
+
+    def shim_residual_add(self, a, b, n, stream=None):
+        self._shim("fish_shim_residual_add", _ptr(a), _ptr(b), n, stream=stream)
 
     def shim_int8_dequant_gemm_fp16(self, W, scale, group_size, act_scale, smooth_inv, X, Y, M_out, N_tok, K,
                                     stream=None):

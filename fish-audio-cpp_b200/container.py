@@ -214,7 +214,12 @@ def write_packed_sidecar(ctx, c: Container, out_path) -> Dict[str, Tuple[int, in
     def dev(a):
         return torch.from_numpy(np.array(a, order="C")).cuda()  # a copy: container views are read-only
 
-    fused = {w1: (prefix, w3) for prefix, w1, w3 in fused_gate_up_names(c)}
+    fused = {}
+    for prefix, w1, w3 in fused_gate_up_names(c):
+        lin = c.linear(w1)
+        # a pair whose interleaved form cannot be streamed is not fused: w1 and w3 are then packed each on its own
+        if lin.N % 8 == 0 and ctx.packed_weight_bytes(2 * lin.N, lin.K, lin.group_size) != 0:
+            fused[w1] = (prefix, w3)
     second = {w3 for _, w3 in fused.values()}
     out: Dict[str, np.ndarray] = {}
     done: Dict[str, Tuple[int, int, int]] = {}
@@ -226,8 +231,6 @@ def write_packed_sidecar(ctx, c: Container, out_path) -> Dict[str, Tuple[int, in
         if name in fused:
             prefix, w3 = fused[name]
             up = c.linear(w3)
-            if ctx.packed_weight_bytes(2 * N, K, g) == 0 or N % 8:
-                continue
             dW = torch.empty((2 * N, K), dtype=torch.int8, device="cuda")
             dS = torch.empty((2 * N, G), dtype=torch.float16, device="cuda")
             ctx.pack_gate_up(dev(lin.W), dev(lin.scale.reshape(N, G)), dev(up.W), dev(up.scale.reshape(N, G)), N, K, G, dW, dS)

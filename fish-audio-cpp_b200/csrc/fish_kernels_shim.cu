@@ -100,3 +100,46 @@ extern "C" FISH_SHIM_API int fish_shim_int8_dequant_gemm_fp16(const void* W, con
         return 1;
     }
 }
+
+namespace {
+template <class F>
+int shim_guard(char* err, int err_len, F&& f) {
+    try {
+        f();
+        return 0;
+    } catch (const std::exception& e) {
+        if (err && err_len > 0) snprintf(err, err_len, "%s", e.what());
+        return 1;
+    }
+}
+}  // namespace
+
+extern "C" FISH_SHIM_API int fish_shim_rms_norm(const void* x, const void* weight, void* out, int n_tokens, int dim,
+                                                float eps, void* stream, char* err, int err_len) {
+    return shim_guard(err, err_len, [&] {
+        fish::kernels::rms_norm(static_cast<const __half*>(x), static_cast<const __half*>(weight),
+                                static_cast<__half*>(out), n_tokens, dim, eps, static_cast<cudaStream_t>(stream));
+    });
+}
+
+extern "C" FISH_SHIM_API int fish_shim_silu_forward(void* x, int n, void* stream, char* err, int err_len) {
+    return shim_guard(err, err_len, [&] {
+        fish::kernels::silu_forward(static_cast<__half*>(x), n, static_cast<cudaStream_t>(stream));
+    });
+}
+
+extern "C" FISH_SHIM_API int fish_shim_mul_forward(void* a, const void* b, int n, void* stream, char* err,
+                                                   int err_len) {
+    return shim_guard(err, err_len, [&] {
+        fish::kernels::mul_forward(static_cast<__half*>(a), static_cast<const __half*>(b), n,
+                                   static_cast<cudaStream_t>(stream));
+    });
+}
+
+extern "C" FISH_SHIM_API int fish_shim_residual_add(void* a, const void* b, int n, void* stream, char* err,
+                                                    int err_len) {
+    return shim_guard(err, err_len, [&] {
+        fish::kernels::residual_add(static_cast<__half*>(a), static_cast<const __half*>(b), n,
+                                    static_cast<cudaStream_t>(stream));
+    });
+}

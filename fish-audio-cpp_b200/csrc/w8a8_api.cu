@@ -17,7 +17,11 @@ struct w8a8_ctx {
     int* splitk_counters = nullptr;   // one arrival counter per 16-row tile, zero between launches
     // raw weight pointer -> its packed image; filled by the loader (w8a8_register_packed_weight), the
     // same pointer-keyed lookup as DualAREngine::weight_quant_meta_ (src/engine/dual_ar_engine.h:105)
-    std::unordered_map<const void*, const void*> packed;
+    struct PackedEntry {
+        const void* image;
+        int N, K, g;  // the shape the image was packed for: a call with another shape must not stream it
+    };
+    std::unordered_map<const void*, PackedEntry> packed;
     std::mutex packed_mu;
     w8a8::TpState* tp = nullptr;  // tensor-parallel exchange, when w8a8_tp_create was called
 };
@@ -125,7 +129,10 @@ static void fill_scratch(w8a8_ctx* ctx, LinearArgs& a) {
     if (a.M <= 32 && !ctx->packed.empty()) {
         std::lock_guard<std::mutex> lock(ctx->packed_mu);
         auto it = ctx->packed.find(a.W);
-        if (it != ctx->packed.end()) a.packed = it->second;
+        // A pointer may outlive its registration (the caller freed the weight and the allocator handed the
+        // address to another tensor): the image is used only for the shape it was packed for.
+        if (it != ctx->packed.end() && it->second.N == a.N && it->second.K == a.K && it->second.g == a.g)
+            a.packed = it->second.image;
     }
 }
 
@@ -474,11 +481,17 @@ int w8a8_pack_weight(w8a8_ctx* ctx, const void* W, const void* w_scale, int N, i
                               packed_out, static_cast<cudaStream_t>(stream));
 }
 
-int w8a8_register_packed_weight(w8a8_ctx* ctx, const void* W, const void* packed) {
+int w8a8_register_packed_weight(w8a8_ctx* ctx, const void* W, const void* packed, int N, int K, int group_size) {
     if (!ctx || !W) return fail(W8A8_ERR_INVALID_ARG, "register_packed_weight: null argument");
     std::lock_guard<std::mutex> lock(ctx->packed_mu);
-    if (packed) ctx->packed[W] = packed;
-    else ctx->packed.erase(W);
+    if (!packed) {
+        ctx->packed.erase(W);
+        return W8A8_OK;
+    }
+    if (N <= 0 || K <= 0 || packed_weight_bytes(N, K, group_size) == 0)
+        return fail(W8A8_ERR_INVALID_ARG, "register_packed_weight: N=%d K=%d group=%d is not a packable shape", N, K,
+                    group_size);
+    ctx->packed[W] = w8a8_ctx::PackedEntry{packed, N, K, norm_group(K, group_size)};
     return W8A8_OK;
 }
 

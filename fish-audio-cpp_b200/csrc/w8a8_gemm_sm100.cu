@@ -39,6 +39,10 @@ constexpr int kAccStages = 2;  // 2 x 256 columns = the whole tensor memory
 constexpr int kStageBytes = (BM + BN) * BK;
 constexpr int kEpiWarps = 8;                // two per tensor-memory lane quadrant, 128 columns each
 constexpr int kThreads = 128 + kEpiWarps * 32;  // warpgroup 0: producer, MMA issuer, two idle warps; 1-2: epilogue
+// Registers per thread the 384-thread CTA is launched with (what ptxas reports for this kernel): warpgroup 0 gives up
+// 128 x (168 - 40) = 16384, the two epilogue warpgroups take 2 x 128 x (232 - 168) = 16384.
+constexpr int kLaunchRegs = 168;
+static_assert(128 * (kLaunchRegs - 40) == (kEpiWarps / 4) * 128 * (232 - kLaunchRegs), "setmaxnreg sums must balance");
 constexpr uint32_t kSpin = 1u << 21;
 constexpr int kWsGroups = 4;
 
@@ -441,11 +445,21 @@ int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t str
     const size_t smem = static_cast<size_t>(kStages) * kStageBytes + 1024;
     const bool magic = a.g <= 256;
     auto kernel = magic ? gemm_i8_kernel<true> : gemm_i8_kernel<false>;
-    static bool attr_set[2] = {false, false};
-    if (!attr_set[magic]) {
+    {
+        // The attribute is per device and this library serves several devices of one process: set it on every
+        // launch (a host-side table write) rather than remember it per process.
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        attr_set[magic] = true;
+        // setmaxnreg moves registers between the warpgroups; the sums balance only for the register count the
+        // kernel was compiled to (kLaunchRegs per thread). An unbalanced sum blocks for ever in setmaxnreg.inc,
+        // a wait nothing bounds, so a build that came out differently is refused here.
+        cudaFuncAttributes fa;
+        e = cudaFuncGetAttributes(&fa, kernel);
+        if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncGetAttributes: %s", cudaGetErrorString(e));
+        if (fa.numRegs != kLaunchRegs)
+            return fail(W8A8_ERR_UNSUPPORTED,
+                        "gemm_i8_kernel was compiled to %d registers per thread, its setmaxnreg balance needs %d",
+                        fa.numRegs, kLaunchRegs);
     }
     cudaLaunchConfig_t cfg = {};
     int sms = 148, dev = 0;

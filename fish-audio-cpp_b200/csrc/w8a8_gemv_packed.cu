@@ -528,15 +528,12 @@ struct Plan {
     long long U;
 };
 
-int num_sms() {
-    static int n = [] {
-        int dev = 0, v = 0;
-        if (cudaGetDevice(&dev) != cudaSuccess ||
-            cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
-            v = 148;
-        return v;
-    }();
-    return n;
+int num_sms() {  // of the current device (not cached: one process may drive several devices)
+    int dev = 0, v = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0)
+        v = 148;
+    return v;
 }
 
 }  // namespace
@@ -609,12 +606,10 @@ int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_
     p.status = status;
     auto kern = gemv_packed_kernel<MT, GM, FUSED>;
     const size_t smem = static_cast<size_t>(kWarps) * kRingBytes + 128 + (FUSED ? fused_smem_bytes(a.K, a.G) : 0);
-    static bool attr_set = false;  // per template instance
-    if (!attr_set) {
+    {  // per device, so on every launch (a host-side table write)
         const size_t most = static_cast<size_t>(kWarps) * kRingBytes + 128 + (FUSED ? fused_smem_bytes(4096, 64) : 0);
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(most));
         if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-        attr_set = true;
     }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(pl.ctas, 1, 1);

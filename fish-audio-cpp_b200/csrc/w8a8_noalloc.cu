@@ -132,4 +132,21 @@ int w8a8_linear_static_scratch(const void* W, const void* w_scale, int group_siz
     return dispatch_linear_q(a, kernel, slots->status, s);
 }
 
+int w8a8_static_scratch_check_status(void* stream) {
+    using namespace w8a8;
+    DeviceSlots* slots = nullptr;
+    int rc = static_slots(&slots);
+    if (rc) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    int host = 0;
+    cudaError_t e = cudaMemcpyAsync(&host, slots->status, sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "status read: %s", cudaGetErrorString(e));
+    if (host != 0) {
+        cudaMemsetAsync(slots->status, 0, sizeof(int), s);
+        return fail(W8A8_ERR_TIMEOUT, "a kernel gave up a bounded wait (code %d)", host);
+    }
+    return W8A8_OK;
+}
+
 }  // extern "C"

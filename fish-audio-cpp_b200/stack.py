@@ -74,6 +74,75 @@ def shard_plan(cfg: SlowARConfig, tp_size: int, tp_rank: int):
     return nq_l, nkv_l, qkv_n, attn_k, lo, hi
 
 
+def _seeded(torch, dev, seed, tag):
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed * 1000003 + tag)
+    return gen
+
+
+def random_weight(torch, n, k, g, seed, tag, dev="cuda"):
+    """int8 uniform [-127, 127] weights [n, k] and fp16 scales in [1e-3, 5e-3] per (row, group), seeded."""
+    gen = _seeded(torch, dev, seed, tag)
+    w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev, generator=gen)
+    s = torch.empty((n, k // g), dtype=torch.float32, device=dev).uniform_(1e-3, 5e-3, generator=gen).half()
+    return w, s
+
+
+def random_vector(torch, n, seed, tag, dev="cuda"):
+    gen = _seeded(torch, dev, seed, tag)
+    return torch.empty((n,), dtype=torch.float32, device=dev).uniform_(0.8, 1.2, generator=gen).half()
+
+
+def layer_tensors(torch, cfg: SlowARConfig, l: int, seed: int, dev="cuda"):
+    """The UNSHARDED random-init tensors of layer l, as a checkpoint would hold them (w1 and w3 apart, like the
+    reference's loader sees them): every rank of a tensor-parallel run, the single-GPU stack and the
+    reference-kernel chain all cut or use the same values. torch only; no call into the library."""
+    c, g, D, t = cfg, cfg.group, cfg.head_dim, l * 16
+    wqkv, sqkv = random_weight(torch, (c.n_head + 2 * c.n_kv) * D, c.dim, g, seed, t + 1, dev)
+    wo, so = random_weight(torch, c.dim, c.n_head * D, g, seed, t + 2, dev)
+    w1, s1 = random_weight(torch, c.inter, c.dim, g, seed, t + 3, dev)
+    w3, s3 = random_weight(torch, c.inter, c.dim, g, seed, t + 4, dev)
+    w2, s2 = random_weight(torch, c.dim, c.inter, g, seed, t + 5, dev)
+    return dict(wqkv=wqkv, sqkv=sqkv, wo=wo, so=so, w1=w1, s1=s1, w3=w3, s3=s3, w2=w2, s2=s2,
+                attn_norm=random_vector(torch, c.dim, seed, t + 6, dev), ffn_norm=random_vector(torch, c.dim, seed, t + 7, dev),
+                q_norm=random_vector(torch, D, seed, t + 8, dev) if c.qk_norm else None,
+                k_norm=random_vector(torch, D, seed, t + 9, dev) if c.qk_norm else None)
+
+
+def final_norm_weight(torch, cfg: SlowARConfig, seed: int, dev="cuda"):
+    return random_vector(torch, cfg.dim, seed, 999983, dev)
+
+
+def rope_frequencies(torch, cfg: SlowARConfig, dev="cuda"):
+    """freq_i = base^(-2i/D) in fp32 on the host, as DualAREngine::init computes them (dual_ar_engine.cc:161-167)."""
+    D = cfg.head_dim
+    freqs = (1.0 / np.power(np.float32(cfg.rope_base), (np.float32(2.0) * np.arange(D // 2, dtype=np.float32) /
+                                                          np.float32(D)))).astype(np.float32)
+    return torch.from_numpy(freqs).to(dev)
+
+
+def synthetic_kv(torch, cfg: SlowARConfig, batch: int, context: int, max_new: int, seed: int, dev="cuda",
+                 kv_heads=None):
+    """Paged fp16 KV cache [blocks, layers, kv heads, 16, head_dim] already holding `context` tokens per sequence
+    (a synthetic prefill) with a shuffled block table. kv_heads = (first, count) keeps only those heads (one
+    tensor-parallel rank's share of the same cache). Returns (k_cache, v_cache, block_table, max_blocks)."""
+    c, bt = cfg, cfg.block_tokens
+    max_blocks = (context + max_new + bt - 1) // bt
+    nblocks = batch * max_blocks
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed + 4242)
+    lo, n = kv_heads if kv_heads is not None else (0, c.n_kv)
+    caches = []
+    for _ in range(2):  # k, then v; generated layer by layer over all heads so that every rank sees the same values
+        full = torch.empty((nblocks, c.n_layer, n, bt, c.head_dim), dtype=torch.float16, device=dev)
+        for l in range(c.n_layer):
+            part = torch.randn((nblocks, c.n_kv, bt, c.head_dim), dtype=torch.float32, device=dev, generator=gen) * 0.5
+            full[:, l] = part[:, lo:lo + n].half()
+        caches.append(full)
+    perm = torch.randperm(nblocks, device=dev, generator=gen).to(torch.int32)
+    return caches[0], caches[1], perm.view(batch, max_blocks).contiguous(), max_blocks
+
+
 class SlowARStack:
     def __init__(self, torch, ctx: capi.Context, cfg: SlowARConfig, batch: int, context: int, max_new: int = 256,
                  tp_rank: int = 0, tp_size: int = 1, seed: int = 0, all_reduce=None, pack: bool = True,
@@ -99,48 +168,33 @@ class SlowARStack:
         self.nq_l, self.nkv_l, self.qkv_n, self.attn_k, self.inter_lo, self.inter_hi = shard_plan(cfg, tp_size, tp_rank)
         self.inter_l = self.inter_hi - self.inter_lo
         dev = "cuda"
-        gen = torch.Generator(device=dev)
-
-        def rand_w(n, k, tag):
-            gen.manual_seed(seed * 1000003 + tag)
-            w = torch.randint(-127, 128, (n, k), dtype=torch.int8, device=dev, generator=gen)
-            s = torch.empty((n, k // g), dtype=torch.float32, device=dev).uniform_(1e-3, 5e-3, generator=gen).half()
-            return w, s
-
-        def rand_vec(n, tag):
-            gen.manual_seed(seed * 1000003 + tag)
-            return torch.empty((n,), dtype=torch.float32, device=dev).uniform_(0.8, 1.2, generator=gen).half()
 
         D = c.head_dim
         q_lo, q_hi = tp_rank * self.nq_l * D, (tp_rank + 1) * self.nq_l * D
         kv_lo, kv_hi = tp_rank * self.nkv_l * D, (tp_rank + 1) * self.nkv_l * D
         self.layers = []
         self._keep = []
+        self._registered = []
         for l in range(c.n_layer):
-            t = l * 16
-            wqkv_f, sqkv_f = rand_w((c.n_head + 2 * c.n_kv) * D, c.dim, t + 1)
+            f = layer_tensors(torch, cfg, l, seed, dev)
             kq, kk = c.n_head * D, c.n_kv * D
             rows = torch.cat([torch.arange(q_lo, q_hi), kq + torch.arange(kv_lo, kv_hi),
                               kq + kk + torch.arange(kv_lo, kv_hi)]).to(dev)
-            wqkv, sqkv = wqkv_f[rows].contiguous(), sqkv_f[rows].contiguous()
-            wo_f, so_f = rand_w(c.dim, c.n_head * D, t + 2)
-            wo = wo_f[:, q_lo:q_hi].contiguous()
-            so = so_f[:, q_lo // g:q_hi // g].contiguous()
-            w1_f, s1_f = rand_w(c.inter, c.dim, t + 3)
-            w3_f, s3_f = rand_w(c.inter, c.dim, t + 4)
-            w1, s1 = w1_f[self.inter_lo:self.inter_hi].contiguous(), s1_f[self.inter_lo:self.inter_hi].contiguous()
-            w3, s3 = w3_f[self.inter_lo:self.inter_hi].contiguous(), s3_f[self.inter_lo:self.inter_hi].contiguous()
+            wqkv, sqkv = f["wqkv"][rows].contiguous(), f["sqkv"][rows].contiguous()
+            wo = f["wo"][:, q_lo:q_hi].contiguous()
+            so = f["so"][:, q_lo // g:q_hi // g].contiguous()
+            w1, s1 = f["w1"][self.inter_lo:self.inter_hi].contiguous(), f["s1"][self.inter_lo:self.inter_hi].contiguous()
+            w3, s3 = f["w3"][self.inter_lo:self.inter_hi].contiguous(), f["s3"][self.inter_lo:self.inter_hi].contiguous()
             G = c.dim // g
             w13 = torch.empty((2 * self.inter_l, c.dim), dtype=torch.int8, device=dev)
             s13 = torch.empty((2 * self.inter_l, G), dtype=torch.float16, device=dev)
             ctx.pack_gate_up(w1, s1, w3, s3, self.inter_l, c.dim, G, w13, s13)
-            w2_f, s2_f = rand_w(c.dim, c.inter, t + 5)
-            w2 = w2_f[:, self.inter_lo:self.inter_hi].contiguous()
-            s2 = s2_f[:, self.inter_lo // g:self.inter_hi // g].contiguous()
+            w2 = f["w2"][:, self.inter_lo:self.inter_hi].contiguous()
+            s2 = f["s2"][:, self.inter_lo // g:self.inter_hi // g].contiguous()
             torch.cuda.synchronize()
-            del wqkv_f, sqkv_f, wo_f, so_f, w1_f, s1_f, w3_f, s3_f, w2_f, s2_f, w1, w3, s1, s3
-            lw = dict(attn_norm=rand_vec(c.dim, t + 6), ffn_norm=rand_vec(c.dim, t + 7),
-                      q_norm=rand_vec(D, t + 8) if c.qk_norm else None, k_norm=rand_vec(D, t + 9) if c.qk_norm else None, wqkv=wqkv, sqkv=sqkv, wo=wo, so=so, w13=w13, s13=s13, w2=w2, s2=s2)
+            lw = dict(attn_norm=f["attn_norm"], ffn_norm=f["ffn_norm"], q_norm=f["q_norm"], k_norm=f["k_norm"],
+                      wqkv=wqkv, sqkv=sqkv, wo=wo, so=so, w13=w13, s13=s13, w2=w2, s2=s2)
+            del f, w1, w3, s1, s3
             if pack:  # what the loader does once per weight: pack for the decode kernel and register the pair
                 for name, sname, n, k in (("wqkv", "sqkv", self.qkv_n, c.dim), ("wo", "so", c.dim, self.attn_k),
                                           ("w13", "s13", 2 * self.inter_l, c.dim), ("w2", "s2", c.dim, self.inter_l)):
@@ -148,25 +202,16 @@ class SlowARStack:
                     if nbytes:
                         P = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
                         ctx.pack_weight(lw[name], lw[sname], n, k, g, P)
-                        ctx.register_packed_weight(lw[name], P)
+                        ctx.register_packed_weight(lw[name], P, n, k, g)
+                        self._registered.append(lw[name])
                         self._keep.append(P)
                         lw[name + "_packed"] = P
             self.layers.append(lw)
-        self.final_norm = rand_vec(c.dim, 999983)
-        freqs = (1.0 / np.power(np.float32(c.rope_base), (np.float32(2.0) * np.arange(D // 2, dtype=np.float32) /
-                                                           np.float32(D)))).astype(np.float32)
-        self.freqs = torch.from_numpy(freqs).to(dev)
-
-        # paged KV, already holding `context` tokens per sequence (synthetic prefill)
-        bt = c.block_tokens
-        self.max_blocks = (context + max_new + bt - 1) // bt
-        nblocks = batch * self.max_blocks
-        gen.manual_seed(seed + 4242 + tp_rank)
-        shape = (nblocks, c.n_layer, self.nkv_l, bt, D)
-        self.k_cache = (torch.randn(shape, dtype=torch.float32, device=dev, generator=gen) * 0.5).half()
-        self.v_cache = (torch.randn(shape, dtype=torch.float32, device=dev, generator=gen) * 0.5).half()
-        perm = torch.randperm(nblocks, device=dev, generator=gen).to(torch.int32)
-        self.block_table = perm.view(batch, self.max_blocks).contiguous()
+        self.final_norm = final_norm_weight(torch, cfg, seed, dev)
+        self.freqs = rope_frequencies(torch, cfg, dev)
+        # paged KV, already holding `context` tokens per sequence (synthetic prefill); a rank keeps its kv heads
+        self.k_cache, self.v_cache, self.block_table, self.max_blocks = synthetic_kv(
+            torch, cfg, batch, context, max_new, seed, dev, kv_heads=(tp_rank * self.nkv_l, self.nkv_l))
         self.positions = torch.full((batch,), context, dtype=torch.int32, device=dev)   # the new token's position
         self.seq_lens = torch.full((batch,), context + 1, dtype=torch.int32, device=dev)
         self.context0 = context
@@ -306,6 +351,12 @@ class SlowARStack:
             ctx.linear_q(lw["w13"], lw["s13"], g, self.xq, self.xs, self.act, B, 2 * self.inter_l, c.dim,
                          epilogue=capi.EPI_SWIGLU)
             ctx.linear_q(lw["w2"], lw["s2"], g, self.actq, self.acts, self.delta, B, c.dim, self.inter_l)
+
+    def close(self):
+        """Removes this stack's weights from the context's packed-weight registry (before the tensors are freed)."""
+        for W in self._registered:
+            self.ctx.register_packed_weight(W, None)
+        self._registered = []
 
     def reset_positions(self):
         self.positions.fill_(self.context0)

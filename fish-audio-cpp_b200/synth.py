@@ -9,8 +9,12 @@ from __future__ import annotations
 
 import numpy as np
 
-# The slow-AR projections: name -> (K, N). gate_up is the two 9728-row matrices, packed.
-PROJECTIONS = {"qkv": (2560, 6144), "o": (4096, 2560), "gate_up": (2560, 19456), "down": (9728, 2560)}
+# The slow-AR projections: name -> (K, N). gate_up is the two 9728-row matrices, packed; gate is one of them
+# alone (w1 as the reference runs it, src/engine/dual_ar_engine.cc:640-644): the single-GEMM headline case.
+PROJECTIONS = {"qkv": (2560, 6144), "o": (4096, 2560), "gate_up": (2560, 19456), "down": (9728, 2560),
+               "gate": (2560, 9728)}
+# The four projections of a layer (the decode sweep and the prefill cases run over these).
+LAYER_PROJECTIONS = ("qkv", "o", "gate_up", "down")
 
 
 def num_groups(K: int, g: int) -> int:

@@ -4,8 +4,12 @@
  * Drop-in for the kernel-layer boundary of KBlackMeow/fish-audio-cpp: every
  * entry point names the reference interface it replaces (path:line inside
  * that project). All pointers are DEVICE pointers owned by the caller unless
- * said otherwise; `stream` is a cudaStream_t passed as void*. Every call is
- * asynchronous on `stream`, never allocates, never synchronises, and returns a
+ * said otherwise; `stream` is a cudaStream_t passed as void*. The calls of "the
+ * path" and "decode-step neighbours" below are asynchronous on `stream`, never
+ * allocate and never synchronise. Set-up and read-out calls are the exception and
+ * say so: w8a8_create / w8a8_destroy / w8a8_tp_create / w8a8_tp_connect allocate
+ * or map device memory, w8a8_check_device_status, w8a8_static_scratch_check_status
+ * and w8a8_decode_stack_timeline synchronise the stream. Every call returns a
  * status code (no C++ exception crosses this boundary).
  *
  * Naming: M = tokens, N = output features (weight rows), K = input features,
@@ -61,7 +65,8 @@ typedef struct w8a8_ctx w8a8_ctx;
 
 W8A8_API int w8a8_create(w8a8_ctx** out, int device, size_t workspace_bytes);
 W8A8_API int w8a8_destroy(w8a8_ctx* ctx);
-/* Scratch a w8a8_linear call of this shape needs (codes + scales for M > 32; 0 below). */
+/* Scratch a w8a8_linear call of this shape needs in the context's workspace: the int8 codes
+ * [M, K] and fp32 scales [M, G], each rounded up to 256 bytes (the same for every M). */
 W8A8_API size_t w8a8_workspace_bytes(int M, int N, int K, int group_size);
 W8A8_API size_t w8a8_ctx_workspace_bytes(const w8a8_ctx* ctx);
 /* Polls the context's device error word (set by a kernel whose bounded wait ran
@@ -176,6 +181,11 @@ W8A8_API int w8a8_linear_static_scratch(const void* W, const void* w_scale, int 
                                const void* act_scale, const void* smooth_inv, const void* X,
                                void* Y, int M, int N, int K, const w8a8_linear_opts* opts,
                                void* stream);
+/* No counterpart in the reference. w8a8_check_device_status for the context-free entry point above:
+ * reads (and clears) the error word that w8a8_linear_static_scratch's kernels set on the current
+ * device when one of their bounded waits runs out. Synchronises `stream`; allocates nothing.
+ * Returns W8A8_OK or W8A8_ERR_TIMEOUT. */
+W8A8_API int w8a8_static_scratch_check_status(void* stream);
 
 /* ---- loader side --------------------------------------------------------- */
 /* ---- decode-step neighbours inside a layer ----------------------------------------------- */
@@ -303,8 +313,13 @@ W8A8_API int w8a8_tp_allreduce_rmsnorm_quantize(w8a8_ctx* ctx, void* x, const vo
 W8A8_API size_t w8a8_packed_weight_bytes(int N, int K, int group_size);
 W8A8_API int w8a8_pack_weight(w8a8_ctx* ctx, const void* W, const void* w_scale, int N, int K,
                      int group_size, void* packed_out, void* stream);
-/* packed == NULL removes the entry. */
-W8A8_API int w8a8_register_packed_weight(w8a8_ctx* ctx, const void* W, const void* packed);
+/* Registers the image `packed` (made by w8a8_pack_weight for exactly this N, K, group_size) under the
+ * raw weight pointer W. The image is used only by calls whose N, K and group size equal the registered
+ * ones: should W be freed and its address reused for another tensor before the entry is removed, a call
+ * with another shape falls back to the row-major kernels instead of streaming a stale image. Remove the
+ * entry (packed == NULL; N, K, group_size ignored) before freeing either buffer. */
+W8A8_API int w8a8_register_packed_weight(w8a8_ctx* ctx, const void* W, const void* packed, int N, int K,
+                                int group_size);
 
 /* Pre-pack for W8A8_EPI_SWIGLU: interleaves w1 (gate) and w3 (up), both int8 [inter, K] with
  * fp16 scales [inter, G], into W_out int8 [2*inter, K] / scale_out fp16 [2*inter, G] in blocks

@@ -6,6 +6,7 @@ Needs a GPU to run. Arguments are device pointers (ints) in the reference's own 
 from __future__ import annotations
 
 import ctypes as C
+import os
 import subprocess
 from pathlib import Path
 
@@ -18,9 +19,16 @@ def available() -> bool:
     return LIB_PATH.exists()
 
 
-def build(reference_root: str = "/root/reference") -> Path | None:
+def reference_root_default() -> str | None:
+    """The reference checkout: $FISH_REFERENCE_ROOT, else a directory named `reference` beside this repository."""
+    cand = os.environ.get("FISH_REFERENCE_ROOT") or str(HERE.parent.parent / "reference")
+    return cand if Path(cand, "src/kernels/int8_gemm.cu").exists() else None
+
+
+def build(reference_root_dir: str | None = None) -> Path | None:
     """Compiles the harness when the reference checkout is present; otherwise keeps what is there."""
-    if Path(reference_root, "src/kernels/int8_gemm.cu").exists():
+    reference_root = reference_root_dir or reference_root_default()
+    if reference_root and Path(reference_root, "src/kernels/int8_gemm.cu").exists():
         subprocess.run(["make", "-C", str(HERE), "ref", f"REF={reference_root}"], check=True, capture_output=True)
     return LIB_PATH if LIB_PATH.exists() else None
 

@@ -1,7 +1,7 @@
 """Generates tests/golden/w8a8_reference_kernels.npz by running the REFERENCE's own CUDA kernels
 (oracle/_ref/libfishref.so, built from the reference checkout) on seeded inputs. Run on a GPU box:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py [OUTPUT.npz]     (default: w8a8_reference_kernels.npz beside this script)
 
 The fixtures hold, per case, the seed and shape (inputs are regenerated from the seed by
 fish-audio-cpp_b200/synth.py) and the reference's int8 codes, fp32 activation scales and fp16
@@ -66,8 +66,8 @@ def main():
     out.update(rms_x=x.view(np.uint16), rms_w=w.view(np.uint16), rms_out=do.cpu().numpy().view(np.uint16),
                elt_a=a.view(np.uint16), elt_b=b.view(np.uint16), elt_silu=outs["silu"], elt_mul=outs["mul"],
                elt_add=outs["add"])
-    dst = ROOT / "gpurun_out" / "w8a8_reference_kernels.npz"
-    dst.parent.mkdir(exist_ok=True)
+    dst = Path(sys.argv[1]) if len(sys.argv) > 1 else Path(__file__).resolve().parent / "w8a8_reference_kernels.npz"
+    dst.parent.mkdir(parents=True, exist_ok=True)
     np.savez_compressed(dst, **out)
     print("wrote", dst, dst.stat().st_size, "bytes")
 

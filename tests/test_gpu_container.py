@@ -68,7 +68,7 @@ def test_sidecar_images_equal_the_numpy_pack_and_stream_through_the_decode_kerne
     X = synth.activations(np.random.default_rng(3), M, lin.K)
     dW, dS, dX = dev(lin.W), dev(lin.scale), dev(X)
     dImg = dev(side.get(name + ct.PACKED_SUFFIX).view(np.uint8))
-    ctx.register_packed_weight(dW, dImg)
+    ctx.register_packed_weight(dW, dImg, lin.N, lin.K, lin.group_size)
     try:
         dY = torch.empty((M, lin.N), dtype=torch.float16, device="cuda")
         dD = torch.full((M, lin.N, lin.G), -1, dtype=torch.int32, device="cuda")
@@ -107,7 +107,7 @@ def test_sampled_rows_lm_head_equals_the_rows_of_the_full_head(ctx, oracle, pkg)
     n = len(rows)
     img = torch.empty(ctx.packed_weight_bytes(n, K, g), dtype=torch.uint8, device="cuda")
     ctx.pack_weight(dWc, dSc, n, K, g, img)
-    ctx.register_packed_weight(dWc, img)
+    ctx.register_packed_weight(dWc, img, n, K, g)
     try:
         dYc = torch.empty((M, n), dtype=torch.float16, device="cuda")
         ctx.linear(dWc, dSc, g, dX, dYc, M, n, K, kernel=pkg.KERNEL_GEMV_PACKED)

@@ -20,6 +20,10 @@ REL_BAR = 2e-3
 # (The reference's own M <= 4 kernels sum per-thread partials in a tree and differ from its M > 4
 # path by the same kind of amount.)
 REORDER_EPS = 4 * 2.0 ** -24
+# The third clause must stay the exception: at most this fraction of a case's elements may need it.
+# conftest.py prints the observed counts at the end of the run.
+REORDER_FRACTION_BAR = 1e-3
+REORDER_STATS = {}  # case label -> [elements compared, elements that passed only through the third clause]
 
 
 def dev(a):
@@ -53,7 +57,13 @@ def assert_close_fp16(oracle, got, want, what="", abs_terms=None):
     if abs_terms is not None:
         # half an fp16 ulp of slack on each side for the final roundings of got and want
         slack = REORDER_EPS * abs_terms + np.spacing(np.abs(want).astype(np.float16)).astype(np.float64)
+        third_only = bad & (diff <= slack)
         bad &= diff > slack
+        stat = REORDER_STATS.setdefault(what, [0, 0])
+        stat[0] += int(got.size)
+        stat[1] += int(third_only.sum())
+        assert third_only.sum() <= max(1, REORDER_FRACTION_BAR * got.size), \
+            f"{what}: {int(third_only.sum())} of {got.size} elements pass only through the re-ordering clause"
     assert not bad.any(), f"{what}: {bad.sum()} elements off; max ulp {ulp[bad].max()}, max rel {rel[bad].max():.3g}"
 
 
@@ -301,7 +311,7 @@ def test_packed_weight_stream(ctx, oracle, pkg, M, N, K, g):
     ctx.pack_weight(dW, dS, N, K, g, dP)
     torch.cuda.synchronize()
     assert np.array_equal(dP.cpu().numpy(), want_pack)
-    ctx.register_packed_weight(dW, dP)
+    ctx.register_packed_weight(dW, dP, N, K, g)
     try:
         outs = []
         for rep in range(2):
@@ -344,7 +354,7 @@ def test_rmsnorm_linear_equals_two_call_chain(ctx, oracle, pkg, M, N, K, g, with
     if packed and ctx.packed_weight_bytes(N, K, g):
         dP = torch.empty((ctx.packed_weight_bytes(N, K, g),), dtype=torch.uint8, device="cuda")
         ctx.pack_weight(dW, dS, N, K, g, dP)
-        ctx.register_packed_weight(dW, dP)
+        ctx.register_packed_weight(dW, dP, N, K, g)
     try:
         # the chain
         cx = dev(X)
@@ -389,7 +399,7 @@ def test_rmsnorm_linear_epilogues_and_argument_checks(ctx, oracle, pkg):
     dW, dS, dw, dr, dx = dev(W), dev(ws), dev(w), dev(r), dev(X)
     dP = torch.empty((ctx.packed_weight_bytes(2 * inter, K, g),), dtype=torch.uint8, device="cuda")
     ctx.pack_weight(dW, dS, 2 * inter, K, g, dP)
-    ctx.register_packed_weight(dW, dP)
+    ctx.register_packed_weight(dW, dP, 2 * inter, K, g)
     try:
         cq = torch.empty((M, K), dtype=torch.int8, device="cuda")
         cs = torch.empty((M, K // g), dtype=torch.float32, device="cuda")
@@ -455,12 +465,17 @@ def test_gemm_tcgen05_epilogues(ctx, oracle, pkg):
     ctx.check_device_status()
 
 
-@pytest.mark.parametrize("name,g", [("qkv", 256), ("o", 64), ("down", 256), ("gate_up", 64)])
-def test_prefill_shapes_full_size(ctx, oracle, name, g):
-    """configs[2] at M = 2048: the whole GEMM runs on the GPU; a random 48-token x 192-row sub-problem is
-    recomputed by the oracle (each output depends only on its own token row and weight row)."""
+PREFILL_CASES = [(name, g, 2048) for name in ("qkv", "o", "gate_up", "down") for g in (256, 64)] + \
+    [(name, g, 8192) for name in ("qkv", "o", "gate_up", "down") for g in (256, 64)]
+
+
+@pytest.mark.parametrize("name,g,M", PREFILL_CASES)
+def test_prefill_shapes_full_size(ctx, oracle, name, g, M):
+    """configs[2], all sixteen cases (four projections x g in {256, 64} x M in {2048, 8192}): the whole GEMM
+    runs on the GPU; a random 48-token x 192-row sub-problem is recomputed by the oracle (each output
+    depends only on its own token row and weight row) and must agree bit for bit; two runs of the full
+    problem must agree bit for bit as well."""
     K, N = synth.PROJECTIONS[name]
-    M = 2048
     rng = np.random.default_rng(7 + g)
     X = synth.activations(rng, M, K)
     gen = torch.Generator(device="cuda").manual_seed(g + K)
@@ -468,9 +483,14 @@ def test_prefill_shapes_full_size(ctx, oracle, name, g):
     G = K // g
     dS = torch.empty((N, G), dtype=torch.float32, device="cuda").uniform_(1e-3, 5e-3, generator=gen).half()
     dY = torch.empty((M, N), dtype=torch.float16, device="cuda")
-    ctx.linear(dW, dS, g, dev(X), dY, M, N, K)
+    dX = dev(X)
+    ctx.linear(dW, dS, g, dX, dY, M, N, K)
+    dY2 = torch.empty_like(dY)
+    ctx.linear(dW, dS, g, dX, dY2, M, N, K)
     torch.cuda.synchronize()
     ctx.check_device_status()
+    assert torch.equal(dY.view(torch.int16), dY2.view(torch.int16))
+    del dY2
     ti = np.sort(rng.choice(M, 48, replace=False))
     ri = np.sort(rng.choice(N, 192, replace=False))
     tt, rr = torch.from_numpy(ti).cuda(), torch.from_numpy(ri).cuda()
@@ -583,6 +603,64 @@ def test_shim_has_reference_semantics(ctx, oracle):
         assert_close_fp16(oracle, dY.cpu().numpy(), oracle.linear(W, ws1, gs, X), f"group_size={gs}")
 
 
+def test_shim_neighbours_run_and_equal_the_c_abi(ctx, oracle):
+    """fish::kernels::rms_norm / silu_forward / mul_forward / residual_add through the C++ shim (reference
+    signatures, src/kernels/kernels.h:10-19, :111-141): executed, and bit-equal to the C ABI calls and the oracle."""
+    rng = np.random.default_rng(12)
+    T, D = 5, 2560
+    x = rng.standard_normal((T, D)).astype(np.float16)
+    w = rng.uniform(0.5, 1.5, D).astype(np.float16)
+    dx, dw = dev(x), dev(w)
+    a_out, b_out = torch.empty_like(dx), torch.empty_like(dx)
+    ctx.shim_rms_norm(dx, dw, a_out, T, D, 1e-6)
+    ctx.rms_norm(dx, dw, b_out, T, D, 1e-6)
+    torch.cuda.synchronize()
+    assert torch.equal(a_out, b_out)
+    assert oracle.ulp_distance_fp16(a_out.cpu().numpy(), oracle.rms_norm(x, w, 1e-6)).max() <= 1
+    n = T * D
+    a = (rng.standard_normal(n) * 2).astype(np.float16)
+    b = rng.standard_normal(n).astype(np.float16)
+    db = dev(b)
+    s1, s2 = dev(a), dev(a)
+    ctx.shim_silu_forward(s1, n); ctx.silu(s2, n)
+    m1, m2 = dev(a), dev(a)
+    ctx.shim_mul_forward(m1, db, n); ctx.mul(m2, db, n)
+    r1, r2 = dev(a), dev(a)
+    ctx.shim_residual_add(r1, db, n); ctx.residual_add(r2, db, n)
+    torch.cuda.synchronize()
+    assert torch.equal(s1, s2) and torch.equal(m1, m2) and torch.equal(r1, r2)
+    assert np.array_equal(m1.cpu().numpy(), oracle.mul(a, b))
+    assert np.array_equal(r1.cpu().numpy(), oracle.residual_add(a, b))
+    assert oracle.ulp_distance_fp16(s1.cpu().numpy(), oracle.silu(a)).max() <= 1
+
+
+def test_registered_image_is_ignored_for_another_shape(ctx, oracle, pkg):
+    """A packed image is streamed only by calls of the shape it was registered for: the same W pointer with
+    another N / K / group size (an address reused after a free) takes the row-major kernels and stays correct."""
+    M, N, K, g = 4, 64, 512, 256
+    X, W, ws = synth.linear_case(91, M, N, K, g)
+    dW, dS, dX = dev(W), dev(ws), dev(X)
+    img = torch.empty((ctx.packed_weight_bytes(N, K, g),), dtype=torch.uint8, device="cuda")
+    ctx.pack_weight(dW, dS, N, K, g, img)
+    ctx.register_packed_weight(dW, img, N, K, g)
+    try:
+        # the same bytes read as a [128, 256] matrix with its own scales: must not use the [64, 512] image
+        N2, K2 = 128, 256
+        W2 = W.reshape(N2, K2)
+        ws2 = synth.weight_scales(np.random.default_rng(3), N2, 1)
+        X2 = synth.activations(np.random.default_rng(4), M, K2)
+        dY = torch.empty((M, N2), dtype=torch.float16, device="cuda")
+        ctx.linear(dW, dev(ws2), g, dev(X2), dY, M, N2, K2)
+        torch.cuda.synchronize()
+        assert_close_fp16(oracle, dY.cpu().numpy(), oracle.linear(W2, ws2, g, X2), "stale registration")
+        with pytest.raises(pkg.W8A8Error):
+            ctx.linear(dW, dev(ws2), g, dev(X2), dY, M, N2, K2, kernel=pkg.KERNEL_GEMV_PACKED)
+        with pytest.raises(pkg.W8A8Error):  # a shape that cannot be packed cannot be registered
+            ctx.register_packed_weight(dW, img, N, 640, 64)
+    finally:
+        ctx.register_packed_weight(dW, None)
+
+
 @pytest.mark.skipif(not fishref.available(), reason="reference harness not built")
 @pytest.mark.parametrize("M,N,K,g", [(1, 256, 2560, 256), (3, 128, 4096, 64), (8, 256, 2560, 256), (16, 192, 1024, 64),
                                      (32, 64, 512, 256)])
@@ -631,9 +709,11 @@ def test_gemm_tcgen05_extreme_codes(ctx, oracle, pkg, g, wval, qval):
 
 
 # ---------------------------------------------------------------- headline shapes at full size
-@pytest.mark.parametrize("name", ["qkv", "o", "gate_up", "down"])
-@pytest.mark.parametrize("g", [256, 64])
-@pytest.mark.parametrize("M", [1, 4, 16])
+DECODE_CASES = [(name, g, M) for name in ("qkv", "o", "gate_up", "down") for g in (256, 64) for M in (1, 4, 16)] + \
+    [("gate", 256, 16)]  # configs[0]: the un-fused gate projection, M = 16, K = 2560, N = 9728, g = 256
+
+
+@pytest.mark.parametrize("name,g,M", DECODE_CASES)
 def test_decode_shapes_full_size(ctx, oracle, name, g, M):
     K, N = synth.PROJECTIONS[name]
     X, W, ws = synth.linear_case(1000 + M, M, N, K, g)
@@ -651,7 +731,7 @@ def test_decode_shapes_full_size(ctx, oracle, name, g, M):
 
 @pytest.mark.parametrize("name,g,M", [("qkv", 256, 8), ("o", 256, 8), ("gate_up", 256, 8), ("down", 256, 8), ("qkv", 64, 1),
                                       ("o", 64, 5), ("gate_up", 64, 8), ("down", 64, 3), ("gate_up", 256, 16), ("down", 64, 32),
-                                      ("lm_head", 256, 8), ("codebook_head", 64, 8)])
+                                      ("lm_head", 256, 8), ("codebook_head", 64, 8), ("gate", 256, 16)])
 def test_packed_decode_shapes_full_size(ctx, oracle, pkg, name, g, M):
     """The decode kernel proper (weights packed and registered, as the loader does) at the sizes of the
     benchmarks, the int8 LM head (2560 -> 155776) and the fast AR's codebook head included: int32 group sums
@@ -662,7 +742,7 @@ def test_packed_decode_shapes_full_size(ctx, oracle, pkg, name, g, M):
     dW, dS, dX = dev(W), dev(ws), dev(X)
     dPk = torch.empty((ctx.packed_weight_bytes(N, K, g),), dtype=torch.uint8, device="cuda")
     ctx.pack_weight(dW, dS, N, K, g, dPk)
-    ctx.register_packed_weight(dW, dPk)
+    ctx.register_packed_weight(dW, dPk, N, K, g)
     try:
         dump = N * G * M <= (1 << 27)  # the LM head's sums would be 190 MB: checked through the fp16 output only
         dP = torch.empty((M, N, G), dtype=torch.int32, device="cuda") if dump else None

@@ -44,6 +44,8 @@ def test_static_scratch_matches_context_entry_point_twice_in_a_row(ctx, pkg, ora
         torch.cuda.synchronize()
         assert close(oracle, got.cpu().numpy(), want.cpu().numpy()), (M, N, K, g)
         assert close(oracle, got.cpu().numpy(), oracle.linear(W, ws, g, X)), (M, N, K, g)
+    # no kernel of these calls gave up a bounded wait (the context-free counterpart of check_device_status)
+    pkg.static_scratch_check_status()
 
 
 def test_static_scratch_epilogue_and_per_token_mode(ctx, pkg, oracle):
