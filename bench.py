@@ -111,10 +111,19 @@ def sweep_cases():
     cases = []
     for M in (1, 4, 16):
         for g in (256, 64):
-            for name, (K, N) in synth.PROJECTIONS.items():
+            for name in synth.LAYER_PROJECTIONS:
+                K, N = synth.PROJECTIONS[name]
                 if ONLY is None or ONLY == (name, M, g):
                     cases.append({"name": name, "M": M, "N": N, "K": K, "g": g})
     return cases
+
+
+def config0_cases():
+    """configs[0]: the single gate-projection GEMM, M = 16, K = 2560, N = 9728, g = 256."""
+    from fish_audio_cpp_b200 import synth
+
+    K, N = synth.PROJECTIONS["gate"]
+    return [{"name": "gate", "M": 16, "N": N, "K": K, "g": 256}]
 
 
 class DecodeSweep:
@@ -128,17 +137,20 @@ class DecodeSweep:
 
     ROTATION_BYTES = 320e6
 
-    def __init__(self, torch, ctx, seed=1234, reference=False, pack=True):
+    def __init__(self, torch, ctx, seed=1234, reference=False, pack=True, cases=None):
         from fish_audio_cpp_b200 import synth
 
         self.torch, self.ctx, self.reference = torch, ctx, reference
-        self.cases = sweep_cases()
+        self.cases = sweep_cases() if cases is None else cases
         gen = torch.Generator(device="cuda")
         gen.manual_seed(seed)
         rng = np.random.default_rng(seed)
         self.weights = {}
+        self.packed = []
         for g in (256, 64):
             for name, (K, N) in synth.PROJECTIONS.items():
+                if not any(c["name"] == name and c["g"] == g for c in self.cases):
+                    continue
                 G = synth.num_groups(K, g)
                 copies = max(3, int(np.ceil(self.ROTATION_BYTES / (N * K))))
                 self.weights[(name, g)] = [
@@ -147,12 +159,11 @@ class DecodeSweep:
                     for _ in range(copies)]
                 if not reference and pack:
                     # what a loader does once per weight: pack for the decode kernel and register the pair
-                    self.packed = getattr(self, "packed", [])
                     for (W, S) in self.weights[(name, g)]:
                         P = torch.empty((ctx.packed_weight_bytes(N, K, g),), dtype=torch.uint8, device="cuda")
                         ctx.pack_weight(W, S, N, K, g, P)
-                        ctx.register_packed_weight(W, P)
-                        self.packed.append(P)
+                        ctx.register_packed_weight(W, P, N, K, g)
+                        self.packed.append((W, P))
         self.host_x, self.dev_x, self.dev_y, self.host_y = [], [], [], []
         for c in self.cases:
             x = synth.activations(rng, c["M"], c["K"])
@@ -175,6 +186,12 @@ class DecodeSweep:
             from oracle import fishref
 
             self.fishref = fishref
+
+    def close(self):
+        """Unregisters the packed images (before the tensors are freed) and drops the graphs."""
+        for W, _ in self.packed:
+            self.ctx.register_packed_weight(W, None)
+        self.packed, self.graphs = [], {}
 
     def launch_case(self, i, copy):
         c = self.cases[i]
@@ -253,43 +270,56 @@ class PrefillSweep:
     tcgen05 GEMM), fp16 in, fp16 out. Activations + weights of a case (up to ~370 MB) exceed L2 together
     with the rotation over the eight weight sets."""
 
-    def __init__(self, torch, ctx, seed=4321, Ms=(2048, 8192)):
+    def __init__(self, torch, ctx, seed=4321, Ms=(2048, 8192), reference=False):
         from fish_audio_cpp_b200 import synth
 
-        self.torch, self.ctx = torch, ctx
+        self.torch, self.ctx, self.reference = torch, ctx, reference
+        if reference:
+            from oracle import fishref
+
+            self.fishref = fishref
+        proj = {n: synth.PROJECTIONS[n] for n in synth.LAYER_PROJECTIONS}
         gen = torch.Generator(device="cuda").manual_seed(seed)
-        rng = np.random.default_rng(seed)
         self.cases, self.w = [], {}
         for g in (256, 64):
-            for name, (K, N) in synth.PROJECTIONS.items():
+            for name, (K, N) in proj.items():
                 G = K // g
                 self.w[(name, g)] = (
                     torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda", generator=gen),
                     torch.empty((N, G), dtype=torch.float32, device="cuda").uniform_(1e-3, 5e-3, generator=gen).half())
         self.x = {}
         for M in Ms:
-            for K in sorted({k for k, _ in synth.PROJECTIONS.values()}):
+            for K in sorted({k for k, _ in proj.values()}):
                 x = torch.randn((M, K), dtype=torch.float32, device="cuda", generator=gen)
                 idx = torch.randperm(K, device="cuda", generator=gen)[:max(1, round(0.005 * K))]
                 x[:, idx] *= 20.0
                 self.x[(M, K)] = x.half()
         for M in Ms:
             for g in (256, 64):
-                for name, (K, N) in synth.PROJECTIONS.items():
+                for name, (K, N) in proj.items():
                     if ONLY is None or ONLY == (name, M, g):
                         self.cases.append({"name": name, "M": M, "N": N, "K": K, "g": g})
         self.y = torch.empty((max(Ms), 19456), dtype=torch.float16, device="cuda")
         self.ops_per_step = sum(2 * c["M"] * c["N"] * c["K"] for c in self.cases)
         self.bytes_per_step = sum(algorithmic_bytes(c["M"], c["N"], c["K"], c["g"]) for c in self.cases)
-        self.launches_per_step = 2 * len(self.cases)
+        # the reference: quantiser + per group (cuBLAS GEMM + accumulate) + memset + cast (int8_gemm.cu:415-505)
+        self.launches_per_step = 2 * len(self.cases) if not reference else sum(
+            2 * (c["K"] // c["g"]) + 3 for c in self.cases)
         self.eager, self.split_k, self.graphs = False, 0, {}
-        self.host_x = {k: v.cpu().pin_memory() for k, v in self.x.items() if k[0] == min(Ms)}
-        self.host_y = torch.empty((min(Ms), 19456), dtype=torch.float16).pin_memory()
         self.h2d = self.d2h = 0
+
+    def close(self):
+        self.w, self.x, self.y = {}, {}, None
 
     def run_case(self, c):
         W, S = self.w[(c["name"], c["g"])]
-        self.ctx.linear(W, S, c["g"], self.x[(c["M"], c["K"])], self.y, c["M"], c["N"], c["K"])
+        if self.reference:
+            s = self.torch.cuda.current_stream().cuda_stream or None
+            self.fishref.int8_dequant_gemm_fp16(W.data_ptr(), S.data_ptr(), c["g"], None, None,
+                                                self.x[(c["M"], c["K"])].data_ptr(), self.y.data_ptr(), c["N"], c["M"],
+                                                c["K"], s)
+        else:
+            self.ctx.linear(W, S, c["g"], self.x[(c["M"], c["K"])], self.y, c["M"], c["N"], c["K"])
 
     def step(self, e2e=False):
         for c in self.cases:
@@ -318,31 +348,12 @@ class PrefillSweep:
                         "tops": round(2 * c["M"] * c["N"] * c["K"] / us / 1e6, 1)})
         return out
 
-    def library_int8_tops(self):
-        """cuBLASLt int8 -> int32 at 8192^3 through torch._int_mm: a library figure for context only."""
-        t = self.torch
-        try:
-            a = t.randint(-127, 128, (8192, 8192), dtype=t.int8, device="cuda")
-            bm = t.randint(-127, 128, (8192, 8192), dtype=t.int8, device="cuda")
-            for _ in range(3):
-                t._int_mm(a, bm)
-            t.cuda.synchronize()
-            best = 1e9
-            for _ in range(10):
-                e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
-                e0.record()
-                t._int_mm(a, bm)
-                e1.record()
-                t.cuda.synchronize()
-                best = min(best, e0.elapsed_time(e1))
-            return round(2 * 8192 ** 3 / (best * 1e-3) / 1e12, 1)
-        except Exception:  # noqa: BLE001
-            return None
-
 
 class DecodeStack:
     """configs[3]: the full slow-AR decoder stack, batch 8, context 1024, g256, tensor-parallel over the
-    ranks of the job. One step = one token for each of the 8 sequences, replayed from a CUDA graph."""
+    ranks of the job. One step = one token for each of the 8 sequences, replayed from a CUDA graph.
+    reference=True: the same step through the reference's own CUDA kernels (oracle/ref_stack.py), eager, built with
+    torch alone (the product library is not loaded)."""
 
     def __init__(self, torch, ctx, world, rank, dist, layers=36, batch=8, context=1024, group=256, reference=False,
                  tp_mode="fused"):
@@ -350,8 +361,28 @@ class DecodeStack:
 
         self.torch, self.ctx, self.dist, self.world = torch, ctx, dist, world
         cfg = S.SlowARConfig(n_layer=layers, group=group)
-        ar, gather = None, None
+        self.cfg, self.batch, self.context = cfg, batch, context
         self.tp_mode = tp_mode if world > 1 else "none"
+        self.host_x = (torch.randn((batch, cfg.dim), generator=torch.Generator().manual_seed(3)) * 0.5).half().pin_memory()
+        self.dev_x = self.host_x.cuda()
+        self.host_out = torch.empty((batch, cfg.dim), dtype=torch.float16).pin_memory()
+        self.graphs, self.eager, self.split_k, self.one_launch, self.cases = {}, False, 0, False, []
+        self.h2d, self.d2h = self.host_x.numel() * 2, self.host_out.numel() * 2
+        self.steps_done = 0
+        weight_bytes_full = layers * sum(n * k + 2 * n * (k // group) for n, k in (
+            ((cfg.n_head + 2 * cfg.n_kv) * cfg.head_dim, cfg.dim), (cfg.dim, cfg.n_head * cfg.head_dim),
+            (2 * cfg.inter, cfg.dim), (cfg.dim, cfg.inter)))
+        kv_full = 2 * batch * context * layers * cfg.n_kv * cfg.head_dim * 2
+        if reference:
+            from oracle import ref_stack
+
+            self.st = None
+            self.ref = ref_stack.ReferenceStack(torch, cfg, batch, context, max_new=128, seed=7)
+            self.launches_per_step = 0
+            self.bytes_per_step = weight_bytes_full + kv_full
+            self.ops_per_step = 0
+            return
+        ar, gather = None, None
         if world > 1 and tp_mode == "nccl":
             ar = lambda t: dist.all_reduce(t)  # noqa: E731  (fp16 sum over NVLink, NCCL: the baseline)
         if world > 1 and tp_mode == "fused":
@@ -360,24 +391,17 @@ class DecodeStack:
                 dist.all_gather_object(out, handle)
                 return out
         self.st = S.SlowARStack(torch, ctx, cfg, batch, context, max_new=128, tp_rank=rank, tp_size=world,
-                                seed=7, all_reduce=ar, pack=not reference, tp_mode=tp_mode, gather_handles=gather)
-        self.cfg, self.batch, self.context = cfg, batch, context
-        self.ref = ReferenceStack(torch, self.st) if reference else None
-        self.host_x = (torch.randn((batch, cfg.dim), generator=torch.Generator().manual_seed(3)) * 0.5).half().pin_memory()
-        self.dev_x = self.host_x.cuda()
-        self.host_out = torch.empty((batch, cfg.dim), dtype=torch.float16).pin_memory()
-        self.graphs = {}
-        self.eager = False
-        self.split_k = 0
-        self.one_launch = False
+                                seed=7, all_reduce=ar, pack=True, tp_mode=tp_mode, gather_handles=gather)
+        self.ref = None
         self.launches_per_step = self.st.launches_per_step
-        self.h2d = self.host_x.numel() * 2
-        self.d2h = self.host_out.numel() * 2
-        self.cases = []
         # algorithmic bytes of one step on one rank: its weight shards + scales, the KV it reads, activations ~0
         self.bytes_per_step = self.st.weight_bytes + self.st.kv_bytes_per_step(context)
         self.ops_per_step = 2 * batch * sum(lw[n].numel() for lw in self.st.layers for n in ("wqkv", "wo", "w13", "w2"))
-        self.steps_done = 0
+
+    def close(self):
+        self.graphs = {}
+        if self.st is not None:
+            self.st.close()
 
     def body(self, e2e):
         if e2e:
@@ -432,8 +456,8 @@ class DecodeStack:
     def step(self, e2e=False):
         t = self.torch
         if self.ref is not None:
-            self.st.reset_positions()
-            self.ref.decode_step(self.dev_x)
+            self.ref.reset_positions()
+            self.ref.decode_step(self.dev_x, advance=False)
             return
         # the context grows by one token per step; go back to 1024 every 64 steps so that it stays "1024"
         if self.steps_done and self.steps_done % 64 == 0:
@@ -464,35 +488,56 @@ class FastARFrame:
     (the mirror of DualAREngine::fast_codebook_decode_device, src/engine/dual_ar_engine.cc:769-844), then the final
     norm and the codebook head 2560 -> 4096 (g64). Sampling and the embedding lookup of the sampled code are left
     out: every codebook step gets the same synthetic input rows. The frame is replayed from one CUDA graph.
-    `lm_head()` times the slow AR's int8 LM head 2560 -> 155776 (g256) at M = 1 and 8 on the side."""
+    `lm_head()` times the slow AR's int8 LM head 2560 -> 155776 (g256) at M = 1 and 8 on the side.
+    reference=True: the same frame through the reference's own CUDA kernels, eager (oracle/ref_stack.py)."""
 
-    def __init__(self, torch, ctx, batch=8, codebooks=10):
-        from fish_audio_cpp_b200 import stack as S, synth
+    def __init__(self, torch, ctx, batch=8, codebooks=10, reference=False):
+        from fish_audio_cpp_b200 import stack as S
 
-        self.torch, self.ctx, self.batch, self.codebooks = torch, ctx, batch, codebooks
+        self.torch, self.ctx, self.batch, self.codebooks, self.reference = torch, ctx, batch, codebooks, reference
         cfg = S.SlowARConfig(n_layer=4, group=64, qk_norm=False)
         self.cfg = cfg
-        self.st = S.SlowARStack(torch, ctx, cfg, batch, 0, max_new=32, seed=17)
         gen = torch.Generator(device="cuda").manual_seed(5)
         self.head_w = torch.randint(-127, 128, (4096, cfg.dim), dtype=torch.int8, device="cuda", generator=gen)
         self.head_s = torch.empty((4096, cfg.dim // 64), dtype=torch.float32, device="cuda").uniform_(
             1e-3, 5e-3, generator=gen).half()
-        P = torch.empty((ctx.packed_weight_bytes(4096, cfg.dim, 64),), dtype=torch.uint8, device="cuda")
-        ctx.pack_weight(self.head_w, self.head_s, 4096, cfg.dim, 64, P)
-        ctx.register_packed_weight(self.head_w, P)
-        self._keep = [P]
         self.logits = torch.empty((batch, 4096), dtype=torch.float16, device="cuda")
         self.host_x = (torch.randn((batch, cfg.dim), generator=torch.Generator().manual_seed(3)) * 0.5).half().pin_memory()
         self.dev_x = self.host_x.cuda()
         self.host_logits = torch.empty((batch, 4096), dtype=torch.float16).pin_memory()
         self.graphs, self.eager, self.split_k, self.cases = {}, False, 0, []
-        self.launches_per_step = codebooks * (self.st.launches_per_step + 2)
         self.h2d, self.d2h = self.host_x.numel() * 2, self.host_logits.numel() * 2
         head_bytes = self.head_w.numel() + self.head_s.numel() * 2
         kv = sum(2 * batch * (t + 1) * cfg.n_layer * cfg.n_kv * cfg.head_dim * 2 for t in range(codebooks))
-        self.bytes_per_step = codebooks * (self.st.weight_bytes + head_bytes) + kv
+        g = cfg.group
+        stack_weight_bytes = cfg.n_layer * sum(n * k + 2 * n * (k // g) for n, k in (
+            ((cfg.n_head + 2 * cfg.n_kv) * cfg.head_dim, cfg.dim), (cfg.dim, cfg.n_head * cfg.head_dim),
+            (2 * cfg.inter, cfg.dim), (cfg.dim, cfg.inter)))
+        self.bytes_per_step = codebooks * (stack_weight_bytes + head_bytes) + kv
+        if reference:
+            from oracle import fishref, ref_stack
+
+            self.fishref = fishref
+            self.st = None
+            self.ref = ref_stack.ReferenceStack(torch, cfg, batch, 0, max_new=32, seed=17)
+            self.launches_per_step = 0
+            self.ops_per_step = 0
+            return
+        self.ref = None
+        self.st = S.SlowARStack(torch, ctx, cfg, batch, 0, max_new=32, seed=17)
+        P = torch.empty((ctx.packed_weight_bytes(4096, cfg.dim, 64),), dtype=torch.uint8, device="cuda")
+        ctx.pack_weight(self.head_w, self.head_s, 4096, cfg.dim, 64, P)
+        ctx.register_packed_weight(self.head_w, P, 4096, cfg.dim, 64)
+        self._keep = [P]
+        self.launches_per_step = codebooks * (self.st.launches_per_step + 2)
         self.ops_per_step = codebooks * 2 * batch * (sum(lw[n].numel() for lw in self.st.layers
                                                            for n in ("wqkv", "wo", "w13", "w2")) + self.head_w.numel())
+
+    def close(self):
+        self.graphs = {}
+        if self.st is not None:
+            self.ctx.register_packed_weight(self.head_w, None)
+            self.st.close()
 
     def body(self, e2e):
         if e2e:
@@ -504,8 +549,18 @@ class FastARFrame:
         if e2e:
             self.host_logits.copy_(self.logits, non_blocking=True)
 
+    def reference_body(self):
+        self.ref.reset_positions()
+        for _ in range(self.codebooks):
+            out = self.ref.decode_step(self.dev_x)
+            self.fishref.int8_dequant_gemm_fp16(self.head_w.data_ptr(), self.head_s.data_ptr(), 64, None, None,
+                                                out.data_ptr(), self.logits.data_ptr(), 4096, self.batch, self.cfg.dim)
+
     def step(self, e2e=False):
         t = self.torch
+        if self.reference:
+            self.reference_body()
+            return
         if self.eager:
             self.body(e2e)
         else:
@@ -532,7 +587,7 @@ class FastARFrame:
         Sc = t.empty((vocab, K // 256), dtype=t.float32, device="cuda").uniform_(1e-3, 5e-3, generator=gen).half()
         P = t.empty((ctx.packed_weight_bytes(vocab, K, 256),), dtype=t.uint8, device="cuda")
         ctx.pack_weight(W, Sc, vocab, K, 256, P)
-        ctx.register_packed_weight(W, P)
+        ctx.register_packed_weight(W, P, vocab, K, 256)
         out = {}
         for M in (1, 8):
             X = (t.randn((M, K), device="cuda", generator=gen) * 0.5).half()
@@ -556,7 +611,7 @@ class FastARFrame:
         n = len(rows)
         Pc = t.empty((ctx.packed_weight_bytes(n, K, 256),), dtype=t.uint8, device="cuda")
         ctx.pack_weight(Wc, Scc, n, K, 256, Pc)
-        ctx.register_packed_weight(Wc, Pc)
+        ctx.register_packed_weight(Wc, Pc, n, K, 256)
         flush = t.empty((256 << 20,), dtype=t.uint8, device="cuda")
         for M in (1, 8):
             X = (t.randn((M, K), device="cuda", generator=gen) * 0.5).half()
@@ -579,76 +634,6 @@ class FastARFrame:
         return out
 
 
-class ReferenceStack:
-    """configs[3] with the reference's own CUDA kernels (oracle/_ref, stock entry points) chained in the
-    order of DualAREngine::decode_step (src/engine/dual_ar_engine.cc:576-657) at batch 8: rms_norm,
-    int8_dequant_gemm_fp16 x5 (gate and up apart), silu, mul, residual_add x2, qk rms_norm x2, rope_qk,
-    paged_attention_decode. The engine itself cannot be built here (its build fetches dependencies from
-    the network and it wants a checkpoint); its per-head cudaMemcpyAsync KV writes, which are batch-1
-    host code, are stood in for by one vectorised scatter per layer. Launches are eager: the reference
-    linear allocates inside the call. Single GPU only (the reference has no multi-GPU path)."""
-
-    def __init__(self, torch, ours_stack):
-        from oracle import fishref
-
-        self.f, self.torch, self.st = fishref, torch, ours_stack
-        st, c = ours_stack, ours_stack.cfg
-        B, D = st.B, c.head_dim
-        h16 = dict(dtype=torch.float16, device="cuda")
-        self.ws1 = torch.empty((B, max(c.dim, c.inter)), **h16)
-        self.ws2 = torch.empty((B, max(st.qkv_n, c.inter, c.dim)), **h16)
-        self.up = torch.empty((B, c.inter), **h16)
-        self.qb = torch.empty((B, c.n_head, D), **h16)
-        self.kb = torch.empty((B, c.n_kv, D), **h16)
-        self.vb = torch.empty((B, c.n_kv, D), **h16)
-        self.att = torch.empty((B, c.n_head * D), **h16)
-        # un-interleave the packed gate/up weights back into the two matrices the reference expects
-        self.w1, self.w3 = [], []
-        for lw in st.layers:
-            W = lw["w13"].view(-1, 2, 8, c.dim)
-            Ssc = lw["s13"].view(-1, 2, 8, c.dim // c.group)
-            self.w1.append((W[:, 0].reshape(-1, c.dim).contiguous(), Ssc[:, 0].reshape(-1, c.dim // c.group).contiguous()))
-            self.w3.append((W[:, 1].reshape(-1, c.dim).contiguous(), Ssc[:, 1].reshape(-1, c.dim // c.group).contiguous()))
-        self.launches_per_step = 0
-
-    def gemm(self, W, S, X, Y, n_out, tokens, K):
-        self.f.int8_dequant_gemm_fp16(W.data_ptr(), S.data_ptr(), self.st.cfg.group, None, None, X.data_ptr(),
-                                      Y.data_ptr(), n_out, tokens, K)
-
-    def decode_step(self, x_in):
-        t, f, st = self.torch, self.f, self.st
-        c, B, D = st.cfg, st.B, st.cfg.head_dim
-        x = st.x
-        x.copy_(x_in)
-        p = lambda tt: tt.data_ptr()  # noqa: E731
-        pos = int(st.context0)
-        for l, lw in enumerate(st.layers):
-            f.rms_norm(p(x), p(lw["attn_norm"]), p(self.ws1), B, c.dim, c.eps)
-            self.gemm(lw["wqkv"], lw["sqkv"], self.ws1, self.ws2, st.qkv_n, B, c.dim)
-            qkv = self.ws2.view(-1)[:B * st.qkv_n].view(B, st.qkv_n)
-            self.qb.copy_(qkv[:, :c.n_head * D].reshape(B, c.n_head, D))
-            self.kb.copy_(qkv[:, c.n_head * D:(c.n_head + c.n_kv) * D].reshape(B, c.n_kv, D))
-            self.vb.copy_(qkv[:, (c.n_head + c.n_kv) * D:].reshape(B, c.n_kv, D))
-            f.rms_norm(p(self.qb), p(lw["q_norm"]), p(self.qb), B * c.n_head, D, c.eps)
-            f.rms_norm(p(self.kb), p(lw["k_norm"]), p(self.kb), B * c.n_kv, D, c.eps)
-            f.rope_qk(p(self.qb), p(self.kb), p(st.freqs), B, c.n_head, c.n_kv, 1, D, pos)
-            phys = st.block_table[:, pos // 16].long()
-            st.k_cache[phys, l, :, pos % 16] = self.kb
-            st.v_cache[phys, l, :, pos % 16] = self.vb
-            f.paged_attention_decode(p(self.qb), p(st.k_cache), p(st.v_cache), p(st.block_table), p(st.seq_lens),
-                                     p(self.att), B, c.n_head, D, st.max_blocks, 1.0 / D ** 0.5, l, c.n_layer, c.n_kv)
-            self.gemm(lw["wo"], lw["so"], self.att, self.ws1, c.dim, B, c.n_head * D)
-            f.residual_add(p(x), p(self.ws1), B * c.dim)
-            f.rms_norm(p(x), p(lw["ffn_norm"]), p(self.ws2), B, c.dim, c.eps)
-            self.gemm(self.w1[l][0], self.w1[l][1], self.ws2, self.ws1, c.inter, B, c.dim)
-            f.silu(p(self.ws1), B * c.inter)
-            self.gemm(self.w3[l][0], self.w3[l][1], self.ws2, self.up, c.inter, B, c.dim)
-            f.mul(p(self.ws1), p(self.up), B * c.inter)
-            self.gemm(lw["w2"], lw["s2"], self.ws1, self.ws2, c.dim, B, c.inter)
-            f.residual_add(p(x), p(self.ws2), B * c.dim)
-        f.rms_norm(p(x), p(st.final_norm), p(st.out), B, c.dim, c.eps)
-
-
 def cpu_baseline_stack(budget_s=12.0):
     """The scalar oracle on the host cores over one decoder layer's four linears at batch 8 (g256), repeated
     until about `budget_s` seconds of CPU work have been timed, scaled to 36 layers: the linears are > 99 % of
@@ -659,7 +644,8 @@ def cpu_baseline_stack(budget_s=12.0):
     threads = oracle.host_threads()
     rng = np.random.default_rng(99)
     cases = []
-    for name, (K, N) in synth.PROJECTIONS.items():
+    for name in synth.LAYER_PROJECTIONS:
+        K, N = synth.PROJECTIONS[name]
         cases.append((synth.activations(rng, 8, K), synth.weights(rng, N, K), synth.weight_scales(rng, N, K // 256), N))
     total_s, reps = 0.0, 0
     while total_s < budget_s and reps < 2000:
@@ -680,7 +666,8 @@ def cpu_baseline_sweep(budget_s=20.0):
     threads = oracle.host_threads()
     rng = np.random.default_rng(99)
     total_bytes, total_s, done = 0, 0.0, []
-    for name, (K, N) in synth.PROJECTIONS.items():
+    for name in synth.LAYER_PROJECTIONS:
+        K, N = synth.PROJECTIONS[name]
         M, g = 16, 256
         X, W, ws = synth.activations(rng, M, K), synth.weights(rng, N, K), synth.weight_scales(rng, N, K // g)
         rows = N
@@ -694,7 +681,124 @@ def cpu_baseline_sweep(budget_s=20.0):
             "sample": f"projections {'+'.join(done)} at M=16 g=256, all rows, one pass ({total_s:.2f} s)"}
 
 
+def cpu_baseline_prefill(budget_s=15.0):
+    """The scalar oracle on the host cores: a 64-token slice of the gate_up projection at g=256 (all 19456 rows),
+    scaled by its ops; reported in TOPS."""
+    from fish_audio_cpp_b200 import synth
+    from oracle import oracle
+
+    threads = oracle.host_threads()
+    rng = np.random.default_rng(98)
+    K, N = synth.PROJECTIONS["gate_up"]
+    M, g = 64, 256
+    X, W, ws = synth.activations(rng, M, K), synth.weights(rng, N, K), synth.weight_scales(rng, N, K // g)
+    total_s, reps = 0.0, 0
+    while total_s < budget_s and reps < 50:
+        total_s += oracle.timed_linear(W, ws, g, X, N, threads)
+        reps += 1
+    return {"value": 2.0 * M * N * K * reps / total_s / 1e12, "unit": "TOPS", "cores": threads, "kind": "port",
+            "sample": f"gate_up at g=256, a {M}-token slice, all rows, {reps} times ({total_s:.1f} s of CPU work)"}
+
+
 # ------------------------------------------------------------------------------------------
+def int8_library_tops(torch):
+    """cuBLASLt int8 -> int32 at 8192^3 through torch._int_mm: the measured int8 tensor figure of this GPU."""
+    t = torch
+    try:
+        a = t.randint(-127, 128, (8192, 8192), dtype=t.int8, device="cuda")
+        bm = t.randint(-127, 128, (8192, 8192), dtype=t.int8, device="cuda")
+        for _ in range(3):
+            t._int_mm(a, bm)
+        t.cuda.synchronize()
+        best = 1e9
+        for _ in range(10):
+            e0, e1 = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            e0.record()
+            t._int_mm(a, bm)
+            e1.record()
+            t.cuda.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        return round(2 * 8192 ** 3 / (best * 1e-3) / 1e12, 1)
+    except Exception:  # noqa: BLE001
+        return None
+
+
+def int8_peak_tops():
+    bf16 = None
+    if MEASURED_PEAKS.exists():
+        bf16 = float(json.loads(MEASURED_PEAKS.read_text()).get("bf16_tflops", 0)) or None
+    return (2 * bf16 if bf16 else 2 * 1590.0), bool(bf16)
+
+
+def timed_steps(torch, wl, steps, warmup=3):
+    for _ in range(warmup):
+        wl.step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        wl.step()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def extra_metrics(torch, ctx, pk):
+    """The other headline configurations, measured in the same process after the decode stack's timed region (one
+    GPU): the single gate GEMM of configs[0], the decode sweep of configs[1], the prefill GEMMs of configs[2] with the
+    library int8 figure, the fast-AR frame of configs[4]. Each with CUDA events over graph replays / repeated launches
+    whose weights rotate through more than L2 holds."""
+    out = {}
+    hbm = pk["hbm_gbs"]
+    wl = DecodeSweep(torch, ctx, cases=config0_cases())
+    c = wl.per_case()[0]
+    out["config0_gate_M16_K2560_N9728_g256"] = {"us": c["us"], "gbs": c["gbs"], "frac_of_hbm": round(c["gbs"] / hbm, 3),
+                                                "tops": round(2 * 16 * 9728 * 2560 / c["us"] / 1e6, 1),
+                                                "includes": "quantiser launch + linear launch"}
+    wl.close()
+    del wl
+    wl = DecodeSweep(torch, ctx)
+    ms = timed_steps(torch, wl, 30)
+    cases = wl.per_case()
+    worst = min(cases, key=lambda c: c["gbs"])
+    best = max(cases, key=lambda c: c["gbs"])
+    agg = wl.bytes_per_step / (ms * 1e-3) / 1e9
+    out["configs1_decode_sweep"] = {
+        "aggregate_gbs": round(agg, 1), "aggregate_frac_of_hbm": round(agg / hbm, 3),
+        "worst": dict(worst, frac=round(worst["gbs"] / hbm, 3)), "best": dict(best, frac=round(best["gbs"] / hbm, 3)),
+        "frac_by_M": {str(M): round(float(np.mean([c["gbs"] for c in cases if c["M"] == M])) / hbm, 3) for M in (1, 4, 16)},
+        "cases": [[c["name"], c["M"], c["g"], c["us"], round(c["gbs"] / hbm, 3)] for c in cases]}
+    wl.close()
+    del wl
+    torch.cuda.empty_cache()
+    peak, measured = int8_peak_tops()
+    wl = PrefillSweep(torch, ctx)
+    ms = timed_steps(torch, wl, 2, warmup=1)
+    cases = wl.per_case(min_ms=10.0)
+    agg = wl.ops_per_step / (ms * 1e-3) / 1e12
+    worst = min(cases, key=lambda c: c["tops"])
+    best = max(cases, key=lambda c: c["tops"])
+    out["configs2_prefill"] = {
+        "aggregate_tops": round(agg, 1), "aggregate_frac_of_int8_peak": round(agg / peak, 3),
+        "best": dict(best, frac=round(best["tops"] / peak, 3)), "worst": dict(worst, frac=round(worst["tops"] / peak, 3)),
+        "int8_peak_tops": round(peak, 1), "int8_peak_source": "2 x measured bf16 burst" if measured else "2 x fallback bf16",
+        "library_int8_tops_8192cubed": int8_library_tops(torch),
+        "cases": [[c["name"], c["M"], c["g"], c["us"], c["tops"]] for c in cases]}
+    wl.close()
+    del wl
+    torch.cuda.empty_cache()
+    wl = FastARFrame(torch, ctx)
+    ms = timed_steps(torch, wl, 20)
+    gbs = wl.bytes_per_step / (ms * 1e-3) / 1e9
+    out["configs4_fast_ar_frame"] = {"ms_per_frame": round(ms, 4), "codebook_tokens_per_s": round(wl.batch * wl.codebooks / (ms * 1e-3), 1),
+                                     "frame_gbs": round(gbs, 1), "frac_of_hbm": round(gbs / hbm, 3),
+                                     "lm_head_int8_155776": wl.lm_head()}
+    wl.close()
+    del wl
+    torch.cuda.empty_cache()
+    return out
+
+
 def finish(dist, wl):
     """Leaves a multi-rank job without tearing NCCL down: a communicator destroyed while captured graphs
     that used it are alive has hung at exit, so graphs go first and the process exits hard."""
@@ -709,20 +813,25 @@ def finish(dist, wl):
     os._exit(0)
 
 
+REFERENCE_SAMPLE = ("the reference's own CUDA kernels (rebuilt for sm_100, stock entry points) on the GPU, eager "
+                    "launches: the reference has no CPU implementation of this path")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--workload", choices=["decode_stack", "decode_sweep", "prefill", "fast_ar"], default="decode_stack")
+    ap.add_argument("--workload", choices=["decode_stack", "decode_sweep", "prefill", "fast_ar", "config0"],
+                    default="decode_stack")
     ap.add_argument("--tp-mode", choices=["fused", "nccl"], default="fused",
                     help="N > 1: all-reduce inside the norm kernel over peer memory (fused) or NCCL (baseline)")
     ap.add_argument("--layers", type=int, default=36, help="decode_stack: number of layers (36 = the named config)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only", default=None, metavar="NAME:M:G",
                     help="restrict the sweep to one case, e.g. gate_up:16:256 (for profiling)")
-    ap.add_argument("--no-detail", action="store_true", help="skip the per-case timings")
+    ap.add_argument("--no-detail", action="store_true", help="skip the per-case timings and the extra configurations")
     ap.add_argument("--split-k", type=int, default=0, help="force the GEMV's K-slice count (tuning aid)")
     ap.add_argument("--no-pack", action="store_true", help="leave weights row-major (skip the loader-side pack)")
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a graph")
@@ -730,7 +839,7 @@ def main():
                     help="with --step-form one-launch: add the device-side per-phase medians of one step to the line")
     ap.add_argument("--step-form", choices=["one-launch", "chain"], default="chain",
                     help="decode_stack on one GPU: the whole step as one persistent kernel (w8a8_decode_stack_step) "
-                         "or as nine launches per layer")
+                         "or as a chain of launches per layer")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
 
@@ -765,7 +874,7 @@ def main():
 
     pkg = ge.package()
     reference = args.impl == "reference"
-    solo_reference = False
+    ctx = None
     if reference:
         from oracle import fishref
 
@@ -774,10 +883,15 @@ def main():
                 print(json.dumps({"impl": "reference", "unavailable":
                                   "oracle/_ref/libfishref.so was not built (no reference checkout at build time)"}))
             return
+        # nothing of the product is loaded on this arm: weights, cache and inputs are made with torch alone
         if args.workload == "decode_stack":
-            ctx = pkg.Context(local_rank, 1 << 24)  # builds the weights and the cache; no kernel of ours is timed
-            wl = DecodeStack(torch, ctx, 1, 0, None, layers=args.layers, reference=True)
-            solo_reference = True
+            wl = DecodeStack(torch, None, 1, 0, None, layers=args.layers, reference=True)
+        elif args.workload == "prefill":
+            wl = PrefillSweep(torch, None, reference=True)
+        elif args.workload == "fast_ar":
+            wl = FastARFrame(torch, None, reference=True)
+        elif args.workload == "config0":
+            wl = DecodeSweep(torch, None, reference=True, cases=config0_cases())
         else:
             wl = DecodeSweep(torch, None, reference=True)
     else:
@@ -788,6 +902,8 @@ def main():
             wl = PrefillSweep(torch, ctx)
         elif args.workload == "fast_ar":
             wl = FastARFrame(torch, ctx)
+        elif args.workload == "config0":
+            wl = DecodeSweep(torch, ctx, pack=not args.no_pack, cases=config0_cases())
         else:
             wl = DecodeSweep(torch, ctx, pack=not args.no_pack)
 
@@ -799,15 +915,19 @@ def main():
     wl.split_k = args.split_k
 
     def barrier():
-        if dist is not None and not solo_reference:
+        if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
+    # The clock record covers everything that runs under load from the first warm-up step on: warm-up, the timed
+    # region, the end-to-end region, the dominant kernel timed alone; a short run keeps stepping until the sampler
+    # has seen about 1.5 s of load.
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    t_load0 = time.perf_counter()
     for _ in range(args.warmup):
         wl.step()
     barrier()
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
@@ -827,11 +947,14 @@ def main():
         barrier()
         e2e_ms = (time.perf_counter() - t0) * 1e3
     cases = [] if args.no_detail else wl.per_case()
+    lin = wl.time_linears() if (args.workload == "decode_stack" and not reference) else None
+    while time.perf_counter() - t_load0 < 1.5:
+        wl.step()
+        torch.cuda.synchronize()
     clocks = sampler.stop()
 
-    lin = wl.time_linears() if (args.workload == "decode_stack" and not reference) else None
     times = torch.tensor([dev_ms, e2e_ms or 0.0, lin[0] if lin else 0.0], dtype=torch.float64, device="cuda")
-    if dist is not None and not solo_reference:
+    if dist is not None:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     dev_ms, e2e_ms_max, lin_s = times.tolist()
     if rank != 0:
@@ -839,13 +962,22 @@ def main():
         return
 
     pk = peaks()
+    ms_per_step = dev_ms / args.steps
+    par = f"replicas x{world}" if world > 1 else "single GPU"
+    if reference:
+        par = "single GPU (the reference has no multi-GPU path; rank 0 alone ran)"
+
+    def reference_keys(line, unit):
+        line["impl"] = "reference"
+        line["n_gpus"] = declared_world
+        line["gpu_launches"] = None
+        line["cpu_baseline"] = {"value": line["value"], "unit": unit, "cores": 0, "kind": "reference",
+                                "sample": REFERENCE_SAMPLE}
+        line["e2e"] = {"value": line["value"], "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+
     if args.workload == "prefill":
-        ms_per_step = dev_ms / args.steps
         tops = wl.ops_per_step * world / (ms_per_step * 1e-3) / 1e12
-        bf16 = None
-        if MEASURED_PEAKS.exists():
-            bf16 = float(json.loads(MEASURED_PEAKS.read_text()).get("bf16_tflops", 0)) or None
-        peak = 2 * bf16 if bf16 else 2 * 1590.0
+        peak, measured = int8_peak_tops()
         line = {
             "metric": "w8a8_prefill_gemm_int8_tops", "value": round(tops, 1), "unit": "TOPS", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 3),
@@ -853,8 +985,8 @@ def main():
             "config": {"workload": "configs[2]: slow-AR projections qkv/o/gate_up/down x g{256,64} x M{2048,8192}, one "
                                    "W8A8 linear (row quantiser + tcgen05 GEMM) each per step", "cases_per_step": len(wl.cases),
                        "l2": "inputs larger than L2: 8 weight sets + 8 activation sets in rotation (> 600 MB)",
-                       "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
-                       "library_int8_tops_8192cubed": wl.library_int8_tops()},
+                       "parallelism": par,
+                       "library_int8_tops_8192cubed": int8_library_tops(torch)},
             "roofline": {"bound": "tensor", "achieved": round(tops / world, 1), "peak": round(peak, 1), "unit": "TOP/s",
                          "frac": round(tops / world / peak, 4),
                          "traffic": int(GEMM_TRAFFIC_RATIO * sum(
@@ -863,19 +995,23 @@ def main():
                          "traffic_source": "bytes per launch (mean over the cases) scaled by the DRAM/algorithmic ratio "
                                            "of one ncu capture (gate_up M=2048 g=256)",
                          "peak_source": "2 x measured bf16 burst (int8 dense runs at twice the bf16 rate; no "
-                                        "int8 figure is in MEASURED_PEAKS.json)" if bf16 else "2 x fallback bf16",
-                         "kernel": "gemm_i8_kernel"},
+                                        "int8 figure is in MEASURED_PEAKS.json)" if measured else "2 x fallback bf16",
+                         "kernel": "gemm_i8_kernel" if not reference else "reference kernels (per-group cuBLAS + accumulate)"},
             "clocks": clocks, "gpu_launches": wl.launches_per_step * args.steps,
             "cases": [dict(c, frac=round(c["tops"] / peak, 3)) for c in cases],
             "e2e": {"value": None, "unit": "TOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0,
                     "note": "prefill activations are produced on the device by the embedding / previous layer; "
                             "the end-to-end figure of this repository is the decode_stack workload's"},
         }
+        if reference:
+            line["roofline"]["traffic"] = None
+            reference_keys(line, "TOPS")
+        elif not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline_prefill()
         print(json.dumps(line), flush=True)
         finish(dist, wl)
         return
     if args.workload == "fast_ar":
-        ms_per_step = dev_ms / args.steps
         tok_s = wl.batch * wl.codebooks / (ms_per_step * 1e-3)
         gbs = wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9
         line = {
@@ -886,23 +1022,25 @@ def main():
                                    "hidden 2560, 32q/8kv x128, SwiGLU 9728, no qk-norm, W8A8 g64) + codebook head 2560->4096, "
                                    "batch 8; sampling and embedding lookup outside; one CUDA graph per frame",
                        "global_batch": wl.batch, "codebooks": wl.codebooks,
-                       "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+                       "parallelism": par,
                        "l2": "a frame streams 10 x 0.42 GB of weights: each codebook step's weights exceed L2",
-                       "lm_head_int8_155776": None if args.no_detail else wl.lm_head()},
+                       "lm_head_int8_155776": None if (args.no_detail or reference) else wl.lm_head()},
             "roofline": {"bound": "hbm", "achieved": round(gbs, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                          "frac": round(gbs / pk["hbm_gbs"], 4), "traffic": None, "peak_source": pk["source"],
-                         "kernel": "the whole frame (weights + scales + KV read, algorithmic bytes over frame time)",
-                         "algorithmic_bytes_per_launch": int(wl.bytes_per_step / wl.launches_per_step)},
+                         "kernel": "the whole frame (weights + scales + KV read, algorithmic bytes over frame time)"},
             "clocks": clocks, "gpu_launches": wl.launches_per_step * args.steps,
-            "e2e": {"value": round(wl.batch * wl.codebooks / (e2e_ms_max / args.steps * 1e-3), 1), "unit": "tokens/s",
-                    "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h},
         }
+        if reference:
+            reference_keys(line, "tokens/s")
+        else:
+            line["roofline"]["algorithmic_bytes_per_launch"] = int(wl.bytes_per_step / wl.launches_per_step)
+            line["e2e"] = {"value": round(wl.batch * wl.codebooks / (e2e_ms_max / args.steps * 1e-3), 1), "unit": "tokens/s",
+                           "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h}
         print(json.dumps(line), flush=True)
         finish(dist, wl)
         return
     if args.workload == "decode_stack":
-        ms_per_step = dev_ms / args.steps
-        n_gpus = 1 if solo_reference else world
+        n_gpus = world
         tok_s = wl.batch / (ms_per_step * 1e-3)
         line = {
             "metric": "slow_ar_decode_tokens_per_s", "value": round(tok_s, 1), "unit": "tokens/s", "n_gpus": world,
@@ -934,37 +1072,37 @@ def main():
                                 "kernel": "gemv_packed_kernel (the 4 linears of each layer, timed alone)",
                                 "algorithmic_bytes_per_launch": int(lin[1]), "us_per_launch": round(lin_s * 1e6, 2)}
         if reference:
-            line["impl"] = "reference"
-            line["n_gpus"] = declared_world
-            line["config"]["parallelism"] = "single GPU (the reference has no multi-GPU path; rank 0 alone ran)"
-            line["gpu_launches"] = None
-            line["cpu_baseline"] = {"value": line["value"], "unit": "tokens/s", "cores": 0, "kind": "reference",
-                                    "sample": "the reference's own CUDA kernels (rebuilt for sm_100) chained in the "
-                                              "order of DualAREngine::decode_step at batch 8, eager launches, on the "
-                                              "GPU: the reference has no CPU implementation of this path"}
-            line["e2e"] = {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+            reference_keys(line, "tokens/s")
+            line["config"]["parallelism"] = par
         else:
             line["e2e"] = {"value": round(wl.batch / (e2e_ms_max / args.steps * 1e-3), 1), "unit": "tokens/s",
                            "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h}
             if not args.no_cpu_baseline:
                 line["cpu_baseline"] = cpu_baseline_stack()
+            if world == 1 and not args.no_detail and args.layers == 36:
+                wl.close()
+                del wl
+                torch.cuda.empty_cache()
+                wl = None
+                line["extra"] = extra_metrics(torch, ctx, pk)
         print(json.dumps(line), flush=True)
         finish(dist, wl)
         return
-    ms_per_step = dev_ms / args.steps
+    # decode_sweep / config0
     total_bytes = wl.bytes_per_step * world
     value = total_bytes / (ms_per_step * 1e-3) / 1e9
     per_launch_bytes = wl.bytes_per_step / len(wl.cases)
     per_launch_s = ms_per_step * 1e-3 / len(wl.cases)
     achieved = per_launch_bytes / per_launch_s / 1e9
+    what = ("configs[0]: one W8A8 linear, the gate projection, M=16 K=2560 N=9728 g=256" if args.workload == "config0" else
+            "configs[1]: slow-AR projections qkv/o/gate_up/down x g{256,64} x M{1,4,16}, one W8A8 linear each per step")
     line = {
         "metric": "w8a8_decode_gemv_hbm_gbs", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8", "data": "synthetic",
-        "config": {"workload": "configs[1]: slow-AR projections qkv/o/gate_up/down x g{256,64} x M{1,4,16}, "
-                               "one W8A8 linear each per step", "cases_per_step": len(wl.cases),
+        "config": {"workload": what, "cases_per_step": len(wl.cases),
                    "l2": "inputs larger than L2: >= 320 MB of copies per weight set in rotation, M outermost",
-                   "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+                   "parallelism": par,
                    "tops": round(wl.ops_per_step * world / (ms_per_step * 1e-3) / 1e12, 2)},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4),
@@ -977,11 +1115,7 @@ def main():
         "cases": [dict(c, frac=round(c["gbs"] / pk["hbm_gbs"], 3)) for c in cases],
     }
     if reference:
-        line["impl"] = "reference"
-        line["cpu_baseline"] = {"value": line["value"], "unit": "GB/s", "cores": 0, "kind": "reference",
-                                "sample": "the reference's own CUDA kernels rebuilt for sm_100, stock entry point, "
-                                          "on the GPU (the reference has no CPU implementation of this path)"}
-        line["e2e"] = {"value": line["value"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+        reference_keys(line, "GB/s")
     else:
         e2e_value = total_bytes / (e2e_ms_max / args.steps * 1e-3) / 1e9
         line["e2e"] = {"value": round(e2e_value, 1), "unit": "GB/s", "h2d_bytes_per_step": wl.h2d,

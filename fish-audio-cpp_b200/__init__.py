@@ -17,6 +17,9 @@ from .capi import (  # noqa: F401
     KERNEL_GEMV_PACKED,
     KERNEL_GEMV_TMA,
     KERNEL_GENERIC,
+    TAIL_GROUPQUANT,
+    TAIL_NONE,
+    TAIL_ROWNORM,
     Context,
     W8A8Error,
     library_path,

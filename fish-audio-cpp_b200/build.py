@@ -40,11 +40,15 @@ def sources() -> list[Path]:
     return sorted(CSRC.glob("*.cu"))
 
 
-def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False) -> Path:
-    OBJ.mkdir(exist_ok=True)
-    LIB.parent.mkdir(exist_ok=True)
+def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False, defines=(), out_dir=None) -> Path:
+    """defines / out_dir: a diagnostic build with extra -D flags goes to a directory of its own
+    (out_dir/_build, out_dir/libw8a8.so) and leaves the product library alone."""
+    OBJ = globals()["OBJ"] if out_dir is None else Path(out_dir) / "_build"
+    LIB = globals()["LIB"] if out_dir is None else Path(out_dir) / "libw8a8.so"
+    OBJ.mkdir(parents=True, exist_ok=True)
+    LIB.parent.mkdir(parents=True, exist_ok=True)
     hdr = _newest_header()
-    defines = []
+    defines = [f"-D{d}" for d in defines]
     jobs = []
     for src in sources():
         obj = OBJ / (src.stem + ".o")

@@ -28,6 +28,15 @@ class LinearOpts(C.Structure):
     ]
 
 
+class Tail(C.Structure):
+    """w8a8_tail of include/w8a8.h."""
+    _fields_ = [("kind", C.c_int), ("x", C.c_void_p), ("norm_weight", C.c_void_p), ("eps", C.c_float),
+                ("group_size", C.c_int), ("Xq", C.c_void_p), ("Xs", C.c_void_p), ("normed_out", C.c_void_p)]
+
+
+TAIL_NONE, TAIL_ROWNORM, TAIL_GROUPQUANT = 0, 1, 2
+
+
 class DecodeStack(C.Structure):
     """w8a8_decode_stack of include/w8a8.h."""
     _fields_ = [("n_layers", C.c_int), ("batch", C.c_int), ("dim", C.c_int), ("n_q_heads", C.c_int),
@@ -42,7 +51,11 @@ DECODE_LAYER_POINTERS = 8  # w8a8_decode_layer: attn_norm, ffn_norm, q_norm, k_n
 
 
 def library_path() -> Path:
-    return Path(__file__).resolve().parent / "lib" / "libw8a8.so"
+    """lib/libw8a8.so beside this file; $W8A8_LIBRARY names another build of the same library (diagnostic builds)."""
+    import os
+
+    alt = os.environ.get("W8A8_LIBRARY")
+    return Path(alt) if alt else Path(__file__).resolve().parent / "lib" / "libw8a8.so"
 
 
 def load_library() -> C.CDLL:
@@ -72,6 +85,8 @@ def load_library() -> C.CDLL:
         "w8a8_linear": (I, [P, P, P, I, P, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_linear_q": (I, [P, P, P, I, P, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_rmsnorm_linear": (I, [P, P, P, I, P, P, P, P, F, P, I, I, I, C.POINTER(LinearOpts), P, P, P]),
+        "w8a8_linear_q_tail": (I, [P, P, P, I, P, P, P, I, I, I, C.POINTER(LinearOpts), C.POINTER(Tail), P]),
+        "w8a8_debug_tail_counters": (I, [P, P, I, P]),
         "w8a8_pack_gate_up": (I, [P, P, P, P, P, I, I, I, P, P, P]),
         "w8a8_decode_stack_workspace_bytes": (Z, [C.POINTER(DecodeStack)]),
         "w8a8_decode_stack_step": (I, [P, C.POINTER(DecodeStack), P]),
@@ -105,7 +120,7 @@ EXPORTS = [
     "w8a8_status_string", "w8a8_last_error", "w8a8_create", "w8a8_destroy", "w8a8_workspace_bytes",
     "w8a8_ctx_workspace_bytes", "w8a8_check_device_status", "w8a8_quantize", "w8a8_rms_norm",
     "w8a8_rmsnorm_quantize", "w8a8_silu", "w8a8_mul", "w8a8_residual_add", "w8a8_linear", "w8a8_linear_q",
-    "w8a8_rmsnorm_linear", "w8a8_decode_stack_workspace_bytes", "w8a8_decode_stack_step",
+    "w8a8_rmsnorm_linear", "w8a8_linear_q_tail", "w8a8_debug_tail_counters", "w8a8_decode_stack_workspace_bytes", "w8a8_decode_stack_step",
     "w8a8_decode_stack_timeline",
     "w8a8_pack_gate_up", "w8a8_qknorm_rope_kvwrite", "w8a8_paged_attention_decode", "w8a8_qkv_attention_decode", "w8a8_tp_create", "w8a8_tp_connect",
     "w8a8_tp_allreduce_rmsnorm_quantize", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
@@ -239,6 +254,22 @@ class Context:
         self._check(self.lib.w8a8_linear_q(self.handle, _ptr(W), _ptr(w_scale), group_size, _ptr(Xq), _ptr(Xs),
                                            _ptr(Y), M, N, K, self._opts(0, epilogue, residual, dump, kernel, split_k),
                                            _stream(stream)), "w8a8_linear_q")
+
+    def linear_q_tail(self, W, w_scale, group_size, Xq, Xs, Y, M, N, K, tail_kind, tail_group_size, tail_Xq=None,
+                      tail_Xs=None, x=None, norm_weight=None, eps=0.0, normed_out=None, epilogue=EPI_NONE, kernel=KERNEL_AUTO,
+                      stream=None):
+        """w8a8_linear_q followed, in the same launch where the decode kernel takes the shape, by the tail on its
+        output: TAIL_ROWNORM (x += Y, RMSNorm, quantiser) or TAIL_GROUPQUANT (the quantiser alone)."""
+        tail = Tail(tail_kind, _ptr(x), _ptr(norm_weight), eps, tail_group_size, _ptr(tail_Xq), _ptr(tail_Xs),
+                    _ptr(normed_out))
+        self._check(self.lib.w8a8_linear_q_tail(self.handle, _ptr(W), _ptr(w_scale), group_size, _ptr(Xq), _ptr(Xs),
+                                                _ptr(Y), M, N, K, self._opts(0, epilogue, None, None, kernel, 0),
+                                                C.byref(tail), _stream(stream)), "w8a8_linear_q_tail")
+
+    def debug_tail_counters(self, count=256, stream=None):
+        buf = (C.c_int * count)()
+        self._check(self.lib.w8a8_debug_tail_counters(self.handle, buf, count, _stream(stream)), "w8a8_debug_tail_counters")
+        return list(buf)
 
     def rmsnorm_linear(self, W, w_scale, group_size, x, norm_weight, eps, Y, M, N, K, residual=None, x_out=None,
                        epilogue=EPI_NONE, epi_residual=None, kernel=KERNEL_AUTO, act_mode=ACT_PER_TOKEN_GROUP,

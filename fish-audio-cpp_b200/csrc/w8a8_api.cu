@@ -23,6 +23,7 @@ struct w8a8_ctx {
     };
     std::unordered_map<const void*, PackedEntry> packed;
     std::mutex packed_mu;
+    int* tail_counters = nullptr;     // arrival counters of the decode kernel's tails, zero between launches
     w8a8::TpState* tp = nullptr;  // tensor-parallel exchange, when w8a8_tp_create was called
 };
 
@@ -126,6 +127,7 @@ static void fill_scratch(w8a8_ctx* ctx, LinearArgs& a) {
     a.splitk_partial_bytes = kSplitkPartialBytes;
     a.splitk_counters = ctx->splitk_counters;
     a.splitk_counter_count = kSplitkCounters;
+    a.tail_counters = ctx->tail_counters;
     if (a.M <= 32 && !ctx->packed.empty()) {
         std::lock_guard<std::mutex> lock(ctx->packed_mu);
         auto it = ctx->packed.find(a.W);
@@ -193,12 +195,15 @@ int w8a8_create(w8a8_ctx** out, int device, size_t workspace_bytes) {
     if (e == cudaSuccess) e = cudaMalloc(&c->splitk_partials, kSplitkPartialBytes);
     if (e == cudaSuccess) e = cudaMalloc(&c->splitk_counters, kSplitkCounters * sizeof(int));
     if (e == cudaSuccess) e = cudaMemset(c->splitk_counters, 0, kSplitkCounters * sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&c->tail_counters, kTailCounterInts * sizeof(int));
+    if (e == cudaSuccess) e = cudaMemset(c->tail_counters, 0, kTailCounterInts * sizeof(int));
     cudaSetDevice(prev);
     if (e != cudaSuccess) {
         cudaFree(c->workspace);
         cudaFree(c->device_status);
         cudaFree(c->splitk_partials);
         cudaFree(c->splitk_counters);
+        cudaFree(c->tail_counters);
         delete c;
         return fail(W8A8_ERR_CUDA, "context allocation: %s", cudaGetErrorString(e));
     }
@@ -212,6 +217,7 @@ int w8a8_destroy(w8a8_ctx* ctx) {
     cudaFree(ctx->device_status);
     cudaFree(ctx->splitk_partials);
     cudaFree(ctx->splitk_counters);
+    cudaFree(ctx->tail_counters);
     tp_destroy(ctx->tp);
     delete ctx;
     return W8A8_OK;
@@ -234,6 +240,8 @@ int w8a8_check_device_status(w8a8_ctx* ctx, void* stream) {
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "status read: %s", cudaGetErrorString(e));
     if (host != 0) {
         cudaMemsetAsync(ctx->device_status, 0, sizeof(int), s);
+        // a kernel that gave up may have left arrival counters half-counted
+        cudaMemsetAsync(ctx->tail_counters, 0, kTailCounterInts * sizeof(int), s);
         return fail(W8A8_ERR_TIMEOUT, "a kernel gave up a bounded wait (code %d)", host);
     }
     return W8A8_OK;
@@ -302,6 +310,68 @@ int w8a8_linear_q(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_s
     a.Xq = static_cast<const int8_t*>(Xq);
     a.Xs = static_cast<const float*>(Xs);
     return dispatch_q(ctx, a, opts ? opts->kernel : W8A8_KERNEL_AUTO, static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_linear_q_tail(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size, const void* Xq,
+                       const void* Xs, void* Y, int M, int N, int K, const w8a8_linear_opts* opts,
+                       const w8a8_tail* tail, void* stream) {
+    if (!tail || tail->kind == W8A8_TAIL_NONE)
+        return w8a8_linear_q(ctx, W, w_scale, group_size, Xq, Xs, Y, M, N, K, opts, stream);
+    int rc = check_linear_common(ctx, W, w_scale, Y, M, N, K, opts);
+    if (rc) return rc;
+    if (M > 0 && (!Xq || !Xs)) return fail(W8A8_ERR_INVALID_ARG, "null Xq or Xs");
+    const int epi = opts ? opts->epilogue : W8A8_EPI_NONE;
+    const int cols = epi == W8A8_EPI_SWIGLU ? N / 2 : N;
+    if (tail->kind == W8A8_TAIL_ROWNORM) {
+        if (epi != W8A8_EPI_NONE) return fail(W8A8_ERR_INVALID_ARG, "W8A8_TAIL_ROWNORM goes with W8A8_EPI_NONE");
+        if (!tail->x || !tail->norm_weight || tail->x == Y)
+            return fail(W8A8_ERR_INVALID_ARG, "W8A8_TAIL_ROWNORM needs x (other than Y) and a norm weight");
+        if (tail->Xq && !tail->Xs) return fail(W8A8_ERR_INVALID_ARG, "tail: Xq without Xs");
+    } else if (tail->kind == W8A8_TAIL_GROUPQUANT) {
+        if (epi == W8A8_EPI_RESIDUAL || !tail->Xq || !tail->Xs)
+            return fail(W8A8_ERR_INVALID_ARG, "W8A8_TAIL_GROUPQUANT needs Xq and Xs and no residual epilogue");
+    } else {
+        return fail(W8A8_ERR_INVALID_ARG, "unknown tail kind %d", tail->kind);
+    }
+    if (M == 0) return W8A8_OK;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int kernel = opts ? opts->kernel : W8A8_KERNEL_AUTO;
+    LinearArgs a = make_args(W, w_scale, group_size, Y, M, N, K, opts);
+    a.Xq = static_cast<const int8_t*>(Xq);
+    a.Xs = static_cast<const float*>(Xs);
+    if (kernel == W8A8_KERNEL_AUTO || kernel == W8A8_KERNEL_GEMV_PACKED) {
+        LinearArgs f = a;
+        fill_scratch(ctx, f);
+        f.tail_kind = tail->kind == W8A8_TAIL_ROWNORM ? kTailRowNorm : kTailGroupQuant;
+        f.tail_counters = ctx->tail_counters;
+        f.tail_x = static_cast<__half*>(tail->x);
+        f.tail_norm_weight = static_cast<const __half*>(tail->norm_weight);
+        f.tail_eps = tail->eps;
+        f.tail_g = norm_group(cols, tail->group_size);
+        f.tail_Xq = static_cast<int8_t*>(tail->Xq);
+        f.tail_Xs = static_cast<float*>(tail->Xs);
+        f.tail_normed_out = static_cast<__half*>(tail->normed_out);
+        if (f.packed && gemv_packed_supports(f)) return launch_linear_gemv_packed(f, ctx->device_status, s);
+    }
+    // the separate kernels, back to back
+    rc = dispatch_q(ctx, a, kernel, s);
+    if (rc) return rc;
+    if (tail->kind == W8A8_TAIL_ROWNORM) {
+        if (tail->Xq)
+            return launch_rowquant(static_cast<const __half*>(tail->x), static_cast<__half*>(tail->x),
+                                   static_cast<const __half*>(Y), static_cast<const __half*>(tail->norm_weight), tail->eps,
+                                   nullptr, nullptr, M, N, tail->group_size, W8A8_ACT_PER_TOKEN_GROUP,
+                                   static_cast<__half*>(tail->normed_out), static_cast<int8_t*>(tail->Xq),
+                                   static_cast<float*>(tail->Xs), s);
+        rc = launch_residual_add(static_cast<__half*>(tail->x), static_cast<const __half*>(Y), static_cast<long>(M) * N, s);
+        if (rc || !tail->normed_out) return rc;
+        return launch_rowquant(static_cast<const __half*>(tail->x), nullptr, nullptr,
+                               static_cast<const __half*>(tail->norm_weight), tail->eps, nullptr, nullptr, M, N, N,
+                               W8A8_ACT_PER_TOKEN_GROUP, static_cast<__half*>(tail->normed_out), nullptr, nullptr, s);
+    }
+    return launch_rowquant(static_cast<const __half*>(Y), nullptr, nullptr, nullptr, 0.0f, nullptr, nullptr, M, cols,
+                           tail->group_size, W8A8_ACT_PER_TOKEN_GROUP, nullptr, static_cast<int8_t*>(tail->Xq),
+                           static_cast<float*>(tail->Xs), s);
 }
 
 int w8a8_rmsnorm_linear(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size, const void* x,
@@ -469,6 +539,15 @@ int w8a8_tp_allreduce_rmsnorm_quantize(w8a8_ctx* ctx, void* x, const void* parti
                                         static_cast<const __half*>(act_scale), M, K, group_size, act_mode,
                                         static_cast<__half*>(normed_out), static_cast<int8_t*>(Xq),
                                         static_cast<float*>(Xs), ctx->device_status, static_cast<cudaStream_t>(stream));
+}
+
+int w8a8_debug_tail_counters(w8a8_ctx* ctx, int* out, int count, void* stream) {
+    if (!ctx || !out || count < 0 || count > kTailCounterInts) return fail(W8A8_ERR_INVALID_ARG, "debug_tail_counters: bad arguments");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    cudaError_t e = cudaMemcpyAsync(out, ctx->tail_counters, count * sizeof(int), cudaMemcpyDeviceToHost, s);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(s);
+    if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "counter read: %s", cudaGetErrorString(e));
+    return W8A8_OK;
 }
 
 size_t w8a8_packed_weight_bytes(int N, int K, int group_size) { return packed_weight_bytes(N, K, group_size); }

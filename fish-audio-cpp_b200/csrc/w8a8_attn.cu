@@ -15,6 +15,7 @@
 
 #include "sm100_ptx.cuh"
 #include "w8a8_internal.h"
+#include "w8a8_trace.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -228,8 +229,10 @@ __device__ __forceinline__ uint32_t reg_of(const uint4& v, int i) {
 // before that work, so its latency hides under theirs.
 template <bool ROPE>
 __global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_kernel(const AttnParams p) {
+    W8A8_TRACE_SCOPE();
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
+    W8A8_TRACE_WAITED();
     __shared__ __align__(16) __half q_s[ROPE ? kQPerKv : 1][kHeadDim];
     __shared__ float red_m[kAttnWarps][kQPerKv], red_l[kAttnWarps][kQPerKv];
     __shared__ float red_acc[kAttnWarps][kQPerKv][kHeadDim];
@@ -477,6 +480,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_ker
             }
         }
     }
+    W8A8_TRACE_END(4u);
 }
 
 }  // namespace
@@ -572,3 +576,5 @@ int launch_attention(const AttnParams& base, int B, int splits, cudaStream_t str
 }  // namespace
 
 }  // namespace w8a8
+
+W8A8_TRACE_READER(attn)

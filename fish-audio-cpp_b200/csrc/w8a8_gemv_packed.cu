@@ -32,17 +32,19 @@
 
 #include "sm100_ptx.cuh"
 #include "w8a8_internal.h"
+#include "w8a8_trace.cuh"
 
 namespace w8a8 {
 namespace {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kStages = 3;
 constexpr int kBlockW = 16 * 256;        // weight bytes of a block
 constexpr int kStagePitch = kBlockW + 128;  // room for the largest scale tail, keeps stages 128-byte aligned
-constexpr int kRingBytes = kStages * kStagePitch;
 constexpr int kLocalTiles = 128;  // row tiles per CTA whose arrival counters live in shared memory
+// How the activations arrive (template parameter PRO):
+enum { kProCodes = 0,   // int8 codes + fp32 scales made by an earlier launch (Xq, Xs)
+       kProNorm = 1 };  // fp16 rows: every CTA does [x + residual] -> RMSNorm -> quantiser itself, in its prologue
 
 struct GemvPackedParams {
     LinearArgs a;
@@ -86,19 +88,249 @@ __device__ __forceinline__ float ld_cg(const float* p) {
     return v;
 }
 
+#ifdef W8A8_TAIL_TIMELINE
+// Diagnostic build only: the last CTA to arrive leaves nanosecond stamps of its launch in tail_counters[128..].
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+#define W8A8_STAMP(slot) do { if (threadIdx.x == 0) tl[slot] = now_ns(); } while (0)
+#define W8A8_STAMP_FLUSH(counters, is_last) do { if (threadIdx.x == 0 && (is_last)) { \
+    unsigned long long* o = reinterpret_cast<unsigned long long*>((counters) + 128); \
+    for (int i_ = 0; i_ < 8; ++i_) o[i_] = tl[i_]; o[8] = blockIdx.x; } } while (0)
+#else
+#define W8A8_STAMP(slot) do {} while (0)
+#define W8A8_STAMP_FLUSH(counters, is_last) do {} while (0)
+#endif
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Tail, kind kTailRowNorm. Called by all 256 threads of a CTA after its last tile is stored. The CTA takes a ticket;
+// the last min(M, grid) CTAs to arrive each wait (bounded) until every CTA of the grid has arrived, i.e. until the
+// whole output Y = [M, N] is in L2, and then run, for the token rows they own, exactly what the kernel launched next
+// would have run (rowquant_compact_kernel): x = half(x + Y) (ffn_activations.cu:41-45), RMSNorm with the
+// reference's 1024-thread summation order (rms_norm.cu:23-49), the group quantiser (int8_gemm.cu:147-211).
+// N % 256 == 0, 512 < N <= 4096. The last row CTA to finish puts the counters back to zero.
+__device__ __forceinline__ void tail_row_norm(const LinearArgs& a, unsigned char* scratch, int* status,
+                                              unsigned long long (&tl)[8]) {
+    __shared__ int s_ticket, s_fail;
+    __shared__ float s_red[32];
+    __half* row_s = reinterpret_cast<__half*>(scratch);  // [N]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int total = gridDim.x, n_row = a.M < total ? a.M : total, first = total - n_row;
+    if (tid == 0) {
+        __threadfence();  // this CTA's tiles (stored by all its warps, ordered by the barrier before the call)
+        s_ticket = atomicAdd(&a.tail_counters[0], 1);
+        s_fail = 0;
+    }
+    __syncthreads();
+    const int ticket = s_ticket;
+    W8A8_STAMP(3);
+    if (ticket < first) return;
+    if (tid == 0) {
+        unsigned spins = 0;
+        while (ld_acquire_gpu(&a.tail_counters[0]) < total) {
+            if (++spins > (1u << 22)) { atomicExch(status, 610); s_fail = 1; break; }
+            if (spins > 32) __nanosleep(32);
+        }
+    }
+    __syncthreads();
+    W8A8_STAMP(4);
+    const int K = a.N, T = 1024, VW = T / kThreads, pieces = K / 8;
+    const int G = K / a.tail_g;
+    if (!s_fail) {
+        for (int row = ticket - first; row < a.M; row += n_row) {
+            const size_t base = static_cast<size_t>(row) * K;
+            uint4 xv[2], dv[2], wv[2];
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {  // every load first (at most two pieces per thread)
+                const int c8 = tid + i * kThreads;
+                const int cc = c8 < pieces ? c8 : 0;
+                wv[i] = __ldg(reinterpret_cast<const uint4*>(a.tail_norm_weight) + cc);
+                xv[i] = __ldcg(reinterpret_cast<const uint4*>(a.tail_x + base) + cc);
+                dv[i] = __ldcg(reinterpret_cast<const uint4*>(a.Y + base) + cc);  // written by other SMs: past L1
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int c8 = tid + i * kThreads;
+                if (c8 < pieces) {
+                    __half* hx = reinterpret_cast<__half*>(&xv[i]);
+                    const __half* hd = reinterpret_cast<const __half*>(&dv[i]);
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) hx[e] = __float2half(__half2float(hx[e]) + __half2float(hd[e]));
+                    *reinterpret_cast<uint4*>(a.tail_x + base + c8 * 8) = xv[i];
+                    reinterpret_cast<uint4*>(row_s)[c8] = xv[i];
+                }
+            }
+            __syncthreads();
+            W8A8_STAMP(5);
+#pragma unroll 1
+            for (int k = 0; k < VW; ++k) {  // real warp w plays the reference's warps w*VW .. w*VW + VW - 1
+                float local_sum = 0.0f;
+#pragma unroll 1
+                for (int e = (warp * VW + k) * 32 + lane; e < K; e += T) {
+                    float val = __half2float(row_s[e]);
+                    local_sum += val * val;
+                }
+                for (int offset = 16; offset > 0; offset /= 2) local_sum += __shfl_down_sync(0xffffffffu, local_sum, offset);
+                if (lane == 0) s_red[warp * VW + k] = local_sum;
+            }
+            __syncthreads();
+            float total_sum = 0.0f;
+            if (warp == 0) {
+                total_sum = s_red[lane];
+                for (int offset = 16; offset > 0; offset /= 2) total_sum += __shfl_down_sync(0xffffffffu, total_sum, offset);
+            }
+            __syncthreads();
+            if (tid == 0) s_red[0] = rsqrtf(total_sum / K + a.tail_eps);
+            __syncthreads();
+            const float rms = s_red[0];
+            const int lanes = a.tail_g / 8;  // threads per quantisation group: 8, 16 or 32
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int c8 = tid + i * kThreads;
+                const bool live = c8 < pieces;  // whole warps are live or not (pieces is a multiple of 32)
+                __half* hx = reinterpret_cast<__half*>(&xv[i]);
+                const __half* hw = reinterpret_cast<const __half*>(&wv[i]);
+                float v[8], amax = 0.0f;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    float val = __half2float(hx[e]) * rms;
+                    hx[e] = __float2half(val * __half2float(hw[e]));
+                    v[e] = __half2float(hx[e]);
+                    amax = fmaxf(amax, fabsf(v[e]));
+                }
+                if (live && a.tail_normed_out) *reinterpret_cast<uint4*>(a.tail_normed_out + base + c8 * 8) = xv[i];
+                if (!a.tail_Xq) continue;
+                for (int o = lanes / 2; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                if (!live) continue;
+                float scale = amax / 127.0f;
+                if (scale < 1e-8f) scale = 1e-8f;
+                if ((lane & (lanes - 1)) == 0) a.tail_Xs[static_cast<size_t>(row) * G + (c8 * 8) / a.tail_g] = scale;
+                const float inv_scale = 1.0f / scale;
+                uint32_t lo = 0, hi = 0;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    int q = __float2int_rn(v[e] * inv_scale);
+                    q = max(-127, min(127, q));
+                    if (e < 4) lo |= (static_cast<uint32_t>(q) & 0xffu) << (8 * e);
+                    else hi |= (static_cast<uint32_t>(q) & 0xffu) << (8 * (e - 4));
+                }
+                *reinterpret_cast<uint2*>(a.tail_Xq + base + c8 * 8) = make_uint2(lo, hi);
+            }
+            __syncthreads();  // row_s and s_red are reused by the next row of this CTA
+        }
+    }
+    W8A8_STAMP(6);
+    W8A8_STAMP_FLUSH(a.tail_counters, ticket == total - 1);
+    if (tid == 0) {
+        const int done = atomicAdd(&a.tail_counters[1], 1);
+        if (done == n_row - 1) {  // every row CTA is past its wait: the counters can go back to zero
+            a.tail_counters[1] = 0;
+            __threadfence();
+            a.tail_counters[0] = 0;
+        }
+    }
+}
+
+// Tail, kind kTailGroupQuant: the quantiser (int8_gemm.cu:147-211) of the launch's own output for the linear that
+// follows. out = Y as stored: [M, N] (16 channels per row tile) or, with the SwiGLU epilogue, [M, N/2] (8 channels
+// per tile). A CTA adds the number of its tiles in each quantisation group to that group's counter; the CTA whose
+// add completes a group quantises it (one warp per token row, 8 channels per lane and step) and zeroes the counter.
+// Nothing waits. tail_g % 8 == 0 and a multiple of the channels per tile.
+__device__ __forceinline__ void tail_group_quant(const LinearArgs& a, int ct0, int ct1, unsigned char* scratch,
+                                                 unsigned long long (&tl)[8]) {
+    int* s_mine = reinterpret_cast<int*>(scratch);  // [groups this CTA touches]: 1 = this CTA completes the group
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int cpt = a.epilogue == W8A8_EPI_SWIGLU ? 8 : 16;      // output channels per row tile
+    const int Kout = a.epilogue == W8A8_EPI_SWIGLU ? a.N / 2 : a.N;
+    const int tpg = a.tail_g / cpt;                               // tiles per group
+    const int tiles = (a.N + 15) / 16, G = (Kout + a.tail_g - 1) / a.tail_g;
+    if (ct1 <= ct0) return;
+    const int j0 = ct0 / tpg, j1 = (ct1 - 1) / tpg;
+    if (tid <= j1 - j0) {
+        const int j = j0 + tid;
+        const int lo = max(ct0, j * tpg), hi = min(ct1, (j + 1) * tpg);
+        const int in_group = min(tiles, (j + 1) * tpg) - j * tpg;
+        __threadfence();  // this CTA's tiles (ordered before by the barrier before the call)
+        const int old = atomicAdd(&a.tail_counters[j], hi - lo);
+        const int mine = (old + (hi - lo) == in_group) ? 1 : 0;
+        if (mine) {
+            a.tail_counters[j] = 0;
+            __threadfence();  // acquire side: the other CTAs' tiles are visible to the loads below
+        }
+        s_mine[tid] = mine;
+    }
+    __syncthreads();
+    W8A8_STAMP(3);
+    bool any_mine = false;
+    for (int j = j0; j <= j1; ++j) any_mine |= s_mine[j - j0] != 0;
+    for (int j = j0; j <= j1; ++j) {
+        if (!s_mine[j - j0]) continue;
+        const int c0 = j * a.tail_g, width = min(a.tail_g, Kout - c0);
+        for (int row = warp; row < a.M; row += kWarps) {
+            const __half* src = a.Y + static_cast<size_t>(row) * Kout + c0;
+            float amax = 0.0f;
+            for (int e = lane * 8; e < width; e += 256) {
+                const uint4 u = __ldcg(reinterpret_cast<const uint4*>(src + e));
+                const __half* h = reinterpret_cast<const __half*>(&u);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(__half2float(h[i])));
+            }
+            for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+            float scale = amax / 127.0f;
+            if (scale < 1e-8f) scale = 1e-8f;
+            if (lane == 0) a.tail_Xs[static_cast<size_t>(row) * G + j] = scale;
+            const float inv_scale = 1.0f / scale;
+            for (int e = lane * 8; e < width; e += 256) {
+                const uint4 u = __ldcg(reinterpret_cast<const uint4*>(src + e));
+                const __half* h = reinterpret_cast<const __half*>(&u);
+                uint32_t lo = 0, hi = 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    int q = __float2int_rn(__half2float(h[i]) * inv_scale);
+                    q = max(-127, min(127, q));
+                    if (i < 4) lo |= (static_cast<uint32_t>(q) & 0xffu) << (8 * i);
+                    else hi |= (static_cast<uint32_t>(q) & 0xffu) << (8 * (i - 4));
+                }
+                *reinterpret_cast<uint2*>(a.tail_Xq + static_cast<size_t>(row) * Kout + c0 + e) = make_uint2(lo, hi);
+            }
+        }
+    }
+    __syncthreads();
+    W8A8_STAMP(6);
+    W8A8_STAMP_FLUSH(a.tail_counters, any_mine && j1 == G - 1);
+    (void)any_mine;
+}
+
 // GM: 64 or 128 = the group size itself; 256 = any group size that is a multiple of 256 (a unit is then
 // one whole group = g/256 blocks).
 //
-// FUSED: the activations arrive as fp16 rows and every CTA forms codes and scales itself, in shared memory,
-// before it consumes its first block (whose copy is already in flight): [x + residual] -> RMSNorm with the
-// summation order of the reference's 1024-thread launch (rms_norm.cu:23-49) -> group quantiser
-// (int8_gemm.cu:147-211). One warp per token row, so M <= 8. This replaces a separate launch of a kernel
-// that runs on M CTAs and leaves the rest of the GPU idle.
-template <int MT, int GM, bool FUSED>
-__global__ void __launch_bounds__(kThreads, 1)
+// PRO == kProNorm: the activations arrive as fp16 rows and every CTA forms codes and scales itself before it
+// consumes its first block (whose copy is already in flight): [x + residual] -> RMSNorm with the summation
+// order of the reference's 1024-thread launch (rms_norm.cu:23-49) -> group quantiser (int8_gemm.cu:147-211).
+// One warp per token row (M <= 8), the row in registers from the load to the codes; only the codes and scales
+// go to shared memory. This replaces a separate launch of a kernel that runs on M CTAs and leaves the rest of
+// the GPU idle, and the trip of its results through L2.
+// ST: stages of a warp's ring (3; 2 for kProNorm so that two CTAs fit an SM beside the code rows).
+// KI: kProNorm only, the 16-byte pieces of a row a lane holds (K <= 256 * KI): 10 for the stack's K = 2560, else 16.
+template <int MT, int GM, int PRO, int ST, int KI>
+__global__ void __launch_bounds__(kThreads, (PRO == kProNorm || MT == 1) ? 2 : 1)
 gemv_packed_kernel(const GemvPackedParams p) {
-    static_assert(!FUSED || MT == 1, "the fused prologue handles one row per warp");
+    constexpr bool FUSED = PRO == kProNorm;
+    constexpr int kStages = ST;
+    constexpr int kRingBytes = kStages * kStagePitch;
+    static_assert(PRO == kProCodes || MT == 1, "the fused prologue handles one row per warp");
     extern __shared__ unsigned char smem_raw[];
+    W8A8_TRACE_SCOPE();
+    unsigned long long tl[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    (void)tl;
+    W8A8_STAMP(0);
     __shared__ __align__(8) uint64_t bars[kWarps][kStages];
     const LinearArgs& a = p.a;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -150,147 +382,177 @@ gemv_packed_kernel(const GemvPackedParams p) {
         const int pre = T < kStages ? T : kStages;
         for (int i = 0; i < pre; ++i) issue();
     }
+    // kProNorm shared memory behind the rings: norm weight [K] fp16 | code rows [8][K + 64] | scales [8][G] fp32
+    unsigned char* const fbase = smem_raw + (ring - warp * kRingBytes - ptx::smem_u32(smem_raw)) + kWarps * kRingBytes;
     if constexpr (FUSED) {  // the norm weight is a parameter too: stage it before the wait
-        unsigned char* fbase = smem_raw + (ring - warp * kRingBytes - ptx::smem_u32(smem_raw)) + kWarps * kRingBytes;
-        __half* normw_s = reinterpret_cast<__half*>(fbase) + 8 * a.K;
+        __half* normw_s = reinterpret_cast<__half*>(fbase);
         for (int c8 = threadIdx.x; c8 < a.K / 8; c8 += kThreads)
             reinterpret_cast<uint4*>(normw_s)[c8] = __ldg(reinterpret_cast<const uint4*>(a.norm_weight) + c8);
+        __syncthreads();  // staged by all threads, read by each warp on its own after the wait
     }
     // Everything above touches only weights. Let the next launch begin its own prologue, then wait
     // for the kernel before this one: it produces the activations.
     ptx::pdl_launch_dependents();
     ptx::pdl_wait();
+    W8A8_TRACE_WAITED();
+    W8A8_STAMP(1);
 
     const int8_t* xq[MT];
     const float* xsp[MT][2];
-    uint32_t xq_s = 0;                    // FUSED: this lane's code row in shared memory
+    uint32_t xq_s = 0;                    // kProNorm: this lane's code row in shared memory
     const float* xsp_s[2] = {nullptr, nullptr};
     if constexpr (FUSED) {
         const int K = a.K, pitch = K + 64;  // the pitch puts rows gq and gq+1 in different bank halves
-        unsigned char* fbase = smem_raw + (ring - warp * kRingBytes - ptx::smem_u32(smem_raw)) + kWarps * kRingBytes;
-        __half* rows_s = reinterpret_cast<__half*>(fbase);                       // [8][K] fp16
-        __half* normw_s = rows_s + 8 * K;                                        // [K]
-        int8_t* codes_s = reinterpret_cast<int8_t*>(normw_s + K);                // [8][pitch]
-        float* scales_s = reinterpret_cast<float*>(codes_s + 8 * pitch);         // [8][G]
+        const __half* normw_s = reinterpret_cast<const __half*>(fbase);
+        int8_t* codes_s = reinterpret_cast<int8_t*>(fbase + static_cast<size_t>(K) * 2);   // [8][pitch]
+        float* scales_s = reinterpret_cast<float*>(codes_s + 8 * pitch);                    // [8][G]
         const int row = warp;
         const bool writer = blockIdx.x == 0;
-        __half* my_row = rows_s + row * K;
+        // Lane l owns the 16-byte pieces c8 = l + 32 i of its row, i.e. elements e = 8 l + j + 256 i (j < 8): these
+        // are ALL the elements of the reference's virtual threads vt = 8 l + j + 256 r (r = i mod 4 < 4), which sum
+        // e = vt, vt + 1024, vt + 2048, ... in that order (rms_norm.cu:23-27 with a 1024-thread block).
+        constexpr int kMaxI = KI;  // K <= 256 * KI
+        const int iters = K / 256;
+        uint4 v[kMaxI];
         if (row < a.M) {
-            // All loads of a batch are requested before anything is stored: a load placed after a store that
-            // might alias it would wait for it, and ten such round trips in a row cost more than the GEMV.
-            constexpr int kBatch = 8;
-            for (int c0 = 0; c0 < K / 8; c0 += 32 * kBatch) {
-                uint4 v[kBatch], r[kBatch];
+            // All loads are requested before anything is used or stored: a load placed after a store that might
+            // alias it would wait for it.
+            uint4 r[kMaxI];
 #pragma unroll
-                for (int u = 0; u < kBatch; ++u) {
-                    const int c8 = c0 + u * 32 + lane;
-                    const size_t off = static_cast<size_t>(row) * K + c8 * 8;
-                    v[u] = make_uint4(0u, 0u, 0u, 0u);
-                    r[u] = make_uint4(0u, 0u, 0u, 0u);
-                    if (c8 < K / 8) {
-                        v[u] = ld_cg16(a.X + off);
-                        if (a.norm_residual) r[u] = ld_cg16(a.norm_residual + off);
-                    }
+            for (int i = 0; i < kMaxI; ++i) {
+                v[i] = make_uint4(0u, 0u, 0u, 0u);
+                r[i] = make_uint4(0u, 0u, 0u, 0u);
+                if (i < iters) {
+                    const size_t off = static_cast<size_t>(row) * K + (lane + 32 * i) * 8;
+                    v[i] = ld_cg16(a.X + off);
+                    if (a.norm_residual) r[i] = ld_cg16(a.norm_residual + off);
                 }
+            }
+            if (a.norm_residual) {
 #pragma unroll
-                for (int u = 0; u < kBatch; ++u) {
-                    const int c8 = c0 + u * 32 + lane;
-                    if (c8 >= K / 8) continue;
-                    const size_t off = static_cast<size_t>(row) * K + c8 * 8;
-                    if (a.norm_residual) {
-                        __half* hv = reinterpret_cast<__half*>(&v[u]);
-                        const __half* hr = reinterpret_cast<const __half*>(&r[u]);
+                for (int i = 0; i < kMaxI; ++i) {
+                    if (i < iters) {
+                        __half* hv = reinterpret_cast<__half*>(&v[i]);
+                        const __half* hr = reinterpret_cast<const __half*>(&r[i]);
 #pragma unroll
                         for (int e = 0; e < 8; ++e) hv[e] = __float2half(__half2float(hv[e]) + __half2float(hr[e]));
-                        if (writer && a.norm_x_out) *reinterpret_cast<uint4*>(a.norm_x_out + off) = v[u];
-                    }
-                    reinterpret_cast<uint4*>(my_row)[c8] = v[u];
-                }
-            }
-        }
-        __syncthreads();  // the norm weight is staged (and each warp's own row)
-        if (row < a.M) {
-            // Lane l stands for lane l of each of the 32 warps of the reference's 1024-thread block:
-            // virtual thread vw*32 + l sums x[e]^2 over e = vw*32 + l + i*1024, i ascending.
-            float ls[32];
-#pragma unroll
-            for (int vw = 0; vw < 32; ++vw) ls[vw] = 0.0f;
-            for (int i = 0; i * 1024 < K; ++i) {
-#pragma unroll
-                for (int vw = 0; vw < 32; ++vw) {
-                    const int e = i * 1024 + vw * 32 + lane;
-                    if (e < K) {
-                        float val = __half2float(my_row[e]);
-                        ls[vw] += val * val;
+                        if (writer && a.norm_x_out)
+                            *reinterpret_cast<uint4*>(a.norm_x_out + static_cast<size_t>(row) * K + (lane + 32 * i) * 8) = v[i];
                     }
                 }
             }
-            float total_sum = 0.0f;  // lane vw: the partial of virtual warp vw (the reference's s_red[vw])
+            W8A8_STAMP(2);
+            // per virtual thread (r, j): local_sum over i = r, r + 4, r + 8, r + 12 ascending
+            float ls[4][8];
 #pragma unroll
-            for (int vw = 0; vw < 32; ++vw) {
-                float local_sum = ls[vw];
-                for (int offset = 16; offset > 0; offset /= 2)
-                    local_sum += __shfl_down_sync(0xffffffffu, local_sum, offset);
-                local_sum = __shfl_sync(0xffffffffu, local_sum, 0);
-                if (lane == vw) total_sum = local_sum;
+            for (int r4 = 0; r4 < 4; ++r4)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ls[r4][j] = 0.0f;
+#pragma unroll
+            for (int i = 0; i < kMaxI; ++i) {
+                if (i < iters) {
+                    const __half* hv = reinterpret_cast<const __half*>(&v[i]);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        float val = __half2float(hv[j]);
+                        ls[i & 3][j] += val * val;
+                    }
+                }
+            }
+            // The reference's shuffle-down tree over a virtual warp. Virtual warp (r, l / 4) is made of the
+            // virtual lanes vl = 8 (l % 4) + j: offsets 16 and 8 cross real lanes (l + 2, l + 1), offsets 4, 2, 1
+            // stay inside the lane's eight j. Only virtual lane 0 (l % 4 == 0, j == 0) is used afterwards, and its
+            // sum takes exactly the reference's operands in the reference's order.
+            float wsum[4];
+#pragma unroll
+            for (int r4 = 0; r4 < 4; ++r4) {
+                float b8[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float local_sum = ls[r4][j];
+                    local_sum += __shfl_down_sync(0xffffffffu, local_sum, 2);   // virtual offset 16
+                    local_sum += __shfl_down_sync(0xffffffffu, local_sum, 1);   // virtual offset 8
+                    b8[j] = local_sum;
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) b8[j] += b8[j + 4];                  // virtual offset 4
+                b8[0] += b8[2];                                                  // virtual offset 2
+                b8[1] += b8[3];
+                wsum[r4] = b8[0] + b8[1];                                        // virtual offset 1
+            }
+            // second tree (rms_norm.cu:36-42): lane vw takes s_red[vw]; virtual warp vw = 8 r + q lives in lane 4 q
+            float total_sum = 0.0f;
+#pragma unroll
+            for (int r4 = 0; r4 < 4; ++r4) {
+                const float t = __shfl_sync(0xffffffffu, wsum[r4], 4 * (lane & 7));
+                if ((lane >> 3) == r4) total_sum = t;
             }
             for (int offset = 16; offset > 0; offset /= 2)
                 total_sum += __shfl_down_sync(0xffffffffu, total_sum, offset);
             total_sum = __shfl_sync(0xffffffffu, total_sum, 0);
             const float rms = rsqrtf(total_sum / K + a.norm_eps);
-            // normalise in place (rounded to fp16 like rms_norm's output) and find the group maxima;
-            // lane l owns elements (l + 32 i) * 8 .. + 8, so a 256-wide run is one i across the warp
+            W8A8_STAMP(3);
+            // normalise in registers (rounded to fp16 like rms_norm's output) and find the group maxima; a run
+            // of 256 channels is one i across the warp
             constexpr int kLanesPerGroup = GM == 64 ? 8 : GM == 128 ? 16 : 32;
-            float run_max = 0.0f;
-            const int iters = K / 256, per_group = GM == 256 ? a.g / 256 : 1;
-            for (int i = 0; i < iters; ++i) {
-                const int c8 = lane + 32 * i;
-                uint4 v = reinterpret_cast<const uint4*>(my_row)[c8];
-                const uint4 w = reinterpret_cast<const uint4*>(normw_s)[c8];
-                __half* hv = reinterpret_cast<__half*>(&v);
-                const __half* hw = reinterpret_cast<const __half*>(&w);
-                float m = 0.0f;
+            const int per_group = GM == 256 ? a.g / 256 : 1;
+            float gmax[kMaxI];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    float val = __half2float(hv[e]) * rms;
-                    hv[e] = __float2half(val * __half2float(hw[e]));
-                    m = fmaxf(m, fabsf(__half2float(hv[e])));
+            for (int i = 0; i < kMaxI; ++i) {
+                gmax[i] = 0.0f;
+                if (i < iters) {
+                    const uint4 w = reinterpret_cast<const uint4*>(normw_s)[lane + 32 * i];
+                    __half* hv = reinterpret_cast<__half*>(&v[i]);
+                    const __half* hw = reinterpret_cast<const __half*>(&w);
+                    float m = 0.0f;
+#pragma unroll
+                    for (int e = 0; e < 8; ++e) {
+                        float val = __half2float(hv[e]) * rms;
+                        hv[e] = __float2half(val * __half2float(hw[e]));
+                        m = fmaxf(m, fabsf(__half2float(hv[e])));
+                    }
+#pragma unroll
+                    for (int o = 1; o < kLanesPerGroup; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+                    gmax[i] = m;
                 }
-                reinterpret_cast<uint4*>(my_row)[c8] = v;
+            }
+            W8A8_STAMP(4);
+            if (GM == 256 && per_group > 1) {  // a group spans per_group consecutive runs: give each run its group's maximum
 #pragma unroll
-                for (int o = 1; o < kLanesPerGroup; o <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-                run_max = fmaxf(run_max, m);
-                if (GM != 256 || (i + 1) % per_group == 0) {
-                    float scale = run_max / 127.0f;
+                for (int i = 1; i < kMaxI; ++i)   // forward: the last run of a group collects the maximum
+                    if (i < iters && i % per_group != 0) gmax[i] = fmaxf(gmax[i], gmax[i - 1]);
+#pragma unroll
+                for (int i = kMaxI - 2; i >= 0; --i)  // backward: hand it to the runs before it
+                    if (i + 1 < iters && (i + 1) % per_group != 0) gmax[i] = gmax[i + 1];
+            }
+#pragma unroll
+            for (int i = 0; i < kMaxI; ++i) {
+                if (i < iters) {
+                    float scale = gmax[i] / 127.0f;
                     if (scale < 1e-8f) scale = 1e-8f;
                     const int j = GM == 256 ? i / per_group : i * (256 / GM) + lane / kLanesPerGroup;
-                    if (lane % kLanesPerGroup == 0) {
+                    if (lane % kLanesPerGroup == 0 && (GM != 256 || i % per_group == 0)) {
                         scales_s[row * a.G + j] = scale;
                         if (writer && a.scales_out) a.scales_out[static_cast<size_t>(row) * a.G + j] = scale;
                     }
-                    run_max = 0.0f;
-                }
-            }
-            __syncwarp();
-            for (int i = 0; i < iters; ++i) {
-                const int c8 = lane + 32 * i;
-                const uint4 v = reinterpret_cast<const uint4*>(my_row)[c8];
-                const __half* hv = reinterpret_cast<const __half*>(&v);
-                const int j = GM == 256 ? i / per_group : i * (256 / GM) + lane / kLanesPerGroup;
-                const float inv_scale = 1.0f / scales_s[row * a.G + j];
-                __align__(8) int8_t q8[8];
+                    const float inv_scale = 1.0f / scale;
+                    const __half* hv = reinterpret_cast<const __half*>(&v[i]);
+                    __align__(8) int8_t q8[8];
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    int q = __float2int_rn(__half2float(hv[e]) * inv_scale);
-                    q8[e] = static_cast<int8_t>(max(-127, min(127, q)));
+                    for (int e = 0; e < 8; ++e) {
+                        int q = __float2int_rn(__half2float(hv[e]) * inv_scale);
+                        q8[e] = static_cast<int8_t>(max(-127, min(127, q)));
+                    }
+                    const int c8 = lane + 32 * i;
+                    *reinterpret_cast<uint2*>(codes_s + row * pitch + c8 * 8) = *reinterpret_cast<const uint2*>(q8);
+                    if (writer && a.codes_out)
+                        *reinterpret_cast<uint2*>(a.codes_out + static_cast<size_t>(row) * K + c8 * 8) =
+                            *reinterpret_cast<const uint2*>(q8);
                 }
-                *reinterpret_cast<uint2*>(codes_s + row * pitch + c8 * 8) = *reinterpret_cast<const uint2*>(q8);
-                if (writer && a.codes_out)
-                    *reinterpret_cast<uint2*>(a.codes_out + static_cast<size_t>(row) * K + c8 * 8) =
-                        *reinterpret_cast<const uint2*>(q8);
             }
         }
         __syncthreads();  // all rows' codes and scales are in place
+        W8A8_STAMP(5);
         xq_s = ptx::smem_u32(codes_s) + min(gq, a.M - 1) * pitch + c * 16;
         xsp_s[0] = scales_s + min(2 * c, a.M - 1) * a.G;
         xsp_s[1] = scales_s + min(2 * c + 1, a.M - 1) * a.G;
@@ -495,6 +757,9 @@ gemv_packed_kernel(const GemvPackedParams p) {
         // (No proxy fence: the shared-memory reads above have returned their data — the MMAs consumed it —
         // before the copy that overwrites the slot is even issued.)
         if (lane == 0 && pt < T) issue();
+#ifdef W8A8_TAIL_TIMELINE
+        if (t == 0) W8A8_STAMP(6);
+#endif
         if (++si == p.bpu) {
             si = 0;
             if (GM == 256) promote(rt, ub, sa[0], sb[0], xsc[0]);
@@ -521,10 +786,31 @@ gemv_packed_kernel(const GemvPackedParams p) {
         for (int s = 0; s < kStages; ++s)
             if (pt > s) ptx::mbar_wait_bounded(&bar[s], ((pt - 1 - s) / kStages) & 1, 1u << 16);
     }
+#ifdef W8A8_TAIL_TIMELINE
+    if (a.tail_kind == kTailNone && a.tail_counters) {
+        W8A8_STAMP(7);
+        W8A8_STAMP_FLUSH(a.tail_counters, blockIdx.x == gridDim.x - 1);
+    }
+#endif
+    if constexpr (PRO == kProCodes && MT == 1) {
+        if (a.tail_kind != kTailNone) {
+            // every copy this CTA asked for has been consumed: the rings are free to serve as the tail's scratch
+            W8A8_STAMP(7);  // this thread's own warp is done
+            __syncthreads();
+            W8A8_STAMP(2);
+            unsigned char* scratch = smem_raw + (ring - warp * kRingBytes - ptx::smem_u32(smem_raw));
+            if (a.tail_kind == kTailRowNorm) tail_row_norm(a, scratch, p.status, tl);
+            else tail_group_quant(a, static_cast<int>(ct0), static_cast<int>(ct1), scratch, tl);
+        }
+    }
+#ifdef W8A8_TRACE
+    __syncthreads();  // diagnostic build: the record's end is the CTA's end, not warp 0's
+    W8A8_TRACE_END(10u + PRO + 4u * a.tail_kind, static_cast<unsigned>(a.N));
+#endif
 }
 
 struct Plan {
-    int MT, GM, upt, bpu, block_bytes, tiles, ctas;
+    int MT, GM, upt, bpu, block_bytes, tiles, ctas, pro, stages;
     long long U;
 };
 
@@ -556,9 +842,8 @@ bool packable(int N, int K, int g) {
     return N > 0 && K > 0 && K % 256 == 0 && K % g == 0 && (g == 64 || g == 128 || g % 256 == 0);
 }
 
-size_t fused_smem_bytes(int K, int G) {  // fp16 rows + norm weight + padded code rows + scales
-    return static_cast<size_t>(8) * K * 2 + static_cast<size_t>(K) * 2 + static_cast<size_t>(8) * (K + 64) +
-           static_cast<size_t>(8) * G * 4;
+size_t fused_smem_bytes(int K, int G) {  // norm weight + padded code rows + scales
+    return static_cast<size_t>(K) * 2 + static_cast<size_t>(8) * (K + 64) + static_cast<size_t>(8) * G * 4;
 }
 
 bool make_plan(const LinearArgs& a, Plan& pl) {
@@ -579,6 +864,29 @@ bool make_plan(const LinearArgs& a, Plan& pl) {
         if (reinterpret_cast<uintptr_t>(a.Xq) & 15u) return false;
     }
     if (a.epilogue == W8A8_EPI_SWIGLU && a.N % 16 != 0) return false;
+    if (a.tail_kind != kTailNone) {
+        if (fused || a.M > 8 || !a.tail_counters) return false;
+        const int tg = a.tail_g;
+        if (a.tail_kind == kTailRowNorm) {
+            // a CTA per row, two 16-byte pieces per thread; the norm emulates the reference's 1024-thread block
+            if (a.epilogue != W8A8_EPI_NONE || a.N % 256 != 0 || a.N <= 512 || a.N > 4096) return false;
+            if (!a.tail_x || !a.tail_norm_weight) return false;
+            if (a.tail_Xq && (!a.tail_Xs || !(tg == 64 || tg == 128 || tg == 256))) return false;
+            if ((reinterpret_cast<uintptr_t>(a.tail_x) | reinterpret_cast<uintptr_t>(a.tail_norm_weight) |
+                 reinterpret_cast<uintptr_t>(a.Y) | reinterpret_cast<uintptr_t>(a.tail_normed_out) |
+                 reinterpret_cast<uintptr_t>(a.tail_Xq)) & 15u)
+                return false;
+        } else {
+            const int kout = a.epilogue == W8A8_EPI_SWIGLU ? a.N / 2 : a.N;
+            const int cpt = a.epilogue == W8A8_EPI_SWIGLU ? 8 : 16;
+            if (a.epilogue == W8A8_EPI_RESIDUAL || !a.tail_Xq || !a.tail_Xs) return false;
+            if (tg <= 0 || tg % cpt != 0 || tg % 8 != 0 || kout % 8 != 0) return false;
+            if ((kout + tg - 1) / tg > kTailCounterInts) return false;
+            if ((reinterpret_cast<uintptr_t>(a.Y) | reinterpret_cast<uintptr_t>(a.tail_Xq)) & 15u) return false;
+        }
+    }
+    pl.pro = fused ? kProNorm : kProCodes;
+    pl.stages = fused ? 2 : 3;
     pl.MT = a.M <= 8 ? 1 : (a.M <= 16 ? 2 : 4);
     pl.GM = a.g == 64 ? 64 : a.g == 128 ? 128 : 256;
     pl.bpu = a.g > 256 ? a.g / 256 : 1;
@@ -586,15 +894,14 @@ bool make_plan(const LinearArgs& a, Plan& pl) {
     pl.block_bytes = kBlockW + 32 * (a.g >= 256 ? 1 : 256 / a.g);
     pl.tiles = (a.N + 15) / 16;
     pl.U = static_cast<long long>(pl.tiles) * pl.upt;
-    // One CTA per SM (two were measured no faster), never more CTAs than row tiles. The warp runs are then those
-    // of the one-launch decode step, whose results are the same bit for bit.
-    pl.ctas = gemv_packed_ctas(pl.tiles, num_sms(), pl.MT == 1 && !fused);
+    // Up to two CTAs per SM at M <= 8 (their registers and shared memory fit twice), never more CTAs than row tiles.
+    pl.ctas = gemv_packed_ctas(pl.tiles, num_sms(), pl.MT == 1);
     if ((pl.U + 1) * static_cast<long long>(pl.ctas) * kWarps >= (1ll << 32)) return false;  // 32-bit range math
     if (pl.tiles / pl.ctas + 2 > kLocalTiles) return false;  // arrival counters of a CTA's tiles sit in shared memory
     return true;
 }
 
-template <int MT, int GM, bool FUSED>
+template <int MT, int GM, int PRO, int ST, int KI>
 int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_t stream) {
     GemvPackedParams p;
     p.a = a;
@@ -604,10 +911,11 @@ int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_
     p.bpu = pl.bpu;
     p.U = static_cast<unsigned>(pl.U);
     p.status = status;
-    auto kern = gemv_packed_kernel<MT, GM, FUSED>;
-    const size_t smem = static_cast<size_t>(kWarps) * kRingBytes + 128 + (FUSED ? fused_smem_bytes(a.K, a.G) : 0);
+    auto kern = gemv_packed_kernel<MT, GM, PRO, ST, KI>;
+    const size_t ring = static_cast<size_t>(kWarps) * ST * kStagePitch + 128;
+    const size_t smem = ring + (PRO == kProNorm ? fused_smem_bytes(a.K, a.G) : 0);
     {  // per device, so on every launch (a host-side table write)
-        const size_t most = static_cast<size_t>(kWarps) * kRingBytes + 128 + (FUSED ? fused_smem_bytes(4096, 64) : 0);
+        const size_t most = ring + (PRO == kProNorm ? fused_smem_bytes(256 * KI, 4 * KI) : 0);
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(most));
         if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
     }
@@ -626,21 +934,23 @@ int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_
     return W8A8_OK;
 }
 
-template <int MT>
-int launch_gm(const LinearArgs& a, const Plan& pl, int* status, cudaStream_t s) {
+template <int MT, int GM>
+int launch_pro(const LinearArgs& a, const Plan& pl, int* status, cudaStream_t s) {
     if constexpr (MT == 1) {
-        if (a.norm_weight) {
-            switch (pl.GM) {
-                case 64: return launch_variant<1, 64, true>(a, pl, status, s);
-                case 128: return launch_variant<1, 128, true>(a, pl, status, s);
-                default: return launch_variant<1, 256, true>(a, pl, status, s);
-            }
+        if (pl.pro == kProNorm) {
+            if (a.K <= 2560) return launch_variant<1, GM, kProNorm, 2, 10>(a, pl, status, s);
+            return launch_variant<1, GM, kProNorm, 2, 16>(a, pl, status, s);
         }
     }
+    return launch_variant<MT, GM, kProCodes, 3, 1>(a, pl, status, s);
+}
+
+template <int MT>
+int launch_gm(const LinearArgs& a, const Plan& pl, int* status, cudaStream_t s) {
     switch (pl.GM) {
-        case 64: return launch_variant<MT, 64, false>(a, pl, status, s);
-        case 128: return launch_variant<MT, 128, false>(a, pl, status, s);
-        default: return launch_variant<MT, 256, false>(a, pl, status, s);
+        case 64: return launch_pro<MT, 64>(a, pl, status, s);
+        case 128: return launch_pro<MT, 128>(a, pl, status, s);
+        default: return launch_pro<MT, 256>(a, pl, status, s);
     }
 }
 
@@ -716,3 +1026,5 @@ int launch_linear_gemv_packed(const LinearArgs& a, int* device_status, cudaStrea
 }
 
 }  // namespace w8a8
+
+W8A8_TRACE_READER(gemv_packed)

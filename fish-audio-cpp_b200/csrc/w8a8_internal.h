@@ -60,7 +60,24 @@ struct LinearArgs {
     __half* norm_x_out;           // [M, K] or null: CTA 0 stores the updated x (must not alias X)
     int8_t* codes_out;            // [M, K] / [M, G] or null: CTA 0 stores the codes and scales it formed
     float* scales_out;
+    // Tail (packed GEMV, M <= 8): work on the launch's own OUTPUT done by the CTAs that finish last, so that the
+    // small kernel that would follow (and the launch edge before it) disappears. Counted in `tail_counters`
+    // (context-owned, zero between launches).
+    //   kTailRowNorm:  x += Y (rounded like residual_add) -> RMSNorm -> quantiser, a CTA per token row
+    //   kTailGroupQuant: the quantiser alone over Y ([M, N] or, with the SwiGLU epilogue, [M, N/2]), by whichever
+    //                    CTA stores the last tile of a quantisation group
+    int tail_kind;
+    int* tail_counters;
+    __half* tail_x;               // kTailRowNorm: residual stream [M, N], updated in place
+    const __half* tail_norm_weight;
+    float tail_eps;
+    int tail_g;                   // group size of the codes the tail produces
+    int8_t* tail_Xq;              // [M, N'] (null with kTailRowNorm: no quantiser, e.g. the final norm)
+    float* tail_Xs;               // [M, N'/tail_g]
+    __half* tail_normed_out;      // kTailRowNorm: optional fp16 [M, N]
 };
+enum { kTailNone = 0, kTailRowNorm = 1, kTailGroupQuant = 2 };
+constexpr int kTailCounterInts = 256;  // two for kTailRowNorm, one per output group for kTailGroupQuant
 
 // w8a8_api.cu : picks the kernel for a linear whose codes and scales exist.
 int dispatch_linear_q(const LinearArgs& a, int kernel, int* device_status, cudaStream_t s);
@@ -87,7 +104,7 @@ int launch_linear_gemv_tma(const LinearArgs& a, int* device_status, cudaStream_t
 size_t packed_weight_bytes(int N, int K, int g);
 int launch_pack_weight(const int8_t* W, const __half* S, int N, int K, int g, void* out, cudaStream_t s);
 int gemv_packed_ctas(int tiles, int sms, bool two_per_sm);  // CTAs that share a linear's row tiles
-bool gemv_packed_supports(const LinearArgs& a);  // also answers for the fused-prologue form (a.norm_weight set)
+bool gemv_packed_supports(const LinearArgs& a);  // also answers for the prologue and tail forms (fields of a set)
 int launch_linear_gemv_packed(const LinearArgs& a, int* device_status, cudaStream_t s);
 // w8a8_attn.cu : decode-step neighbours (qk-norm + RoPE + KV write; paged attention).
 int launch_qknorm_rope_kvwrite(const __half* qkv, const __half* q_norm_w, const __half* k_norm_w, float eps,

@@ -11,6 +11,7 @@
 #include <cstdlib>
 
 #include "w8a8_internal.h"
+#include "w8a8_trace.cuh"
 
 namespace w8a8 {
 namespace {
@@ -324,6 +325,7 @@ __global__ void __launch_bounds__(256) rowquant_compact_kernel(const RowQuantPar
     const int K = p.K, VW = T / kThreads, G = p.G, row = blockIdx.x;
     const size_t base = static_cast<size_t>(row) * K;
     const int pieces = K / 8;
+    W8A8_TRACE_SCOPE();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     uint4 xv[2], dv[2], wv[2];
 #pragma unroll
@@ -332,6 +334,7 @@ __global__ void __launch_bounds__(256) rowquant_compact_kernel(const RowQuantPar
         wv[i] = __ldg(reinterpret_cast<const uint4*>(p.norm_weight) + (c8 < pieces ? c8 : 0));
     }
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    W8A8_TRACE_WAITED();
 #pragma unroll
     for (int i = 0; i < 2; ++i) {  // every load first (at most two pieces per thread)
         const int c8 = tid + i * kThreads;
@@ -408,6 +411,7 @@ __global__ void __launch_bounds__(256) rowquant_compact_kernel(const RowQuantPar
         }
         *reinterpret_cast<uint2*>(p.Xq + base + c8 * 8) = make_uint2(lo, hi);
     }
+    W8A8_TRACE_END(2u);
 }
 
 // The quantiser alone (int8_gemm.cu:147-211) for g in {64, 128, 256}: no shared memory, no block
@@ -421,8 +425,10 @@ __global__ void __launch_bounds__(128) groupquant_kernel(const __half* __restric
                                                          const __half* __restrict__ act_scale,
                                                          int8_t* __restrict__ Xq, float* __restrict__ Xs, int K,
                                                          int G) {
+    W8A8_TRACE_SCOPE();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    W8A8_TRACE_WAITED();
     const int m = blockIdx.y;
     const int e = (blockIdx.x * 128 + threadIdx.x) * 8;
     const bool live = e < K;
@@ -458,6 +464,7 @@ __global__ void __launch_bounds__(128) groupquant_kernel(const __half* __restric
         else hi |= (static_cast<uint32_t>(q) & 0xffu) << (8 * (i - 4));
     }
     *reinterpret_cast<uint2*>(Xq + static_cast<size_t>(m) * K + e) = make_uint2(lo, hi);
+    W8A8_TRACE_END(3u);
 }
 
 template <int LANES>
@@ -581,3 +588,5 @@ int launch_rowquant(const __half* x_in, __half* x_out, const __half* residual,
 }
 
 }  // namespace w8a8
+
+W8A8_TRACE_READER(quant)

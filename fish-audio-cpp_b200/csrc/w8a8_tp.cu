@@ -18,6 +18,7 @@
 #include <cstring>
 
 #include "w8a8_internal.h"
+#include "w8a8_trace.cuh"
 
 namespace w8a8 {
 
@@ -66,8 +67,10 @@ __global__ void __launch_bounds__(1024) tp_allreduce_rowquant_kernel(const TpRow
     const int tid = threadIdx.x, T = blockDim.x, K = p.K, g = p.g, G = p.G, m = blockIdx.x;
     const int lane = tid & (kWarp - 1), warp = tid / kWarp;
     const size_t base = static_cast<size_t>(m) * K;
+    W8A8_TRACE_SCOPE();
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
+    W8A8_TRACE_WAITED();
 
     unsigned char* mine = p.peers[p.rank];
     int* epochs = reinterpret_cast<int*>(mine + p.epochs_off);
@@ -165,7 +168,10 @@ __global__ void __launch_bounds__(1024) tp_allreduce_rowquant_kernel(const TpRow
             }
         }
     }
-    if (!p.Xq) return;
+    if (!p.Xq) {
+        W8A8_TRACE_END(5u);
+        return;
+    }
     float v[kElems];
 #pragma unroll
     for (int i = 0; i < kElems; ++i) {
@@ -205,6 +211,7 @@ __global__ void __launch_bounds__(1024) tp_allreduce_rowquant_kernel(const TpRow
             p.Xq[base + e] = static_cast<int8_t>(q);
         }
     }
+    W8A8_TRACE_END(5u);
 }
 
 }  // namespace
@@ -301,3 +308,5 @@ int launch_tp_allreduce_rowquant(TpState* t, __half* x, const __half* partial, c
 }
 
 }  // namespace w8a8
+
+W8A8_TRACE_READER(tp)

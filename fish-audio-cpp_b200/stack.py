@@ -161,6 +161,12 @@ class SlowARStack:
         # On one GPU the residual add + RMSNorm + quantiser before wqkv and w13 run inside the linear's own
         # launch (w8a8_rmsnorm_linear); with TP the exchange sits in that place instead.
         self.fuse_norm = fuse_norm and tp_size == 1 and pack and os.environ.get("W8A8_STACK_FUSE_NORM", "0") == "1"
+        # W8A8_STACK_TAILS=1 (one GPU, batch <= 8): the small kernels between the linears run as TAILS of the linear
+        # before them (w8a8_linear_q_tail): residual add + RMSNorm + quantiser after wo and w2, the quantiser after
+        # w1|w3; five launches per layer. Measured slower than the eight-launch form inside a replayed graph (a tail
+        # costs what the launch it replaces costs, and the next linear's prefetch overlaps less), so it is off by default.
+        self.tails = (tp_size == 1 and pack and batch <= 8 and cfg.group in (64, 128, 256) and not self.fuse_norm and
+                      os.environ.get("W8A8_STACK_TAILS", "0") == "1")
         # qk-norm + RoPE + KV write inside the attention launch (W8A8_STACK_FUSE_ROPE=0: as two launches)
         self.fuse_rope = os.environ.get("W8A8_STACK_FUSE_ROPE", "1") == "1"
         c = cfg
@@ -233,6 +239,8 @@ class SlowARStack:
         self.acts = torch.empty((B, self.inter_l // g), dtype=torch.float32, device=dev)
         self.out = torch.empty((B, c.dim), **h16)
         self.launches_per_step = c.n_layer * ((7 if self.fuse_norm else 9) - (1 if self.fuse_rope else 0)) + 2
+        if self.tails:
+            self.launches_per_step = c.n_layer * (5 if self.fuse_rope else 6) + 1
         # bytes the step must move at least once (per rank): weights + scales + the KV it reads
         wbytes = sum(lw[n].numel() + lw[s].numel() * 2 for lw in self.layers
                      for n, s in (("wqkv", "sqkv"), ("wo", "so"), ("w13", "s13"), ("w2", "s2")))
@@ -248,6 +256,8 @@ class SlowARStack:
         if x_in is not None:
             self.x.copy_(x_in, non_blocking=True)
         sm_scale = 1.0 / math.sqrt(D)
+        if self.tails:
+            return self._decode_step_tails(sm_scale)
         pending = False  # a projection output waiting to be added to the residual stream
         x, x_alt = self.x, self.x_alt
         for l, lw in enumerate(self.layers):
@@ -304,6 +314,44 @@ class SlowARStack:
         else:
             ctx.residual_add(x, self.delta, B * c.dim)
             ctx.rms_norm(x, self.final_norm, self.out, B, c.dim, c.eps)
+        self.positions.add_(1)
+        self.seq_lens.add_(1)
+        return self.out
+
+    def _attention(self, l, lw, sm_scale):
+        c, ctx, B, g, D = self.cfg, self.ctx, self.B, self.cfg.group, self.cfg.head_dim
+        if self.fuse_rope:
+            ctx.qkv_attention_decode(self.qkv, lw["q_norm"], lw["k_norm"], c.eps, self.freqs, self.positions,
+                                     self.k_cache, self.v_cache, self.block_table, self.seq_lens, None, B, self.nq_l,
+                                     D, self.max_blocks, sm_scale, l, c.n_layer, self.nkv_l, quant_group_size=g,
+                                     Xq=self.aq, Xs=self.as_, context_splits=self.attn_splits)
+        else:
+            ctx.qknorm_rope_kvwrite(self.qkv, lw["q_norm"], lw["k_norm"], c.eps, self.freqs, self.positions,
+                                    self.block_table, self.max_blocks, self.k_cache, self.v_cache, l, c.n_layer, B,
+                                    self.nq_l, self.nkv_l, D, self.q)
+            ctx.paged_attention_decode(self.q, self.k_cache, self.v_cache, self.block_table, self.seq_lens, None, B,
+                                       self.nq_l, D, self.max_blocks, sm_scale, l, c.n_layer, self.nkv_l,
+                                       quant_group_size=g, Xq=self.aq, Xs=self.as_, context_splits=self.attn_splits)
+
+    def _decode_step_tails(self, sm_scale):
+        """The step with the small kernels as tails of the linears (one GPU): per layer wqkv, attention,
+        wo [+ residual add, RMSNorm, quantiser], w1|w3 + SwiGLU [+ quantiser], w2 [+ residual add, the next layer's
+        RMSNorm, quantiser]; one row kernel in front of the first layer."""
+        c, ctx, B, g = self.cfg, self.ctx, self.B, self.cfg.group
+        ctx.rmsnorm_quantize(self.x, self.layers[0]["attn_norm"], c.eps, B, c.dim, g, self.xq, self.xs)
+        for l, lw in enumerate(self.layers):
+            ctx.linear_q(lw["wqkv"], lw["sqkv"], g, self.xq, self.xs, self.qkv, B, self.qkv_n, c.dim)
+            self._attention(l, lw, sm_scale)
+            ctx.linear_q_tail(lw["wo"], lw["so"], g, self.aq, self.as_, self.delta, B, c.dim, self.attn_k,
+                              capi.TAIL_ROWNORM, g, tail_Xq=self.xq, tail_Xs=self.xs, x=self.x,
+                              norm_weight=lw["ffn_norm"], eps=c.eps)
+            ctx.linear_q_tail(lw["w13"], lw["s13"], g, self.xq, self.xs, self.act, B, 2 * self.inter_l, c.dim,
+                              capi.TAIL_GROUPQUANT, g, tail_Xq=self.actq, tail_Xs=self.acts, epilogue=capi.EPI_SWIGLU)
+            last = l + 1 == len(self.layers)
+            ctx.linear_q_tail(lw["w2"], lw["s2"], g, self.actq, self.acts, self.delta, B, c.dim, self.inter_l,
+                              capi.TAIL_ROWNORM, g, tail_Xq=None if last else self.xq, tail_Xs=None if last else self.xs,
+                              x=self.x, norm_weight=self.final_norm if last else self.layers[l + 1]["attn_norm"],
+                              eps=c.eps, normed_out=self.out if last else None)
         self.positions.add_(1)
         self.seq_lens.add_(1)
         return self.out

@@ -164,6 +164,43 @@ W8A8_API int w8a8_linear_q(w8a8_ctx* ctx, const void* W, const void* w_scale, in
                   const void* Xq, const void* Xs, void* Y, int M, int N, int K,
                   const w8a8_linear_opts* opts, void* stream);
 
+/* What the launch of a decode-time linear may do to its own output once the output is complete, in place of the
+ * small kernel the engine would launch next (and of the launch edge before it):
+ *   W8A8_TAIL_ROWNORM     x += Y (ffn_activations.cu:41-45), then rms_norm of x (rms_norm.cu:10-58), then the
+ *                         quantiser of the next linear (int8_gemm.cu:147-211): DualAREngine::decode_step's
+ *                         residual_add + rms_norm after wo and after w2 (src/engine/dual_ar_engine.cc:631-637,
+ *                         :645-647, :580) plus the first stage of the quantized_gemm that follows.
+ *   W8A8_TAIL_GROUPQUANT  the quantiser alone over Y (with W8A8_EPI_SWIGLU: over the [M, N/2] product): the first
+ *                         stage of the w2 call after silu / mul (dual_ar_engine.cc:640-646).
+ * Results are those of the separate calls, bit for bit. */
+enum { W8A8_TAIL_NONE = 0, W8A8_TAIL_ROWNORM = 1, W8A8_TAIL_GROUPQUANT = 2 };
+typedef struct w8a8_tail {
+    int kind;                /* W8A8_TAIL_* */
+    void* x;                 /* ROWNORM: the residual stream, fp16 [M, N], updated in place */
+    const void* norm_weight; /* ROWNORM: fp16 [N] */
+    float eps;               /* ROWNORM */
+    int group_size;          /* quantisation group of the codes written (64, 128 or 256 for ROWNORM) */
+    void* Xq;                /* int8 codes of the result, [M, N] (GROUPQUANT after SwiGLU: [M, N/2]); ROWNORM: may be
+                                NULL (no quantiser, e.g. the final norm) */
+    void* Xs;                /* fp32 scales [M, columns / group_size] */
+    void* normed_out;        /* ROWNORM: optional fp16 [M, N], the normed rows */
+} w8a8_tail;
+
+/* w8a8_linear_q followed by `tail` on its output. For M <= 8 over a weight registered with
+ * w8a8_register_packed_weight this is ONE launch: the CTAs of the decode kernel that finish last do the tail (a
+ * CTA per token row for ROWNORM, after a bounded wait for the rest of the grid; whichever CTA completes a group
+ * for GROUPQUANT). Other shapes run the separate kernels back to back. Y is written as by w8a8_linear_q and must
+ * not alias tail->x. */
+W8A8_API int w8a8_linear_q_tail(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size,
+                       const void* Xq, const void* Xs, void* Y, int M, int N, int K,
+                       const w8a8_linear_opts* opts, const w8a8_tail* tail, void* stream);
+
+/* Diagnostic: copies the first `count` (<= 256) ints of the context's tail arrival counters to host memory
+ * (synchronises the stream). Between launches every counter a tail uses is zero; a diagnostic build of the
+ * library (-DW8A8_TAIL_TIMELINE) additionally leaves the device-timer stamps of the last CTA to arrive in
+ * ints 128.. (nine 64-bit words). */
+W8A8_API int w8a8_debug_tail_counters(w8a8_ctx* ctx, int* out, int count, void* stream);
+
 /* No counterpart in the reference. The same computation as w8a8_linear for callers that may not
  * allocate device memory and therefore cannot create a context (w8a8_create allocates): a plugin
  * inside a host process that owns the whole device-memory budget, or a real-time audio thread that

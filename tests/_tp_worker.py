@@ -112,17 +112,17 @@ def gpu_exchange_worker(rank, world, port, q):
         q.put((rank, False, repr(e)))
 
 
-def gpu_stack_worker(rank, world, port, q, tp_mode="fused", layers=2, steps=2):
+def gpu_stack_worker(rank, world, port, q, tp_mode="fused", layers=2):
     """One rank of the TP-vs-single-GPU test: a `layers`-deep stack of the benchmark's width (hidden 2560, 32 q / 8 kv
-    heads, SwiGLU 9728, g256, batch 8, context 1024) cut over `world` ranks runs `steps` decode steps; every rank
-    also runs the SAME stack uncut on its own GPU and reports how far the tensor-parallel result is from it, and the
-    ranks' outputs are gathered to check that all ranks hold the same bits."""
+    heads, SwiGLU 9728, g256, batch 8, context 1024) cut over `world` ranks runs one decode step; every rank also
+    runs the SAME stack uncut on its own GPU and reports how far the tensor-parallel result is from it, next to a
+    yardstick: how far the uncut stack's own result moves when every element of its input is moved by one fp16 ulp
+    up or down at random. The ranks' outputs are gathered to check that all ranks hold the same bits."""
     try:
         pkg = ge.package()
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
         torch.cuda.set_device(rank)
         dist.init_process_group("gloo", rank=rank, world_size=world)  # host-side plumbing only
-        cfg = S.SlowARConfig(n_layer=layers)
         B, context = 8, 1024
 
         def gather(handle):
@@ -130,34 +130,43 @@ def gpu_stack_worker(rank, world, port, q, tp_mode="fused", layers=2, steps=2):
             dist.all_gather_object(out, handle)
             return out
 
-        ctx_tp = pkg.Context(rank, 1 << 22)
-        st = S.SlowARStack(torch, ctx_tp, cfg, B, context, max_new=8, tp_rank=rank, tp_size=world, seed=31,
-                           tp_mode=tp_mode, gather_handles=gather)
-        ctx_1 = pkg.Context(rank, 1 << 22)
-        solo = S.SlowARStack(torch, ctx_1, cfg, B, context, max_new=8, seed=31)
-        rng = np.random.default_rng(23)
         report = []
-        for step in range(steps):
-            x_in = torch.from_numpy((rng.standard_normal((B, cfg.dim)) * 0.5).astype(np.float16)).cuda()
+        for n_layer in range(1, layers + 1):
+            cfg = S.SlowARConfig(n_layer=n_layer)
+            ctx_tp = pkg.Context(rank, 1 << 22)
+            st = S.SlowARStack(torch, ctx_tp, cfg, B, context, max_new=8, tp_rank=rank, tp_size=world, seed=31,
+                               tp_mode=tp_mode, gather_handles=gather)
+            ctx_1 = pkg.Context(rank, 1 << 22)
+            solo = S.SlowARStack(torch, ctx_1, cfg, B, context, max_new=8, seed=31)
+            rng = np.random.default_rng(23)
+            x_np = (rng.standard_normal((B, cfg.dim)) * 0.5).astype(np.float16)
+            x_in = torch.from_numpy(x_np).cuda()
             dist.barrier()
-            out = st.decode_step(x_in)
+            out = st.decode_step(x_in).clone()
             torch.cuda.synchronize()
             ctx_tp.check_device_status()
-            want = solo.decode_step(x_in)
+            want = solo.decode_step(x_in).clone()
             torch.cuda.synchronize()
-            g32, w32 = out.float(), want.float()
-            rel = ((g32 - w32).norm() / w32.norm()).item()
+            jit = (x_np.view(np.uint16).astype(np.int32) + rng.integers(-1, 2, x_np.shape)).astype(np.uint16).view(np.float16)
+            solo.reset_positions()
+            moved = solo.decode_step(torch.from_numpy(jit).cuda()).clone()
+            torch.cuda.synchronize()
+            w32 = want.float()
+            rel = ((out.float() - w32).norm() / w32.norm()).item()
+            noise = ((moved.float() - w32).norm() / w32.norm()).item()
             ulp = (out.view(torch.int16).int() - want.view(torch.int16).int()).abs()
             same = (ulp == 0).float().mean().item()
             bits = out.cpu().numpy().view(np.uint16).copy()
             all_bits = [None] * world
             dist.all_gather_object(all_bits, bits)
             identical = all(np.array_equal(all_bits[0], b) for b in all_bits)
-            report.append(dict(step=step, rel=rel, same_bits=same, max_ulp=int(ulp.max().item()), ranks_identical=identical))
+            report.append(dict(layers=n_layer, rel=rel, noise=noise, same_bits=same, ranks_identical=identical))
+            st.close(); solo.close()
+            ctx_tp.close(); ctx_1.close()
+            del st, solo
+            torch.cuda.empty_cache()
         dist.barrier()
         q.put((rank, True, report))
-        st.close(); solo.close()
-        ctx_tp.close(); ctx_1.close()
         dist.destroy_process_group()
     except Exception as e:  # noqa: BLE001
         import traceback

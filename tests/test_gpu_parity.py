@@ -423,6 +423,105 @@ def test_rmsnorm_linear_epilogues_and_argument_checks(ctx, oracle, pkg):
         ctx.register_packed_weight(dW, None)
 
 
+TAIL_ROW_SHAPES = [(8, 2560, 4096, 256, 256), (5, 2560, 9728, 256, 256), (8, 1024, 512, 64, 64), (3, 768, 1024, 128, 128),
+                   (1, 4096, 256, 256, 64), (8, 2560, 512, 256, 128),
+                   # not taken by the one-launch form (N too small, M too large): separate kernels, same results
+                   (8, 512, 512, 256, 256), (16, 1024, 512, 64, 64)]
+
+
+@pytest.mark.parametrize("M,N,K,g,g_out", TAIL_ROW_SHAPES)
+@pytest.mark.parametrize("quantise", [True, False])
+def test_linear_q_tail_rownorm_equals_separate_calls(ctx, oracle, pkg, M, N, K, g, g_out, quantise):
+    """w8a8_linear_q_tail with W8A8_TAIL_ROWNORM (the linear, then x += Y, RMSNorm and the next linear's quantiser done
+    by the last CTAs of the same launch) against w8a8_linear_q followed by w8a8_rmsnorm_quantize: Y, x, normed rows,
+    codes and scales bit for bit, three times in a row (the arrival counters must return to zero)."""
+    X, W, ws = synth.linear_case(300 + M + N, M, N, K, g)
+    rng = np.random.default_rng(N + K)
+    x0 = rng.standard_normal((M, N)).astype(np.float16)
+    w = rng.uniform(0.5, 1.5, N).astype(np.float16)
+    Xq, Xs = oracle.quantize(X, g)
+    dW, dS, dXq, dXs, dw = dev(W), dev(ws), dev(Xq), dev(Xs), dev(w)
+    if ctx.packed_weight_bytes(N, K, g):
+        dP = torch.empty((ctx.packed_weight_bytes(N, K, g),), dtype=torch.uint8, device="cuda")
+        ctx.pack_weight(dW, dS, N, K, g, dP)
+        ctx.register_packed_weight(dW, dP, N, K, g)
+    try:
+        G_out = N // g_out
+        cY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        cx = dev(x0)
+        cn = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        cq = torch.empty((M, N), dtype=torch.int8, device="cuda")
+        cs = torch.empty((M, G_out), dtype=torch.float32, device="cuda")
+        ctx.linear_q(dW, dS, g, dXq, dXs, cY, M, N, K)
+        ctx.rmsnorm_quantize(cx, dw, 1e-6, M, N, g_out, cq, cs, residual=cY, normed_out=cn)
+        torch.cuda.synchronize()
+        for rep in range(3):
+            ybuf, dY = guarded((M, N), torch.float16, 77.0)
+            xbuf, dx = guarded((M, N), torch.float16, 0.0)
+            dx.copy_(dev(x0))
+            nbuf, dn = guarded((M, N), torch.float16, 55.0)
+            qbuf, dq = guarded((M, N), torch.int8, 99)
+            sbuf, dsc = guarded((M, G_out), torch.float32, -3.0)
+            ctx.linear_q_tail(dW, dS, g, dXq, dXs, dY, M, N, K, pkg.TAIL_ROWNORM, g_out,
+                              tail_Xq=dq if quantise else None, tail_Xs=dsc if quantise else None, x=dx, norm_weight=dw,
+                              eps=1e-6, normed_out=dn)
+            torch.cuda.synchronize()
+            ctx.check_device_status()
+            assert torch.equal(dY.view(torch.int16), cY.view(torch.int16)), "Y of the plain linear"
+            assert torch.equal(dx.view(torch.int16), cx.view(torch.int16)), "x = half(x + Y)"
+            assert torch.equal(dn.view(torch.int16), cn.view(torch.int16)), "normed rows"
+            if quantise:
+                assert torch.equal(dq, cq) and torch.equal(dsc, cs), "codes and scales of the separate calls"
+            assert guards_intact(ybuf, 77.0) and guards_intact(nbuf, 55.0) and guards_intact(qbuf, 99) and \
+                guards_intact(sbuf, -3.0)
+    finally:
+        ctx.register_packed_weight(dW, None)
+
+
+TAIL_GROUP_SHAPES = [(8, 19456, 2560, 256, 256, True), (4, 2048, 512, 64, 64, True), (8, 2560, 512, 128, 128, False),
+                     (7, 1216 * 2, 768, 256, 256, True), (8, 320, 256, 256, 64, False), (2, 2432, 512, 256, 128, True),
+                     (16, 2048, 512, 64, 64, True)]  # the last: separate kernels (M > 8)
+
+
+@pytest.mark.parametrize("M,N,K,g,g_out,swiglu", TAIL_GROUP_SHAPES)
+def test_linear_q_tail_groupquant_equals_separate_calls(ctx, oracle, pkg, M, N, K, g, g_out, swiglu):
+    """w8a8_linear_q_tail with W8A8_TAIL_GROUPQUANT (the quantiser of the linear's own output, SwiGLU product
+    included, done by whichever CTA completes a quantisation group) against w8a8_linear_q followed by w8a8_quantize:
+    output, codes and scales bit for bit, three times in a row; ragged last groups included."""
+    X, W, ws = synth.linear_case(500 + M + N, M, N, K, g)
+    Xq, Xs = oracle.quantize(X, g)
+    dW, dS, dXq, dXs = dev(W), dev(ws), dev(Xq), dev(Xs)
+    epi = pkg.EPI_SWIGLU if swiglu else pkg.EPI_NONE
+    cols = N // 2 if swiglu else N
+    G_out = (cols + g_out - 1) // g_out
+    if ctx.packed_weight_bytes(N, K, g):
+        dP = torch.empty((ctx.packed_weight_bytes(N, K, g),), dtype=torch.uint8, device="cuda")
+        ctx.pack_weight(dW, dS, N, K, g, dP)
+        ctx.register_packed_weight(dW, dP, N, K, g)
+    try:
+        cY = torch.empty((M, cols), dtype=torch.float16, device="cuda")
+        cq = torch.empty((M, cols), dtype=torch.int8, device="cuda")
+        cs = torch.empty((M, G_out), dtype=torch.float32, device="cuda")
+        ctx.linear_q(dW, dS, g, dXq, dXs, cY, M, N, K, epilogue=epi)
+        ctx.quantize(cY, M, cols, g_out, cq, cs)
+        torch.cuda.synchronize()
+        wq, wsc = oracle.quantize(cY.cpu().numpy(), g_out)
+        assert np.array_equal(cq.cpu().numpy(), wq) and np.array_equal(cs.cpu().numpy(), wsc)
+        for rep in range(3):
+            ybuf, dY = guarded((M, cols), torch.float16, 77.0)
+            qbuf, dq = guarded((M, cols), torch.int8, 99)
+            sbuf, dsc = guarded((M, G_out), torch.float32, -3.0)
+            ctx.linear_q_tail(dW, dS, g, dXq, dXs, dY, M, N, K, pkg.TAIL_GROUPQUANT, g_out, tail_Xq=dq, tail_Xs=dsc,
+                              epilogue=epi)
+            torch.cuda.synchronize()
+            ctx.check_device_status()
+            assert torch.equal(dY.view(torch.int16), cY.view(torch.int16))
+            assert torch.equal(dq, cq) and torch.equal(dsc, cs), f"codes and scales of the separate calls (run {rep})"
+            assert guards_intact(ybuf, 77.0) and guards_intact(qbuf, 99) and guards_intact(sbuf, -3.0)
+    finally:
+        ctx.register_packed_weight(dW, None)
+
+
 def test_unpackable_shapes_report_zero_bytes(ctx):
     assert ctx.packed_weight_bytes(64, 640, 64) == 0      # K % 256 != 0
     assert ctx.packed_weight_bytes(64, 768, 192) == 0     # group size
