@@ -97,6 +97,7 @@ def load_library() -> C.CDLL:
         "w8a8_tp_create": (I, [P, I, I, I, I, P]),
         "w8a8_tp_connect": (I, [P, P]),
         "w8a8_tp_allreduce_rmsnorm_quantize": (I, [P, P, P, P, F, P, P, I, I, I, I, P, P, P, P]),
+        "w8a8_tp_linear_q": (I, [P, P, P, I, P, P, I, I, I, C.POINTER(LinearOpts), P]),
         "w8a8_packed_weight_bytes": (Z, [I, I, I]),
         "w8a8_pack_weight": (I, [P, P, P, I, I, I, P, P]),
         "w8a8_register_packed_weight": (I, [P, P, P, I, I, I]),
@@ -123,7 +124,7 @@ EXPORTS = [
     "w8a8_rmsnorm_linear", "w8a8_linear_q_tail", "w8a8_debug_tail_counters", "w8a8_decode_stack_workspace_bytes", "w8a8_decode_stack_step",
     "w8a8_decode_stack_timeline",
     "w8a8_pack_gate_up", "w8a8_qknorm_rope_kvwrite", "w8a8_paged_attention_decode", "w8a8_qkv_attention_decode", "w8a8_tp_create", "w8a8_tp_connect",
-    "w8a8_tp_allreduce_rmsnorm_quantize", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
+    "w8a8_tp_linear_q", "w8a8_tp_allreduce_rmsnorm_quantize", "w8a8_packed_weight_bytes", "w8a8_pack_weight", "w8a8_register_packed_weight",
     "w8a8_static_scratch_bytes", "w8a8_linear_static_scratch", "w8a8_static_scratch_check_status",
 ]
 
@@ -336,6 +337,12 @@ class Context:
 
     def tp_connect(self, all_handles: bytes):
         self._check(self.lib.w8a8_tp_connect(self.handle, all_handles), "w8a8_tp_connect")
+
+    def tp_linear_q(self, W, w_scale, group_size, Xq, Xs, M, N, K, kernel=KERNEL_AUTO, stream=None):
+        """The row-parallel linear whose fp32 partial goes straight to every rank's exchange buffer."""
+        self._check(self.lib.w8a8_tp_linear_q(self.handle, _ptr(W), _ptr(w_scale), group_size, _ptr(Xq), _ptr(Xs), M, N, K,
+                                              self._opts(0, EPI_NONE, None, None, kernel, 0), _stream(stream)),
+                    "w8a8_tp_linear_q")
 
     def tp_allreduce_rmsnorm_quantize(self, x, partial, weight, eps, M, K, group_size, Xq=None, Xs=None,
                                       smooth_inv=None, act_scale=None, act_mode=ACT_PER_TOKEN_GROUP, normed_out=None,

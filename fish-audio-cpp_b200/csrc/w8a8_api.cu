@@ -528,11 +528,30 @@ int w8a8_tp_connect(w8a8_ctx* ctx, const void* all_ipc_handles) {
     return tp_connect(ctx->tp, all_ipc_handles);
 }
 
+int w8a8_tp_linear_q(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size, const void* Xq, const void* Xs,
+                     int M, int N, int K, const w8a8_linear_opts* opts, void* stream) {
+    if (!ctx || !ctx->tp) return fail(W8A8_ERR_INVALID_ARG, "w8a8_tp_create first");
+    if (M < 0 || N <= 0 || K <= 0 || !W || !w_scale || (M > 0 && (!Xq || !Xs)))
+        return fail(W8A8_ERR_INVALID_ARG, "tp_linear_q: bad arguments");
+    if (opts && opts->epilogue != W8A8_EPI_NONE) return fail(W8A8_ERR_INVALID_ARG, "tp_linear_q takes no epilogue");
+    if (M == 0) return W8A8_OK;
+    LinearArgs a = make_args(W, w_scale, group_size, nullptr, M, N, K, opts);
+    a.Xq = static_cast<const int8_t*>(Xq);
+    a.Xs = static_cast<const float*>(Xs);
+    fill_scratch(ctx, a);
+    int rc = tp_push_args(ctx->tp, M, N, &a.tp);
+    if (rc) return rc;
+    if (!a.packed || !gemv_packed_supports(a))
+        return fail(W8A8_ERR_UNSUPPORTED, "tp_linear_q needs a weight registered with w8a8_register_packed_weight and M <= 32 "
+                                          "(use w8a8_linear_q and hand its output to w8a8_tp_allreduce_rmsnorm_quantize)");
+    return launch_linear_gemv_packed(a, ctx->device_status, static_cast<cudaStream_t>(stream));
+}
+
 int w8a8_tp_allreduce_rmsnorm_quantize(w8a8_ctx* ctx, void* x, const void* partial, const void* weight, float eps,
                                        const void* smooth_inv, const void* act_scale, int M, int K, int group_size,
                                        int act_mode, void* normed_out, void* Xq, void* Xs, void* stream) {
     if (!ctx || !ctx->tp) return fail(W8A8_ERR_INVALID_ARG, "w8a8_tp_create first");
-    if (M < 0 || K <= 0 || (M > 0 && (!x || !partial))) return fail(W8A8_ERR_INVALID_ARG, "tp row kernel: bad arguments");
+    if (M < 0 || K <= 0 || (M > 0 && !x)) return fail(W8A8_ERR_INVALID_ARG, "tp row kernel: bad arguments");
     if (Xq && !Xs) return fail(W8A8_ERR_INVALID_ARG, "tp row kernel: Xq without Xs");
     return launch_tp_allreduce_rowquant(ctx->tp, static_cast<__half*>(x), static_cast<const __half*>(partial),
                                         static_cast<const __half*>(weight), eps, static_cast<const __half*>(smooth_inv),

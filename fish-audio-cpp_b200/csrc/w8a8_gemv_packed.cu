@@ -396,6 +396,10 @@ gemv_packed_kernel(const GemvPackedParams p) {
     ptx::pdl_wait();
     W8A8_TRACE_WAITED();
     W8A8_STAMP(1);
+    // tensor-parallel send: this exchange's epoch = the last finished one + 1 (advanced by the receive kernel)
+    int tp_ep = 0;
+    if (a.tp.world > 0)
+        tp_ep = *reinterpret_cast<const volatile int*>(a.tp.peers[a.tp.rank] + a.tp.ctl_off) + 1;
 
     const int8_t* xq[MT];
     const float* xsp[MT][2];
@@ -596,6 +600,14 @@ gemv_packed_kernel(const GemvPackedParams p) {
                         const int row = rA + 8 * hrow;
                         if (row >= a.N) continue;
                         const size_t o = static_cast<size_t>(tok) * a.N + row;
+                        if (a.tp.world > 0) {
+                            // the fp32 partial as a self-validating word {value, epoch} into slot [rank] of every rank
+                            const size_t word = (static_cast<size_t>((tp_ep & 1) * a.tp.world + a.tp.rank) * a.tp.max_tokens + tok) *
+                                                    a.N + row;
+                            const uint2 w = make_uint2(__float_as_uint(v[nt][2 * hrow + e]), static_cast<unsigned>(tp_ep));
+                            for (int r = 0; r < a.tp.world; ++r) reinterpret_cast<uint2*>(a.tp.peers[r])[word] = w;
+                        }
+                        if (!a.Y) continue;
                         __half y = __float2half(v[nt][2 * hrow + e]);
                         if (a.epilogue == W8A8_EPI_RESIDUAL)
                             y = __float2half(__half2float(y) + __half2float(a.residual[o]));
@@ -864,6 +876,8 @@ bool make_plan(const LinearArgs& a, Plan& pl) {
         if (reinterpret_cast<uintptr_t>(a.Xq) & 15u) return false;
     }
     if (a.epilogue == W8A8_EPI_SWIGLU && a.N % 16 != 0) return false;
+    if (a.tp.world > 0 && (a.epilogue != W8A8_EPI_NONE || a.M > a.tp.max_tokens || a.tail_kind != kTailNone)) return false;
+    if (!a.Y && a.tp.world == 0) return false;
     if (a.tail_kind != kTailNone) {
         if (fused || a.M > 8 || !a.tail_counters) return false;
         const int tg = a.tail_g;

@@ -32,6 +32,13 @@ inline int num_groups(int K, int group_size) {
     return (K + g - 1) / g;
 }
 
+// Where a row-parallel linear sends its fp32 partial output (w8a8_tp.cu): slot [rank] of every rank's exchange buffer.
+struct TpPush {
+    int world, rank, max_tokens;  // world == 0: no send
+    size_t ctl_off;               // control words behind the slots: [0] the epoch of the last finished exchange
+    unsigned char* peers[8];      // every rank's exchange buffer as mapped here (peers[rank] is the local one)
+};
+
 struct LinearArgs {
     const int8_t* W;
     const __half* w_scale;  // [N, G]
@@ -75,6 +82,7 @@ struct LinearArgs {
     int8_t* tail_Xq;              // [M, N'] (null with kTailRowNorm: no quantiser, e.g. the final norm)
     float* tail_Xs;               // [M, N'/tail_g]
     __half* tail_normed_out;      // kTailRowNorm: optional fp16 [M, N]
+    TpPush tp;                    // packed GEMV, W8A8_EPI_NONE: finished tiles also go to every rank's exchange buffer
 };
 enum { kTailNone = 0, kTailRowNorm = 1, kTailGroupQuant = 2 };
 constexpr int kTailCounterInts = 256;  // two for kTailRowNorm, one per output group for kTailGroupQuant
@@ -131,6 +139,7 @@ struct TpState;
 int tp_create(TpState** out, int rank, int world, int max_tokens, int dim, void* ipc_handle_out64);
 int tp_connect(TpState* t, const void* all_handles);
 int tp_destroy(TpState* t);
+int tp_push_args(const TpState* t, int M, int N, TpPush* out);
 int launch_tp_allreduce_rowquant(TpState* t, __half* x, const __half* partial, const __half* norm_weight, float eps,
                                  const __half* smooth_inv, const __half* act_scale, int M, int K, int g, int act_mode,
                                  __half* normed_out, int8_t* Xq, float* Xs, int* status, cudaStream_t stream);

@@ -267,7 +267,7 @@ class SlowARStack:
                 if pending:
                     x, x_alt = x_alt, x
             elif pending and self.tp_fused:
-                ctx.tp_allreduce_rmsnorm_quantize(self.x, self.delta, lw["attn_norm"], c.eps, B, c.dim, g,
+                ctx.tp_allreduce_rmsnorm_quantize(self.x, None, lw["attn_norm"], c.eps, B, c.dim, g,
                                                   Xq=self.xq, Xs=self.xs)
             else:
                 ctx.rmsnorm_quantize(self.x, lw["attn_norm"], c.eps, B, c.dim, g, self.xq, self.xs,
@@ -287,7 +287,10 @@ class SlowARStack:
                                            self.nq_l, D, self.max_blocks, sm_scale, l, c.n_layer, self.nkv_l,
                                            quant_group_size=g, Xq=self.aq, Xs=self.as_,
                                            context_splits=self.attn_splits)
-            ctx.linear_q(lw["wo"], lw["so"], g, self.aq, self.as_, self.delta, B, c.dim, self.attn_k)
+            if self.tp_fused:  # the partial goes from the kernel's epilogue into every rank's exchange buffer
+                ctx.tp_linear_q(lw["wo"], lw["so"], g, self.aq, self.as_, B, c.dim, self.attn_k)
+            else:
+                ctx.linear_q(lw["wo"], lw["so"], g, self.aq, self.as_, self.delta, B, c.dim, self.attn_k)
             if self.all_reduce is not None:
                 self.all_reduce(self.delta)
             if self.fuse_norm:
@@ -296,7 +299,7 @@ class SlowARStack:
                 x, x_alt = x_alt, x
             else:
                 if self.tp_fused:
-                    ctx.tp_allreduce_rmsnorm_quantize(self.x, self.delta, lw["ffn_norm"], c.eps, B, c.dim, g,
+                    ctx.tp_allreduce_rmsnorm_quantize(self.x, None, lw["ffn_norm"], c.eps, B, c.dim, g,
                                                       Xq=self.xq, Xs=self.xs)
                 else:
                     ctx.rmsnorm_quantize(self.x, lw["ffn_norm"], c.eps, B, c.dim, g, self.xq, self.xs,
@@ -304,13 +307,15 @@ class SlowARStack:
                 ctx.linear_q(lw["w13"], lw["s13"], g, self.xq, self.xs, self.act, B, 2 * self.inter_l, c.dim,
                              epilogue=capi.EPI_SWIGLU)
             ctx.quantize(self.act, B, self.inter_l, g, self.actq, self.acts)
-            ctx.linear_q(lw["w2"], lw["s2"], g, self.actq, self.acts, self.delta, B, c.dim, self.inter_l)
+            if self.tp_fused:
+                ctx.tp_linear_q(lw["w2"], lw["s2"], g, self.actq, self.acts, B, c.dim, self.inter_l)
+            else:
+                ctx.linear_q(lw["w2"], lw["s2"], g, self.actq, self.acts, self.delta, B, c.dim, self.inter_l)
             if self.all_reduce is not None:
                 self.all_reduce(self.delta)
             pending = True
         if self.tp_fused:
-            ctx.tp_allreduce_rmsnorm_quantize(self.x, self.delta, self.final_norm, c.eps, B, c.dim, g,
-                                              normed_out=self.out)
+            ctx.tp_allreduce_rmsnorm_quantize(self.x, None, self.final_norm, c.eps, B, c.dim, g, normed_out=self.out)
         else:
             ctx.residual_add(x, self.delta, B * c.dim)
             ctx.rms_norm(x, self.final_norm, self.out, B, c.dim, c.eps)

@@ -320,19 +320,30 @@ W8A8_API int w8a8_decode_stack_timeline(w8a8_ctx* ctx, const w8a8_decode_stack* 
 
 /* ---- tensor parallelism (no counterpart in the reference, which is single-GPU) ------------- */
 
-/* Row-parallel projections (wo, w2 with K cut at quantisation-group boundaries) leave a partial
- * [M, dim] on every rank. w8a8_tp_allreduce_rmsnorm_quantize is w8a8_rmsnorm_quantize whose residual
- * is the SUM of all ranks' partials: the kernel pushes its rank's rows into every rank's exchange
- * buffer over NVLink peer memory, waits (bounded; W8A8_ERR_TIMEOUT through w8a8_check_device_status)
- * for the others' rows, adds them in rank order in fp32, rounds once to fp16, adds that to x in place,
- * and continues with RMSNorm (weight == NULL: none) and the quantiser (Xq == NULL: none).
- * Set-up, once per process: w8a8_tp_create allocates the exchange buffer for at most max_tokens rows of
- * `dim` and returns a 64-byte CUDA IPC handle; the host gathers all ranks' handles (any transport) and
- * passes the world*64 bytes, in rank order, to w8a8_tp_connect (NULL = loop-back onto this rank's own
- * buffer: the other ranks' rows then never arrive — what the time-out test uses). One process per GPU,
- * world <= 8. */
+/* Row-parallel projections (wo, w2 with K cut at quantisation-group boundaries) leave a partial [M, dim] on every
+ * rank; their sum is the projection's output. The exchange is a one-shot all-reduce over NVLink peer memory, split
+ * between the two kernels around it:
+ *   w8a8_tp_linear_q   is w8a8_linear_q whose output, instead of Y, is its fp32 partial sent tile by tile, from the
+ *                      kernel's epilogue, into every rank's exchange buffer (plain peer stores of self-validating
+ *                      {value, epoch} words: no fence, no flag, the transfer overlaps the rest of the kernel). Needs a
+ *                      weight registered with w8a8_register_packed_weight, M <= 32, no epilogue.
+ *   w8a8_tp_allreduce_rmsnorm_quantize   is w8a8_rmsnorm_quantize whose residual is the SUM of all ranks' partials:
+ *                      it waits (bounded; W8A8_ERR_TIMEOUT through w8a8_check_device_status) for every rank's words
+ *                      in its OWN buffer, adds them in rank order in fp32, rounds once to fp16, adds that to x in place
+ *                      and continues with RMSNorm (weight == NULL: none) and the quantiser (Xq == NULL: none).
+ *                      partial == NULL: the partials were sent by w8a8_tp_linear_q. partial != NULL (fp16 [M, K], e.g.
+ *                      the output of a plain w8a8_linear_q): the kernel sends it itself first. smooth_inv / act_scale
+ *                      must be NULL and act_mode W8A8_ACT_PER_TOKEN_GROUP; K % 256 == 0, K <= 4096.
+ * Every rank adds the same values in the same order, so all ranks end with the same bits; against one GPU the sum
+ * differs only by the association of fp32 additions (with partial != NULL: by one fp16 rounding per rank as well).
+ * Set-up, once per process: w8a8_tp_create allocates the exchange buffer for at most max_tokens rows of `dim` and
+ * returns a 64-byte CUDA IPC handle; the host gathers all ranks' handles (any transport) and passes the world*64
+ * bytes, in rank order, to w8a8_tp_connect (NULL = loop-back onto this rank's own buffer: the other ranks' rows then
+ * never arrive, which is what the time-out test uses). One process per GPU, world <= 8. */
 W8A8_API int w8a8_tp_create(w8a8_ctx* ctx, int rank, int world, int max_tokens, int dim, void* ipc_handle_out);
 W8A8_API int w8a8_tp_connect(w8a8_ctx* ctx, const void* all_ipc_handles);
+W8A8_API int w8a8_tp_linear_q(w8a8_ctx* ctx, const void* W, const void* w_scale, int group_size, const void* Xq,
+                     const void* Xs, int M, int N, int K, const w8a8_linear_opts* opts, void* stream);
 W8A8_API int w8a8_tp_allreduce_rmsnorm_quantize(w8a8_ctx* ctx, void* x, const void* partial, const void* weight,
                                        float eps, const void* smooth_inv, const void* act_scale, int M,
                                        int K, int group_size, int act_mode, void* normed_out, void* Xq,

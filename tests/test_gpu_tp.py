@@ -44,6 +44,50 @@ def test_missing_peer_times_out_cleanly(pkg, oracle):
     ctx.close()
 
 
+@pytest.mark.parametrize("M,N,K,g", [(8, 2560, 4096, 256), (5, 2560, 1280, 256), (8, 1024, 512, 64), (3, 768, 1024, 128)])
+def test_send_from_the_linear_with_one_rank_equals_the_plain_chain(pkg, oracle, M, N, K, g):
+    """w8a8_tp_linear_q + w8a8_tp_allreduce_rmsnorm_quantize(partial = NULL) with a world of ONE rank: the linear's
+    fp32 partial goes through the exchange buffer (its own), is summed (one term), rounded to fp16 and added to x.
+    That must equal w8a8_linear_q followed by w8a8_rmsnorm_quantize with its output as the residual, bit for bit,
+    over five consecutive exchanges (epochs advance on the device, slots alternate by parity)."""
+    from fish_audio_cpp_b200 import synth
+
+    torch.cuda.set_device(0)
+    ctx = pkg.Context(0, 1 << 22)
+    ctx.tp_create(0, 1, 8, N)
+    X, W, ws = synth.linear_case(700 + M + N, M, N, K, g)
+    rng = np.random.default_rng(K)
+    w = rng.uniform(0.5, 1.5, N).astype(np.float16)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()  # noqa: E731
+    dW, dS, dw = dev(W), dev(ws), dev(w)
+    dP = torch.empty((ctx.packed_weight_bytes(N, K, g),), dtype=torch.uint8, device="cuda")
+    ctx.pack_weight(dW, dS, N, K, g, dP)
+    ctx.register_packed_weight(dW, dP, N, K, g)
+    try:
+        x0 = rng.standard_normal((M, N)).astype(np.float16)
+        cx, dx = dev(x0), dev(x0)
+        for it in range(5):
+            Xi = synth.activations(rng, M, K)
+            Xq, Xs = oracle.quantize(Xi, g)
+            dXq, dXs = dev(Xq), dev(Xs)
+            cY = torch.empty((M, N), dtype=torch.float16, device="cuda")
+            cq = torch.empty((M, N), dtype=torch.int8, device="cuda"); cs = torch.empty((M, N // g), dtype=torch.float32, device="cuda")
+            cn = torch.empty((M, N), dtype=torch.float16, device="cuda")
+            ctx.linear_q(dW, dS, g, dXq, dXs, cY, M, N, K)
+            ctx.rmsnorm_quantize(cx, dw, 1e-6, M, N, g, cq, cs, residual=cY, normed_out=cn)
+            dq = torch.empty_like(cq); ds = torch.empty_like(cs); dn = torch.empty_like(cn)
+            ctx.tp_linear_q(dW, dS, g, dXq, dXs, M, N, K)
+            ctx.tp_allreduce_rmsnorm_quantize(dx, None, dw, 1e-6, M, N, g, Xq=dq, Xs=ds, normed_out=dn)
+            torch.cuda.synchronize()
+            ctx.check_device_status()
+            assert torch.equal(dx.view(torch.int16), cx.view(torch.int16)), f"exchange {it}: residual stream"
+            assert torch.equal(dn.view(torch.int16), cn.view(torch.int16)), f"exchange {it}: normed rows"
+            assert torch.equal(dq, cq) and torch.equal(ds, cs), f"exchange {it}: codes and scales"
+    finally:
+        ctx.register_packed_weight(dW, None)
+        ctx.close()
+
+
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 def test_two_rank_exchange_matches_oracle():
     world = 2
