@@ -477,7 +477,8 @@ int w8a8_paged_attention_decode(w8a8_ctx* ctx, const void* q, const void* k_cach
                                          static_cast<const __half*>(v_cache), block_table, seq_lens, batch, n_heads,
                                          n_kv_heads, max_blocks_per_seq, sm_scale, layer, n_layers,
                                          static_cast<__half*>(out), quant_group_size, static_cast<int8_t*>(Xq),
-                                         static_cast<float*>(Xs), context_splits, static_cast<cudaStream_t>(stream));
+                                         static_cast<float*>(Xs), context_splits, ctx->device_status,
+                                         static_cast<cudaStream_t>(stream));
 }
 
 int w8a8_qkv_attention_decode(w8a8_ctx* ctx, const void* qkv, const void* q_norm_w, const void* k_norm_w, float eps,
@@ -496,7 +497,8 @@ int w8a8_qkv_attention_decode(w8a8_ctx* ctx, const void* qkv, const void* q_norm
                                        static_cast<__half*>(k_cache), static_cast<__half*>(v_cache), block_table, seq_lens,
                                        batch, n_heads, n_kv_heads, max_blocks_per_seq, sm_scale, layer, n_layers,
                                        static_cast<__half*>(out), quant_group_size, static_cast<int8_t*>(Xq),
-                                       static_cast<float*>(Xs), context_splits, static_cast<cudaStream_t>(stream));
+                                       static_cast<float*>(Xs), context_splits, ctx->device_status,
+                                       static_cast<cudaStream_t>(stream));
 }
 
 size_t w8a8_decode_stack_workspace_bytes(const w8a8_decode_stack* stack) {

@@ -142,31 +142,31 @@ struct AttnParams {
     const int* positions;     // [B]
     __half* k_cache_w;        // the caches again, writable
     __half* v_cache_w;
+    int* status;              // error word for bounded waits that ran out
 };
 
-constexpr int kAttnWarps = 8;
-constexpr int kQPerKv = 4;  // query heads per kv head handled by one CTA
+#ifndef W8A8_ATTN_WARPS
+#define W8A8_ATTN_WARPS 8
+#endif
+#ifndef W8A8_ATTN_RING
+#define W8A8_ATTN_RING 16
+#endif
+constexpr int kAttnWarps = W8A8_ATTN_WARPS;      // consumer warps
+constexpr int kAttnThreads = (kAttnWarps + 1) * 32;  // + one producer warp
+constexpr int kQPerKv = 4;                       // query heads per kv head handled by one CTA
+constexpr int kBoxBytes = kBlockTokens * 128;    // a TMA box: 16 token rows x 128 bytes (64 dims), 128-byte swizzle
+constexpr int kBlkBytes = 2 * kBoxBytes;         // one 16-token block of K (or of V): dims 0..63, then dims 64..127
+constexpr int kStageBytes = 2 * kBlkBytes;       // K block, then V block
+constexpr int kRing = W8A8_ATTN_RING;            // stages of the CTA's ring, 8 KB each: two per consumer warp, so that a
+                                                 // warp's next block is on its way while it works on the current one
 
-// K and V of one 16-token block as one lane sees them (64 registers):
-//   k[j][i]: token j*8 + (lane>>2), 16-byte piece i*4 + (lane&3) of its 128 dims;
-//   v[q][h]: token {2t, 2t+1, 2t+8, 2t+9}[q] with t = lane&3, 16-byte piece (lane>>2) + 8h.
-struct KvFrag {
-    uint4 k[2][4];
-    uint4 v[4][2];
-};
-
-__device__ __forceinline__ uint4 ld_stream16(const __half* ptr) {
-    uint4 r;
-    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
-                 : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(ptr));
-    return r;
+// Byte offset, inside a K or V block in shared memory, of the 16-byte chunk that holds dims [8 c16, 8 c16 + 8) of
+// token row r: the box of its 64-dim half, the row's 128 bytes, the chunk XOR-ed with the row (what the tensor
+// map's 128-byte swizzle does, and what makes eight rows of one chunk column fall into eight different bank groups).
+__device__ __forceinline__ uint32_t kv_chunk(int r, int c16) {
+    return (c16 >> 3) * kBoxBytes + r * 128 + (((c16 & 7) ^ (r & 7)) << 4);
 }
 
-__device__ __forceinline__ uint4 ld_cg16(const __half* ptr) {
-    uint4 r;
-    asm volatile("ld.global.cg.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(ptr));
-    return r;
-}
 
 // One warp, one head of the new token: per-head RMSNorm in the reference's order (rms_norm.cu:23-49 with a
 // 128-thread block) and interleaved-pair RoPE (rope.cu:36-45) — the arithmetic of qknorm_rope_kvwrite_kernel.
@@ -210,229 +210,289 @@ __device__ __forceinline__ void mma_top_rows(float& d0, float& d1, uint32_t a0, 
         : "r"(a0), "r"(0u), "r"(a2), "r"(0u), "r"(b0), "r"(b1), "f"(d0), "f"(d1), "f"(0.0f), "f"(0.0f));
 }
 
-__device__ __forceinline__ uint32_t reg_of(const uint4& v, int i) {
-    return i == 0 ? v.x : i == 1 ? v.y : i == 2 ? v.z : v.w;
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void consumer_barrier() {  // the eight consumer warps only
+    asm volatile("bar.sync 1, %0;" ::"n"(kAttnWarps * 32) : "memory");
 }
 
-// grid (S, n_kv, B), cluster (S,1,1), 8 warps. The four query heads of a kv group are rows 0..3 of a
-// 16-row tensor-core tile (mma.sync.m16n8k16, fp32 accumulate): scores = Q K^T with tokens as the
-// n index, then out += P V with P rounded to fp16 (the softmax denominator is summed from the same
-// rounded values, so the weights stay normalised). The sums over head dims (QK) and over tokens (PV)
-// do not depend on order, so each lane takes whole 16-byte pieces straight from the cache and the
-// "k index" of an MMA is a permutation of the real one, applied to q alike; V's token pairs are put
-// side by side with one byte-permute per register. Nothing is staged in shared memory. Each warp
-// keeps the next block's 8 KB in flight while it works on the current one.
+// grid (S, n_kv, B), cluster (S,1,1); eight consumer warps and one producer warp per CTA.
 //
-// ROPE form: the launch also does what qknorm_rope_kvwrite_kernel does. Warps 0..3 norm and rotate the four
-// query heads into shared memory; in the CTA that attends over the block the new token joins, warps 4 and 5
-// write the new k and v rows into the cache first. The first two KV blocks of every warp are requested
-// before that work, so its latency hides under theirs.
+// The K and V of one (sequence, kv head) are 4 KB blocks scattered over the paged cache. The producer warp brings them
+// into a ring of shared-memory stages with TMA (cp.async.bulk.tensor.2d over the cache seen as rows of 256 bytes,
+// two 16 x 128-byte boxes per block, 128-byte swizzle, completion counted on the stage's mbarrier; single 256-byte
+// row copies were tried first and are bound by the copy engine's request rate) — no registers are tied up by bytes in flight, so the kernel fits beside a CTA of
+// the linear before it, and everything the producer needs (sequence length, block table, every block but the
+// sequence's last) does not depend on that linear: with programmatic dependent launch the ring is already full when
+// the query arrives. 16-token blocks are dealt round-robin, first over the cluster's CTAs, then over the consumer
+// warps; a consumer waits for its block, computes on it from shared memory (ldmatrix into mma.sync.m16n8k16 with
+// fp32 accumulation: scores = Q K^T with the four query heads of the group as rows 0..3 of the tile, then
+// out += P V with P rounded to fp16 and the softmax denominator summed from the same rounded values) and hands the
+// stage back. Partial softmax states are merged over the warps in shared memory and over the cluster through
+// distributed shared memory; the epilogue can emit the o-projection's int8 codes and scales directly.
+//
+// ROPE form: the launch also does what qknorm_rope_kvwrite_kernel does. Consumer warps 0..3 norm and rotate the four
+// query heads into shared memory; warps 4 and 5 do the same for the new k and v rows, which go to shared memory and,
+// in the CTA that owns the block the new token joins, to the cache. That block is read from the cache like any other
+// (possibly before the new rows are there) and the new rows are put over it in shared memory.
+// Without ROPE the new rows were written by the launch before this one, so the sequence's last block is requested
+// only after the dependency wait.
 template <bool ROPE>
-__global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_kernel(const AttnParams p) {
-    W8A8_TRACE_SCOPE();
-    ptx::pdl_launch_dependents();
-    ptx::pdl_wait();
-    W8A8_TRACE_WAITED();
-    __shared__ __align__(16) __half q_s[ROPE ? kQPerKv : 1][kHeadDim];
+__global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_constant__ CUtensorMap map_k,
+                                                               const __grid_constant__ CUtensorMap map_v,
+                                                               const AttnParams p) {
+    extern __shared__ unsigned char attn_smem[];
+    __shared__ __align__(8) uint64_t full_bar[kRing], empty_bar[kRing];
+    __shared__ __align__(16) __half q_s[kQPerKv][kHeadDim];
+    __shared__ __align__(16) __half kv_new_s[2][kHeadDim];
     __shared__ float red_m[kAttnWarps][kQPerKv], red_l[kAttnWarps][kQPerKv];
     __shared__ float red_acc[kAttnWarps][kQPerKv][kHeadDim];
     __shared__ float cta_m[kQPerKv], cta_l[kQPerKv];
     __shared__ __align__(16) float cta_acc[kQPerKv][kHeadDim];
     __shared__ __align__(16) __half out_s[kQPerKv * kHeadDim];
+    __shared__ int s_fail;
+    W8A8_TRACE_SCOPE();
+    ptx::pdl_launch_dependents();
 
     const int s = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, S = p.S;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int seq_len = p.seq_lens[b];
-    // 16-token blocks are dealt round-robin: first over the cluster's CTAs, then over the warps. The physical
-    // numbers of this warp's next 32 blocks, one per lane, are requested before seq_len is used anywhere (the
-    // read is bounded by the table's width), so that the two reads are one round trip, not two.
-    const int stride = S * kAttnWarps, first = s + warp * S;
-    auto fetch_phys = [&](int it0) -> int {
-        const int bi = first + (it0 + lane) * stride;
-        return bi < p.max_blocks ? p.block_table[static_cast<size_t>(b) * p.max_blocks + bi] : 0;
-    };
-    int phys_mine = fetch_phys(0);
-    const int heads_here = p.n_q / p.n_kv;  // == kQPerKv (checked on the host)
-
-    // ROPE: everything the prologue reads is requested here, before the first value is used
-    int pos = 0;
-    bool owner = false;
-    const bool role_q = warp < kQPerKv, is_k = warp == kQPerKv, is_v = warp == kQPerKv + 1;
-    __half hq[4], wq[4];
-    float fr[4];
-    const __half* norm_w = nullptr;
-    if constexpr (ROPE) {
-        pos = p.positions[b];
-        norm_w = role_q ? p.q_norm_w : p.k_norm_w;
-        const int total_heads = p.n_q + 2 * p.n_kv;
-        const __half* src = p.qkv + (static_cast<size_t>(b) * total_heads +
-                                     (role_q ? kvh * heads_here + warp : p.n_q + (is_k ? 0 : p.n_kv) + kvh)) * kHeadDim;
-#pragma unroll
-        for (int v = 0; v < 4; ++v) {
-            hq[v] = (role_q || is_k || is_v) ? src[v * 32 + lane] : __float2half(0.0f);
-            wq[v] = norm_w ? norm_w[v * 32 + lane] : __float2half(1.0f);
-            fr[v] = p.freqs[(v * 32 + lane) >> 1];
+    const uint32_t ring = (ptx::smem_u32(attn_smem) + 1023u) & ~1023u;  // the swizzle pattern repeats every 1024 bytes
+    if (threadIdx.x == 0) {
+        ptx::prefetch_tensormap(&map_k);
+        ptx::prefetch_tensormap(&map_v);
+        for (int i = 0; i < kRing; ++i) {
+            ptx::mbar_init(&full_bar[i], 1);
+            ptx::mbar_init(&empty_bar[i], 1);
         }
-        owner = ((pos / kBlockTokens) % S) == s;  // this CTA attends over the block the new token joins
+        s_fail = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async();
     }
+    __syncthreads();  // the only whole-CTA barrier: from here on the producer warp runs by itself
 
+    // Read before the dependency wait: these are not results of the launch before this one.
+    const int seq_len = p.seq_lens[b];
     const int n_blocks = (seq_len + kBlockTokens - 1) / kBlockTokens;
-    const int n_mine = first < n_blocks ? (n_blocks - first + stride - 1) / stride : 0;
+    const int n_local = s < n_blocks ? (n_blocks - s + S - 1) / S : 0;  // blocks s, s + S, s + 2 S, ...
+    const int heads_here = p.n_q / p.n_kv;                                // == kQPerKv (checked on the host)
 
-    auto load = [&](KvFrag& f, int it) {
-        if ((it & 31) == 0 && it > 0) phys_mine = fetch_phys(it);
-        const int phys = __shfl_sync(0xffffffffu, phys_mine, it & 31);
-        const int bi = first + it * stride;
-        const int tokens = min(kBlockTokens, seq_len - bi * kBlockTokens);
-        const size_t base = (((static_cast<size_t>(phys) * p.n_layers + p.layer) * p.n_kv + kvh) * kBlockTokens) * kHeadDim;
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            const int tok = j * 8 + g;
-            const __half* row = p.k_cache + base + static_cast<size_t>(tok < tokens ? tok : 0) * kHeadDim;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) f.k[j][i] = ROPE ? ld_cg16(row + (i * 4 + t) * 8) : ld_stream16(row + (i * 4 + t) * 8);
+    if (warp == kAttnWarps) {
+        // ------------------------------ producer ------------------------------
+        // Eight blocks per round, four lanes per block (one TMA box each): a single lane issuing every copy of the
+        // CTA one after the other costs more than the copies take.
+        bool waited = false;
+        int phys_mine = 0;
+        bool failed = false;
+        for (int li0 = 0; li0 < n_local && !failed; li0 += 8) {
+            if ((li0 & 31) == 0) {  // the physical numbers of the next 32 local blocks, one per lane
+                const int bi = s + (li0 + lane) * S;
+                phys_mine = (bi < n_blocks && bi < p.max_blocks) ? p.block_table[static_cast<size_t>(b) * p.max_blocks + bi] : 0;
+            }
+            const int li = li0 + (lane >> 2), box = lane & 3;
+            const int phys = __shfl_sync(0xffffffffu, phys_mine, li & 31);
+            const int bi = s + li * S, st = li % kRing;
+            const bool live = li < n_local;
+            // Without ROPE the newest rows come from the launch before this one: wait for it before the round that
+            // holds the sequence's last block.
+            if (!ROPE && !waited && s + (li0 + 7) * S >= n_blocks - 1) {
+                ptx::pdl_wait();
+                waited = true;
+            }
+            if (live && li >= kRing && !ptx::mbar_wait_bounded(&empty_bar[st], ((li / kRing) - 1) & 1)) {
+                if (box == 0) { atomicExch(p.status, 800 + st); s_fail = 1; }
+                failed = true;
+            }
+            failed = __any_sync(0xffffffffu, failed);
+            if (failed) break;
+            if (live && box == 0) ptx::mbar_arrive_expect_tx(&full_bar[st], kStageBytes);
+            __syncwarp();
+            if (live) {  // box 0: K dims 0..63, 1: K dims 64..127, 2: V dims 0..63, 3: V dims 64..127
+                const int y = ((phys < 0 ? 0 : phys) * p.n_layers + p.layer) * p.n_kv * kBlockTokens + kvh * kBlockTokens;
+                asm volatile(
+                    "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                    ::"r"(ring + st * kStageBytes + box * kBoxBytes), "l"(box < 2 ? &map_k : &map_v),
+                      "r"(ptx::smem_u32(&full_bar[st])), "r"((box & 1) * 128), "r"(y)
+                    : "memory");
+            }
         }
+        if (!waited) ptx::pdl_wait();
+    } else {
+        // ------------------------------ consumers ------------------------------
+        int pos = 0;
+        bool owner = false;
+        float fr[4];
+        if constexpr (ROPE) {  // parameters first: they do not depend on the launch before this one
+            pos = p.positions[b];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-            const int tok = 2 * t + (q & 1) + 8 * (q >> 1);
-            const __half* row = p.v_cache + base + static_cast<size_t>(tok < tokens ? tok : 0) * kHeadDim;
-#pragma unroll
-            for (int h = 0; h < 2; ++h) f.v[q][h] = ROPE ? ld_cg16(row + (g + 8 * h) * 8) : ld_stream16(row + (g + 8 * h) * 8);
+            for (int v = 0; v < 4; ++v) fr[v] = p.freqs[(v * 32 + lane) >> 1];
+            owner = ((pos / kBlockTokens) % S) == s;  // this CTA attends over the block the new token joins
         }
-    };
-
-    KvFrag fa, fb;
-    const int new_bi = pos / kBlockTokens;
-    const bool pre0 = n_mine > 0 && !(ROPE && owner && first == new_bi);
-    const bool pre1 = n_mine > 1 && !(ROPE && owner && first + stride == new_bi);
-    if (pre0) load(fa, 0);
-    if (pre1) load(fb, 1);
-    if constexpr (ROPE) {
-        if (role_q || ((is_k || is_v) && owner)) {
-            if (!is_v) head_norm_rope(hq, norm_w != nullptr, wq, p.eps, fr, pos, lane);
-            if (role_q) {
+        ptx::pdl_wait();
+        W8A8_TRACE_WAITED();
+        const int new_bi = pos / kBlockTokens;
+        if constexpr (ROPE) {
+            // six head rows of the new token: the group's four query heads, then its k and its v; a warp per row
+            const int total_heads = p.n_q + 2 * p.n_kv;
+            for (int h = warp; h < kQPerKv + 2; h += kAttnWarps) {
+                const bool role_q = h < kQPerKv, is_k = h == kQPerKv, is_v = h == kQPerKv + 1;
+                const __half* norm_w = role_q ? p.q_norm_w : p.k_norm_w;
+                const __half* src = p.qkv + (static_cast<size_t>(b) * total_heads +
+                                             (role_q ? kvh * heads_here + h : p.n_q + (is_k ? 0 : p.n_kv) + kvh)) * kHeadDim;
+                __half hq[4], wq[4];
 #pragma unroll
-                for (int v = 0; v < 4; ++v) q_s[warp][v * 32 + lane] = hq[v];
-            } else {
-                const int phys = p.block_table[static_cast<size_t>(b) * p.max_blocks + new_bi];
-                if (phys >= 0) {
-                    __half* dst = (is_k ? p.k_cache_w : p.v_cache_w) +
-                                  ((((static_cast<size_t>(phys) * p.n_layers + p.layer) * p.n_kv + kvh) * kBlockTokens) +
-                                   pos % kBlockTokens) * kHeadDim;
+                for (int v = 0; v < 4; ++v) {
+                    hq[v] = src[v * 32 + lane];
+                    wq[v] = (norm_w && !is_v) ? norm_w[v * 32 + lane] : __float2half(1.0f);
+                }
+                if (!is_v) head_norm_rope(hq, norm_w != nullptr, wq, p.eps, fr, pos, lane);
+                if (role_q) {
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) dst[v * 32 + lane] = hq[v];
+                    for (int v = 0; v < 4; ++v) q_s[h][v * 32 + lane] = hq[v];
+                } else {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) kv_new_s[is_v ? 1 : 0][v * 32 + lane] = hq[v];
+                    if (owner) {
+                        const int phys = p.block_table[static_cast<size_t>(b) * p.max_blocks + new_bi];
+                        if (phys >= 0) {
+                            __half* dst = (is_k ? p.k_cache_w : p.v_cache_w) +
+                                          ((((static_cast<size_t>(phys) * p.n_layers + p.layer) * p.n_kv + kvh) * kBlockTokens) +
+                                           pos % kBlockTokens) * kHeadDim;
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) dst[v * 32 + lane] = hq[v];
+                        }
+                    }
+                }
+            }
+            consumer_barrier();  // q and the new k / v rows are in shared memory
+        }
+        // q of head g (rows 4..15 of the tile are zero): A fragments of the eight 16-dim steps
+        uint32_t qa[8][2];
+#pragma unroll
+        for (int kk = 0; kk < 8; ++kk) {
+            qa[kk][0] = 0u;
+            qa[kk][1] = 0u;
+            if (g < kQPerKv) {
+                if constexpr (ROPE) {
+                    qa[kk][0] = *reinterpret_cast<const uint32_t*>(&q_s[g][16 * kk + 2 * t]);
+                    qa[kk][1] = *reinterpret_cast<const uint32_t*>(&q_s[g][16 * kk + 8 + 2 * t]);
+                } else {
+                    const __half* qrow = p.q + (static_cast<size_t>(b) * p.n_q + kvh * heads_here + g) * kHeadDim;
+                    qa[kk][0] = *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 2 * t);
+                    qa[kk][1] = *reinterpret_cast<const uint32_t*>(qrow + 16 * kk + 8 + 2 * t);
                 }
             }
         }
-        __syncthreads();  // q in shared memory; the new k and v rows written (read back past L1)
-        if (n_mine > 0 && !pre0) load(fa, 0);
-        if (n_mine > 1 && !pre1) load(fb, 1);
-    }
-    // q of head g (rows 4..15 of the tile are zero), in the same piece order as K
-    uint32_t qa[4][4];
+
+        float m_run = -1e30f, l_run = 0.0f;
+        float o[16][2];  // head g, dims 8 n + 2 t, 8 n + 2 t + 1
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        for (int n = 0; n < 16; ++n) { o[n][0] = 0.0f; o[n][1] = 0.0f; }
+
+        for (int li = warp; li < n_local; li += kAttnWarps) {
+            const int st = li % kRing, bi = s + li * S;
+            if (!ptx::mbar_wait_bounded(&full_bar[st], (li / kRing) & 1)) {
+                if (lane == 0) { atomicExch(p.status, 810 + st); s_fail = 1; }
+                break;
+            }
+            const uint32_t ks = ring + st * kStageBytes, vs = ks + kBlkBytes;
+            const int tokens = min(kBlockTokens, seq_len - bi * kBlockTokens);
+            if (ROPE && bi == new_bi) {  // the new token's rows over whatever the cache held there (lane: 4 dims)
+                const int r = pos % kBlockTokens;
+                const uint2 kn = reinterpret_cast<const uint2*>(kv_new_s[0])[lane], vn = reinterpret_cast<const uint2*>(kv_new_s[1])[lane];
+                const uint32_t off = kv_chunk(r, lane >> 1) + (lane & 1) * 8;
+                asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(ks + off), "r"(kn.x), "r"(kn.y) : "memory");
+                asm volatile("st.shared.v2.u32 [%0], {%1,%2};" ::"r"(vs + off), "r"(vn.x), "r"(vn.y) : "memory");
+            }
+            // V rows past the sequence's end: their weights are exactly zero, but whatever lies there (it may not be
+            // a number) must not meet the multiply. (K rows past the end only feed scores that are replaced below.)
+            for (int r = tokens; r < kBlockTokens; ++r)
+                asm volatile("st.shared.v2.u32 [%0], {%1,%1};" ::"r"(vs + (lane >> 4) * kBoxBytes + r * 128 + (lane & 15) * 8), "r"(0u)
+                             : "memory");
+            __syncwarp();
+            // scores: two tiles of 8 tokens x eight steps of 16 dims
+            float sc[2][2];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                sc[j][0] = 0.0f; sc[j][1] = 0.0f;
+#pragma unroll
+                for (int k2 = 0; k2 < 4; ++k2) {  // matrices: dims 32 k2 + 8 (lane >> 3) of tokens 8 j + (lane & 7)
+                    uint32_t r4[4];
+                    ldmatrix_x4(r4, ks + kv_chunk(8 * j + (lane & 7), 4 * k2 + (lane >> 3)));
+                    mma_top_rows(sc[j][0], sc[j][1], qa[2 * k2][0], qa[2 * k2][1], r4[0], r4[1]);
+                    mma_top_rows(sc[j][0], sc[j][1], qa[2 * k2 + 1][0], qa[2 * k2 + 1][1], r4[2], r4[3]);
+                }
+            }
+            float mx = -1e30f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int tok = j * 8 + 2 * t + e;
+                    sc[j][e] = tok < tokens ? sc[j][e] * p.sm_scale : -1e30f;
+                    mx = fmaxf(mx, sc[j][e]);
+                }
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float new_m = fmaxf(m_run, mx);
+            const float corr = __expf(m_run - new_m);
+            m_run = new_m;
+            const __half2 p0 = __floats2half2_rn(__expf(sc[0][0] - new_m), __expf(sc[0][1] - new_m));
+            const __half2 p1 = __floats2half2_rn(__expf(sc[1][0] - new_m), __expf(sc[1][1] - new_m));
+            const float2 f0 = __half22float2(p0), f1 = __half22float2(p1);
+            l_run = l_run * corr + ((f0.x + f0.y) + (f1.x + f1.y));
+            const uint32_t pa0 = *reinterpret_cast<const uint32_t*>(&p0), pa2 = *reinterpret_cast<const uint32_t*>(&p1);
+#pragma unroll
+            for (int n2 = 0; n2 < 8; ++n2) {  // matrices (transposed): tokens 8 (m & 1) + (lane & 7), dims 16 n2 + 8 (m >> 1)
+                uint32_t r4[4];
+                const int m = lane >> 3;
+                ldmatrix_x4_trans(r4, vs + kv_chunk(8 * (m & 1) + (lane & 7), 2 * n2 + (m >> 1)));
+                o[2 * n2][0] *= corr; o[2 * n2][1] *= corr;
+                o[2 * n2 + 1][0] *= corr; o[2 * n2 + 1][1] *= corr;
+                mma_top_rows(o[2 * n2][0], o[2 * n2][1], pa0, pa2, r4[0], r4[1]);
+                mma_top_rows(o[2 * n2 + 1][0], o[2 * n2 + 1][1], pa0, pa2, r4[2], r4[3]);
+            }
+            // the stage goes back to the producer; the writes above (the new rows) are ordered before its next copy
+            ptx::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&empty_bar[st]);
+        }
+        // the four lanes of a quad hold the same head: their partial denominators add up
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+        l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
         if (g < kQPerKv) {
-            if constexpr (ROPE) v = *reinterpret_cast<const uint4*>(&q_s[g][(i * 4 + t) * 8]);
-            else v = *reinterpret_cast<const uint4*>(p.q + (static_cast<size_t>(b) * p.n_q + kvh * heads_here + g) * kHeadDim +
-                                                     (i * 4 + t) * 8);
-        }
-        qa[i][0] = v.x; qa[i][1] = v.y; qa[i][2] = v.z; qa[i][3] = v.w;
-    }
-
-    float m_run = -1e30f, l_run = 0.0f;
-    float o[16][2];  // head g; tile n = 8h + e holds dims (2t + 8h)*8 + e and (2t + 1 + 8h)*8 + e
+            if (t == 0) { red_m[warp][g] = m_run; red_l[warp][g] = l_run; }
 #pragma unroll
-    for (int n = 0; n < 16; ++n) { o[n][0] = 0.0f; o[n][1] = 0.0f; }
-
-    auto compute = [&](const KvFrag& f, int it) {
-        const int bi = first + it * stride;
-        const int tokens = min(kBlockTokens, seq_len - bi * kBlockTokens);
-        float sc[2][2];
-#pragma unroll
-        for (int j = 0; j < 2; ++j) {
-            sc[j][0] = 0.0f; sc[j][1] = 0.0f;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h)
-                    mma_top_rows(sc[j][0], sc[j][1], qa[i][2 * h], qa[i][2 * h + 1], reg_of(f.k[j][i], 2 * h),
-                                 reg_of(f.k[j][i], 2 * h + 1));
+            for (int n = 0; n < 16; ++n) {
+                red_acc[warp][g][8 * n + 2 * t] = o[n][0];
+                red_acc[warp][g][8 * n + 2 * t + 1] = o[n][1];
             }
         }
-        float mx = -1e30f;
+        consumer_barrier();
+        // ---- merge the warps: thread -> (head, 4 dims) ----
+        if (threadIdx.x < kQPerKv * 32) {
+            const int hh = threadIdx.x >> 5, d0 = (threadIdx.x & 31) * 4;
+            float m = -1e30f;
+            for (int w = 0; w < kAttnWarps; ++w) m = fmaxf(m, red_m[w][hh]);
+            float l = 0.0f, a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            for (int w = 0; w < kAttnWarps; ++w) {
+                const float scw = __expf(red_m[w][hh] - m);
+                l += red_l[w][hh] * scw;
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int tok = j * 8 + 2 * t + e;
-                sc[j][e] = tok < tokens ? sc[j][e] * p.sm_scale : -1e30f;
-                mx = fmaxf(mx, sc[j][e]);
+                for (int i = 0; i < 4; ++i) a[i] += red_acc[w][hh][d0 + i] * scw;
             }
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float new_m = fmaxf(m_run, mx);
-        const float corr = __expf(m_run - new_m);
-        m_run = new_m;
-        const __half2 p0 = __floats2half2_rn(__expf(sc[0][0] - new_m), __expf(sc[0][1] - new_m));
-        const __half2 p1 = __floats2half2_rn(__expf(sc[1][0] - new_m), __expf(sc[1][1] - new_m));
-        const float2 f0 = __half22float2(p0), f1 = __half22float2(p1);
-        l_run = l_run * corr + ((f0.x + f0.y) + (f1.x + f1.y));
-        const uint32_t pa0 = *reinterpret_cast<const uint32_t*>(&p0), pa2 = *reinterpret_cast<const uint32_t*>(&p1);
 #pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                const int n = h * 8 + e;
-                const uint32_t sel = (e & 1) ? 0x7632u : 0x5410u;
-                const uint32_t b0 = __byte_perm(reg_of(f.v[0][h], e >> 1), reg_of(f.v[1][h], e >> 1), sel);
-                const uint32_t b1 = __byte_perm(reg_of(f.v[2][h], e >> 1), reg_of(f.v[3][h], e >> 1), sel);
-                o[n][0] *= corr;
-                o[n][1] *= corr;
-                mma_top_rows(o[n][0], o[n][1], pa0, pa2, b0, b1);
-            }
-    };
-
-    for (int it = 0; it < n_mine;) {  // fa holds block `it`, fb block `it + 1`
-        compute(fa, it);
-        if (it + 2 < n_mine) load(fa, it + 2);
-        if (++it >= n_mine) break;
-        compute(fb, it);
-        if (it + 2 < n_mine) load(fb, it + 2);
-        ++it;
-    }
-    // the four lanes of a quad hold the same head: their partial denominators add up
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
-    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
-    if (g < kQPerKv) {
-        if (t == 0) { red_m[warp][g] = m_run; red_l[warp][g] = l_run; }
-#pragma unroll
-        for (int h = 0; h < 2; ++h)
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                red_acc[warp][g][(2 * t + 8 * h) * 8 + e] = o[h * 8 + e][0];
-                red_acc[warp][g][(2 * t + 1 + 8 * h) * 8 + e] = o[h * 8 + e][1];
-            }
-    }
-    __syncthreads();
-    // ---- merge the warps: thread -> (head, 4 dims) ----
-    if (threadIdx.x < kQPerKv * 32) {
-        const int hh = threadIdx.x >> 5, d0 = (threadIdx.x & 31) * 4;
-        float m = -1e30f;
-        for (int w = 0; w < kAttnWarps; ++w) m = fmaxf(m, red_m[w][hh]);
-        float l = 0.0f, a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        for (int w = 0; w < kAttnWarps; ++w) {
-            const float scw = __expf(red_m[w][hh] - m);
-            l += red_l[w][hh] * scw;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) a[i] += red_acc[w][hh][d0 + i] * scw;
+            for (int i = 0; i < 4; ++i) cta_acc[hh][d0 + i] = a[i];
+            if ((threadIdx.x & 31) == 0) { cta_m[hh] = m; cta_l[hh] = l; }
         }
-#pragma unroll
-        for (int i = 0; i < 4; ++i) cta_acc[hh][d0 + i] = a[i];
-        if ((threadIdx.x & 31) == 0) { cta_m[hh] = m; cta_l[hh] = l; }
     }
+    // ---- every thread of the cluster (the producer warps included) ----
     cg::cluster_group cluster = cg::this_cluster();
     if (S > 1) cluster.sync(); else __syncthreads();
     // ---- CTA 0 of the cluster merges the S context slices and writes the 4 heads ----
@@ -461,7 +521,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_ker
     }
     if (S > 1) cluster.sync(); else __syncthreads();
     // ---- optional: quantise these 512 channels for the o-projection (int8_gemm.cu:147-211) ----
-    if (s == 0 && p.Xq) {
+    if (s == 0 && p.Xq && warp < kAttnWarps) {
         const int gsz = p.g, K = p.n_q * kHeadDim, G = K / gsz;
         const int ch0 = kvh * heads_here * kHeadDim;          // first channel of this CTA
         const int groups_here = (kQPerKv * kHeadDim) / gsz;   // 2 at g=256, 8 at g=64
@@ -479,6 +539,9 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) paged_attention_decode_ker
                 p.Xq[static_cast<size_t>(b) * K + ch0 + j * gsz + e] = static_cast<int8_t>(qv);
             }
         }
+    }
+    if (s_fail) {  // a bounded wait ran out: give copies that may still be in flight time to land before the CTA goes
+        for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     }
     W8A8_TRACE_END(4u);
 }
@@ -513,8 +576,9 @@ int launch_attention(const AttnParams& base, int B, int splits, cudaStream_t str
 int launch_paged_attention_decode(const __half* q, const __half* k_cache, const __half* v_cache,
                                   const int* block_table, const int* seq_lens, int B, int n_q, int n_kv,
                                   int max_blocks, float sm_scale, int layer, int n_layers, __half* out, int g,
-                                  int8_t* Xq, float* Xs, int splits, cudaStream_t stream) {
+                                  int8_t* Xq, float* Xs, int splits, int* status, cudaStream_t stream) {
     AttnParams p = {};
+    p.status = status;
     p.q = q; p.k_cache = k_cache; p.v_cache = v_cache; p.block_table = block_table; p.seq_lens = seq_lens;
     p.max_blocks = max_blocks; p.n_q = n_q; p.n_kv = n_kv; p.layer = layer; p.n_layers = n_layers; p.sm_scale = sm_scale;
     p.out = out; p.Xq = Xq; p.Xs = Xs; p.g = g;
@@ -525,8 +589,9 @@ int launch_qkv_attention_decode(const __half* qkv, const __half* q_norm_w, const
                                 const float* freqs, const int* positions, __half* k_cache, __half* v_cache,
                                 const int* block_table, const int* seq_lens, int B, int n_q, int n_kv, int max_blocks,
                                 float sm_scale, int layer, int n_layers, __half* out, int g, int8_t* Xq, float* Xs,
-                                int splits, cudaStream_t stream) {
+                                int splits, int* status, cudaStream_t stream) {
     AttnParams p = {};
+    p.status = status;
     p.k_cache = k_cache; p.v_cache = v_cache; p.block_table = block_table; p.seq_lens = seq_lens;
     p.max_blocks = max_blocks; p.n_q = n_q; p.n_kv = n_kv; p.layer = layer; p.n_layers = n_layers; p.sm_scale = sm_scale;
     p.out = out; p.Xq = Xq; p.Xs = Xs; p.g = g;
@@ -555,9 +620,26 @@ int launch_attention(const AttnParams& base, int B, int splits, cudaStream_t str
     if (splits > 8) splits = 8;
     AttnParams p = base;
     p.S = splits;
+    // The caches as rows of 256 bytes (one token of one head); a box is 16 rows x 128 bytes. The row count only bounds
+    // the coordinates the kernel may ask for: the physical block numbers come from the caller's block table.
+    CUtensorMap map_k, map_v;
+    int rc = make_tensor_map_2d_u8(&map_k, p.k_cache, kHeadDim * 2, uint64_t(1) << 30, kHeadDim * 2, 128, kBlockTokens, 1);
+    if (rc) return rc;
+    rc = make_tensor_map_2d_u8(&map_v, p.v_cache, kHeadDim * 2, uint64_t(1) << 30, kHeadDim * 2, 128, kBlockTokens, 1);
+    if (rc) return rc;
+    const size_t smem = static_cast<size_t>(kRing) * kStageBytes + 1024;
+    {  // per device, so on every launch (a host-side table write)
+        cudaError_t e = cudaFuncSetAttribute(paged_attention_decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(paged_attention_decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(smem));
+        if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+    }
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(splits, n_kv, B);
-    cfg.blockDim = dim3(kAttnWarps * 32, 1, 1);
+    cfg.blockDim = dim3(kAttnThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -568,8 +650,8 @@ int launch_attention(const AttnParams& base, int B, int splits, cudaStream_t str
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = pdl_enabled(kPdlAttn) ? 2 : 1;
-    cudaError_t e = p.qkv ? cudaLaunchKernelEx(&cfg, paged_attention_decode_kernel<true>, p)
-                          : cudaLaunchKernelEx(&cfg, paged_attention_decode_kernel<false>, p);
+    cudaError_t e = p.qkv ? cudaLaunchKernelEx(&cfg, paged_attention_decode_kernel<true>, map_k, map_v, p)
+                          : cudaLaunchKernelEx(&cfg, paged_attention_decode_kernel<false>, map_k, map_v, p);
     if (e != cudaSuccess) return fail(W8A8_ERR_CUDA, "paged_attention_decode launch: %s", cudaGetErrorString(e));
     return W8A8_OK;
 }

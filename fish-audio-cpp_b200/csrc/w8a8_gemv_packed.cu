@@ -54,7 +54,15 @@ struct GemvPackedParams {
     int bpu;          // blocks per unit (1, or g / 256 when g > 256)
     unsigned U;       // units in all
     int* status;
+#ifdef W8A8_TRACE
+    int ablate;       // diagnostic build: bit mask of pieces of the kernel to leave out (timing experiments only)
+#endif
 };
+#ifdef W8A8_TRACE
+#define W8A8_ABLATED(bit) ((p.ablate & (bit)) != 0)
+#else
+#define W8A8_ABLATED(bit) false
+#endif
 
 __device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                        uint32_t b0, uint32_t b1) {
@@ -607,7 +615,7 @@ gemv_packed_kernel(const GemvPackedParams p) {
                             const uint2 w = make_uint2(__float_as_uint(v[nt][2 * hrow + e]), static_cast<unsigned>(tp_ep));
                             for (int r = 0; r < a.tp.world; ++r) reinterpret_cast<uint2*>(a.tp.peers[r])[word] = w;
                         }
-                        if (!a.Y) continue;
+                        if (!a.Y || W8A8_ABLATED(4)) continue;
                         __half y = __float2half(v[nt][2 * hrow + e]);
                         if (a.epilogue == W8A8_EPI_RESIDUAL)
                             y = __float2half(__half2float(y) + __half2float(a.residual[o]));
@@ -628,7 +636,7 @@ gemv_packed_kernel(const GemvPackedParams p) {
     // partials in ascending-K order and stores. Nothing waits; nothing leaves the SM.
     auto finish_tile = [&](int rt) {
         const unsigned t_lo = static_cast<unsigned>(rt) * p.upt, t_hi = t_lo + p.upt;  // [t_lo, t_hi)
-        if (u0 <= t_lo && t_hi <= u1) {
+        if ((u0 <= t_lo && t_hi <= u1) || W8A8_ABLATED(8)) {
             store_tile(rt, acc);
         } else {
             const unsigned first = warp_of_unit(t_lo), last = warp_of_unit(t_hi - 1);
@@ -708,6 +716,7 @@ gemv_packed_kernel(const GemvPackedParams p) {
 #pragma unroll
             for (int nt = 0; nt < MT; ++nt) {
                 if constexpr (FUSED) dst[ch][nt] = lds128(xq_s + kbase + ch * 64);
+                else if (W8A8_ABLATED(1)) dst[ch][nt] = make_uint4(0x01010101u, 0x01010101u, 0x01010101u, 0x01010101u);
                 else dst[ch][nt] = __ldg(reinterpret_cast<const uint4*>(xq[nt] + kbase + ch * 64));
             }
     };
@@ -719,6 +728,9 @@ gemv_packed_kernel(const GemvPackedParams p) {
                 if constexpr (FUSED) {
                     dst[q][nt][0] = xsp_s[0][unit_b * GPU + q];
                     dst[q][nt][1] = xsp_s[1][unit_b * GPU + q];
+                } else if (W8A8_ABLATED(2)) {
+                    dst[q][nt][0] = 1.0f;
+                    dst[q][nt][1] = 1.0f;
                 } else {
                     dst[q][nt][0] = __ldg(xsp[nt][0] + unit_b * GPU + q);
                     dst[q][nt][1] = __ldg(xsp[nt][1] + unit_b * GPU + q);
@@ -925,6 +937,12 @@ int launch_variant(const LinearArgs& a, const Plan& pl, int* status, cudaStream_
     p.bpu = pl.bpu;
     p.U = static_cast<unsigned>(pl.U);
     p.status = status;
+#ifdef W8A8_TRACE
+    {
+        const char* v = std::getenv("W8A8_ABLATE");
+        p.ablate = v ? std::atoi(v) : 0;
+    }
+#endif
     auto kern = gemv_packed_kernel<MT, GM, PRO, ST, KI>;
     const size_t ring = static_cast<size_t>(kWarps) * ST * kStagePitch + 128;
     const size_t smem = ring + (PRO == kProNorm ? fused_smem_bytes(a.K, a.G) : 0);

@@ -19,9 +19,9 @@ int check_launch(const char* what);
 // them is still running, and wait inside the kernel for its results). Classes are a bit mask so that
 // the environment variable W8A8_PDL=<mask> can switch them one by one; W8A8_NO_PDL=1 switches all off.
 enum { kPdlLinear = 1, kPdlRow = 2, kPdlAttn = 4 };
-// Measured over the decode stack: early launch pays for the linears (weights are requested while the
-// small kernel before them runs) and the row kernels, and costs time on the clustered attention launch.
-constexpr int kPdlDefaultMask = kPdlLinear | kPdlRow;
+// Early launch pays for the linears (weights are requested while the small kernel before them runs), for the
+// row kernels, and for the attention launch (its ring of K / V blocks fills while the qkv projection runs).
+constexpr int kPdlDefaultMask = kPdlLinear | kPdlRow | kPdlAttn;
 bool pdl_enabled(int kernel_class);
 
 inline int norm_group(int K, int group_size) {
@@ -122,12 +122,12 @@ int launch_qknorm_rope_kvwrite(const __half* qkv, const __half* q_norm_w, const 
 int launch_paged_attention_decode(const __half* q, const __half* k_cache, const __half* v_cache,
                                   const int* block_table, const int* seq_lens, int B, int n_q, int n_kv,
                                   int max_blocks, float sm_scale, int layer, int n_layers, __half* out, int g,
-                                  int8_t* Xq, float* Xs, int splits, cudaStream_t stream);
+                                  int8_t* Xq, float* Xs, int splits, int* status, cudaStream_t stream);
 int launch_qkv_attention_decode(const __half* qkv, const __half* q_norm_w, const __half* k_norm_w, float eps,
                                 const float* freqs, const int* positions, __half* k_cache, __half* v_cache,
                                 const int* block_table, const int* seq_lens, int B, int n_q, int n_kv, int max_blocks,
                                 float sm_scale, int layer, int n_layers, __half* out, int g, int8_t* Xq, float* Xs,
-                                int splits, cudaStream_t stream);
+                                int splits, int* status, cudaStream_t stream);
 // w8a8_decode_stack.cu : a whole decode step as one persistent cooperative kernel.
 size_t decode_stack_workspace_bytes(const w8a8_decode_stack& d);
 int launch_decode_stack(const w8a8_decode_stack& d, unsigned char* workspace, size_t workspace_bytes, float* partials,
