@@ -701,6 +701,75 @@ def cpu_baseline_prefill(budget_s=15.0):
 
 
 # ------------------------------------------------------------------------------------------
+TRACE_KERNELS = {2: "rowquant", 3: "groupquant", 4: "attention", 5: "tp_row", 10: "gemv", 11: "gemv+norm",
+                 14: "gemv+rowtail", 18: "gemv+grouptail"}
+
+
+def read_device_trace():
+    """Records left by a diagnostic build of the library (python fish-audio-cpp_b200/build.py --define W8A8_TRACE
+    --out DIR, then W8A8_LIBRARY=DIR/libw8a8.so): thread 0 of the first and of the last CTA of every decode kernel
+    stamps the GPU's nanosecond timer at kernel entry, after the dependency wait and at the CTA's end. Returns a
+    list of tuples (t_entry, t_waited, t_end, kernel id, cta, ctas, aux) and clears the device buffers; [] when the
+    loaded library was not built with the trace."""
+    import ctypes as C
+
+    from fish_audio_cpp_b200 import capi
+
+    class Rec(C.Structure):
+        _fields_ = [("t_entry", C.c_ulonglong), ("t_waited", C.c_ulonglong), ("t_end", C.c_ulonglong),
+                    ("id", C.c_uint), ("cta", C.c_uint), ("ctas", C.c_uint), ("aux", C.c_uint)]
+    lib, out = capi.load_library(), []
+    for name in ("gemv_packed", "quant", "attn", "tp"):
+        fn = getattr(lib, "w8a8_trace_read_" + name, None)
+        if fn is None:
+            return []
+        fn.restype = C.c_int
+        buf = (Rec * 16384)()
+        n = fn(buf, 16384)
+        out += [(r.t_entry, r.t_waited, r.t_end, r.id, r.cta, r.ctas, r.aux) for r in buf[:max(n, 0)]]
+    return out
+
+
+def step_timeline(torch, wl):
+    """One replayed decode step as a per-kernel device timeline: for every position in a layer's launch sequence the
+    median over the layers of (a) the edge: from the end of the kernel before it to the moment its own dependency
+    wait returned, and (b) the body: from there to its last recorded CTA's end. Microseconds."""
+    read_device_trace()
+    wl.step()
+    torch.cuda.synchronize()
+    recs = sorted(read_device_trace(), key=lambda r: r[2])
+    if not recs:
+        return {"error": "the loaded library has no trace (build it with --define W8A8_TRACE and set W8A8_LIBRARY)"}
+    inst, pending = [], {}
+    for r in recs:
+        key = (r[3], r[5], r[6])
+        if r[5] == 1:
+            inst.append(dict(id=r[3], aux=r[6], W=r[1], E=r[2]))
+        elif key in pending and pending[key][4] != r[4]:
+            o = pending.pop(key)
+            inst.append(dict(id=r[3], aux=r[6], W=max(o[1], r[1]), E=max(o[2], r[2])))
+        else:
+            pending[key] = r
+    inst.sort(key=lambda k: k["E"])
+    L = wl.cfg.n_layer
+    per = len(inst) // L
+    if per == 0 or len(inst) < per * L:
+        return {"error": f"{len(inst)} kernel instances do not divide into {L} layers"}
+    edges, bodies = np.zeros((L - 1, per)), np.zeros((L - 1, per))
+    for l in range(1, L):
+        for j in range(per):
+            k, prev = inst[l * per + j], inst[l * per + j - 1]
+            edges[l - 1, j] = (k["W"] - prev["E"]) / 1e3
+            bodies[l - 1, j] = (k["E"] - k["W"]) / 1e3
+    rows = []
+    for j in range(per):
+        k = inst[per + j]
+        name = TRACE_KERNELS.get(k["id"], str(k["id"])) + (f"[N={k['aux']}]" if k["aux"] else "")
+        rows.append([name, round(float(np.median(edges[:, j])), 2), round(float(np.median(bodies[:, j])), 2)])
+    return {"per_layer": rows, "layer_us": round(float(np.median(edges, 0).sum() + np.median(bodies, 0).sum()), 2),
+            "columns": ["kernel", "edge_us", "body_us"]}
+
+
 def int8_library_tops(torch):
     """cuBLASLt int8 -> int32 at 8192^3 through torch._int_mm: the measured int8 tensor figure of this GPU."""
     t = torch
@@ -835,6 +904,9 @@ def main():
     ap.add_argument("--split-k", type=int, default=0, help="force the GEMV's K-slice count (tuning aid)")
     ap.add_argument("--no-pack", action="store_true", help="leave weights row-major (skip the loader-side pack)")
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a graph")
+    ap.add_argument("--trace", action="store_true",
+                    help="decode_stack: add the per-kernel device timeline of one replayed step to the line (needs a "
+                         "library built with --define W8A8_TRACE, named by W8A8_LIBRARY)")
     ap.add_argument("--timeline", action="store_true",
                     help="with --step-form one-launch: add the device-side per-phase medians of one step to the line")
     ap.add_argument("--step-form", choices=["one-launch", "chain"], default="chain",
@@ -952,6 +1024,12 @@ def main():
         wl.step()
         torch.cuda.synchronize()
     clocks = sampler.stop()
+    # every rank steps (the tensor-parallel exchange needs all of them); rank 0 reports its own GPU's timeline
+    kernel_timeline = None
+    if args.trace and args.workload == "decode_stack" and not reference:
+        barrier()
+        kernel_timeline = step_timeline(torch, wl)
+        barrier()
 
     times = torch.tensor([dev_ms, e2e_ms or 0.0, lin[0] if lin else 0.0], dtype=torch.float64, device="cuda")
     if dist is not None:
@@ -1061,6 +1139,8 @@ def main():
         }
         if args.timeline and getattr(wl, "one_launch", False):
             line["config"]["timeline_us"] = wl.timeline()
+        if kernel_timeline is not None:
+            line["config"]["kernel_timeline"] = kernel_timeline
         if lin:
             ach = lin[1] / lin_s / 1e9
             line["roofline"] = {"bound": "hbm", "achieved": round(ach, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",

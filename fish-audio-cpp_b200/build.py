@@ -81,4 +81,17 @@ def build(verbose: bool = False, force: bool = False, ptxas_info: bool = False, 
 
 
 if __name__ == "__main__":
-    print(build(verbose="-v" in sys.argv, force="-f" in sys.argv, ptxas_info="--ptxas" in sys.argv))
+    # python build.py [-v] [-f] [--ptxas] [--define NAME[=VALUE]]... [--out DIR]
+    #   --define W8A8_TRACE --out DIR   the diagnostic build whose kernels record a device-side timeline
+    #                                   (bench.py --trace reads it; point W8A8_LIBRARY at DIR/libw8a8.so)
+    argv = sys.argv[1:]
+    defs, out = [], None
+    i = 0
+    while i < len(argv):
+        if argv[i] == "--define" and i + 1 < len(argv):
+            defs.append(argv[i + 1]); i += 2
+        elif argv[i] == "--out" and i + 1 < len(argv):
+            out = argv[i + 1]; i += 2
+        else:
+            i += 1
+    print(build(verbose="-v" in argv, force="-f" in argv, ptxas_info="--ptxas" in argv, defines=defs, out_dir=out))

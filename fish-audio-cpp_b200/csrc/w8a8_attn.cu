@@ -277,7 +277,14 @@ __global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_cons
     }
     __syncthreads();  // the only whole-CTA barrier: from here on the producer warp runs by itself
 
-    // Read before the dependency wait: these are not results of the launch before this one.
+    // Read before the dependency wait: these are not results of the launch before this one. The producer asks for the
+    // first 32 block numbers without waiting for the sequence length (the read is bounded by the table's width), so
+    // that the two reads are one round trip, not two.
+    int phys_first = 0;
+    if (warp == kAttnWarps) {
+        const int bi = s + lane * S;
+        phys_first = bi < p.max_blocks ? p.block_table[static_cast<size_t>(b) * p.max_blocks + bi] : 0;
+    }
     const int seq_len = p.seq_lens[b];
     const int n_blocks = (seq_len + kBlockTokens - 1) / kBlockTokens;
     const int n_local = s < n_blocks ? (n_blocks - s + S - 1) / S : 0;  // blocks s, s + S, s + 2 S, ...
@@ -288,10 +295,10 @@ __global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_cons
         // Eight blocks per round, four lanes per block (one TMA box each): a single lane issuing every copy of the
         // CTA one after the other costs more than the copies take.
         bool waited = false;
-        int phys_mine = 0;
+        int phys_mine = phys_first;
         bool failed = false;
         for (int li0 = 0; li0 < n_local && !failed; li0 += 8) {
-            if ((li0 & 31) == 0) {  // the physical numbers of the next 32 local blocks, one per lane
+            if ((li0 & 31) == 0 && li0 > 0) {  // the physical numbers of the next 32 local blocks, one per lane
                 const int bi = s + (li0 + lane) * S;
                 phys_mine = (bi < n_blocks && bi < p.max_blocks) ? p.block_table[static_cast<size_t>(b) * p.max_blocks + bi] : 0;
             }

@@ -19,9 +19,10 @@ int check_launch(const char* what);
 // them is still running, and wait inside the kernel for its results). Classes are a bit mask so that
 // the environment variable W8A8_PDL=<mask> can switch them one by one; W8A8_NO_PDL=1 switches all off.
 enum { kPdlLinear = 1, kPdlRow = 2, kPdlAttn = 4 };
-// Early launch pays for the linears (weights are requested while the small kernel before them runs), for the
-// row kernels, and for the attention launch (its ring of K / V blocks fills while the qkv projection runs).
-constexpr int kPdlDefaultMask = kPdlLinear | kPdlRow | kPdlAttn;
+// Measured over the decode stack: early launch pays for the linears (weights are requested while the small kernel
+// before them runs) and for the row kernels. It costs time on the attention launch: its CTAs, resident early, take
+// the shared memory that the second CTA per SM of the linear before them needs.
+constexpr int kPdlDefaultMask = kPdlLinear | kPdlRow;
 bool pdl_enabled(int kernel_class);
 
 inline int norm_group(int K, int group_size) {

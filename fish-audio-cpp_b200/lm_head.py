@@ -42,3 +42,38 @@ def expand_logits(compact, rows, vocab: int, fill=-np.inf):
     out = np.full((compact.shape[0], vocab), fill, dtype=compact.dtype)
     out[:, np.asarray(rows)] = compact
     return out
+
+
+# ---- column-parallel over the vocabulary (tensor parallelism) ----
+# The reference runs on one GPU. Under tensor parallelism the head's rows are independent outputs (each has its own
+# weight scales, and the activation codes are the same on every rank), so a rank computes the logits of its own row
+# range with the same decode kernel and the ranges are concatenated: bit-identical to the single-GPU logits.
+
+def vocab_shard(vocab: int, world: int, rank: int, unit: int = 16):
+    """Row range ``[lo, hi)`` of rank ``rank``: whole units of ``unit`` rows (the packed decode stream's row tile),
+    the first ``units % world`` ranks one unit longer; a ragged tail of fewer than ``unit`` rows goes to the last rank."""
+    if not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside a world of {world}")
+    units = vocab // unit
+    base, extra = divmod(units, world)
+    lo = (rank * base + min(rank, extra)) * unit
+    hi = ((rank + 1) * base + min(rank + 1, extra)) * unit
+    if rank == world - 1:
+        hi = vocab
+    return lo, hi
+
+
+def gather_logits(torch, dist, local, vocab: int, world: int, group=None):
+    """``[M, vocab]`` logits on every rank from the ranks' ``[M, hi - lo]`` slices: one all-gather of equal-sized
+    (padded) pieces — the ranges differ by at most one unit plus the ragged tail — then the padding is cut away."""
+    bounds = [vocab_shard(vocab, world, r) for r in range(world)]
+    widest = max(hi - lo for lo, hi in bounds)
+    M = local.shape[0]
+    padded = local
+    if local.shape[1] != widest:
+        padded = torch.zeros((M, widest), dtype=local.dtype, device=local.device)
+        padded[:, : local.shape[1]] = local
+    flat = torch.empty((world * M, widest), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(flat, padded.contiguous(), group=group)
+    pieces = flat.view(world, M, widest)
+    return torch.cat([pieces[r, :, : hi - lo] for r, (lo, hi) in enumerate(bounds)], dim=1)

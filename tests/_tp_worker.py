@@ -52,6 +52,26 @@ def worker(rank, world, port, q):
 
 
 
+def lm_head_worker(rank, world, port, q):
+    """One rank of the column-parallel LM head on CPU: the oracle computes this rank's row range of a small head,
+    the slices are gathered (gloo) and must equal the full head bit for bit."""
+    from oracle import oracle
+    from fish_audio_cpp_b200 import lm_head as lmh
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        M, vocab, K, g = 3, 16 * 13 + 5, 512, 256   # 13 row tiles over 2 ranks (7 + 6) and a ragged tail of 5
+        X, W, ws = synth.linear_case(11, M, vocab, K, g)
+        full = oracle.linear(W, ws, g, X)
+        lo, hi = lmh.vocab_shard(vocab, world, rank)
+        # (the fp16 bit patterns travel as int32: gloo has no 16-bit integer all-gather)
+        local = torch.from_numpy(oracle.linear(W[lo:hi], ws[lo:hi], g, X).view(np.uint16).astype(np.int32))
+        got = lmh.gather_logits(torch, dist, local, vocab, world).numpy()
+        q.put((rank, bool(np.array_equal(got, full.view(np.uint16).astype(np.int32))), (lo, hi)))
+    finally:
+        dist.destroy_process_group()
+
+
 def free_port():
     import socket
     with socket.socket() as s:
@@ -110,6 +130,50 @@ def gpu_exchange_worker(rank, world, port, q):
         dist.destroy_process_group()
     except Exception as e:  # noqa: BLE001
         q.put((rank, False, repr(e)))
+
+
+def gpu_lm_head_worker(rank, world, port, q):
+    """One rank of the column-parallel int8 LM head on GPUs: the packed decode kernel over this rank's rows of a
+    [vocab, 2560] head (g256), slices gathered over NCCL, compared with the whole head run on the same GPU."""
+    try:
+        from fish_audio_cpp_b200 import lm_head as lmh
+        pkg = ge.package()
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        ctx = pkg.Context(rank, 1 << 22)
+        vocab, K, g = 155776 // 8, 2560, 256  # an eighth of the real head: 19472 rows = 1217 row tiles (odd)
+        ok, msg = True, ""
+        for M in (1, 8):
+            X, W, ws = synth.linear_case(900 + M, M, vocab, K, g)
+            dX = torch.from_numpy(X).cuda()
+            dW, dS = torch.from_numpy(W).cuda(), torch.from_numpy(ws).cuda()
+
+            def run(Wd, Sd, n):
+                packed = torch.empty((ctx.packed_weight_bytes(n, K, g),), dtype=torch.uint8, device="cuda")
+                ctx.pack_weight(Wd, Sd, n, K, g, packed)
+                ctx.register_packed_weight(Wd, packed, n, K, g)
+                Y = torch.empty((M, n), dtype=torch.float16, device="cuda")
+                ctx.linear(Wd, Sd, g, dX, Y, M, n, K)
+                torch.cuda.synchronize()
+                ctx.register_packed_weight(Wd, None)
+                return Y
+
+            full = run(dW, dS, vocab)
+            lo, hi = lmh.vocab_shard(vocab, world, rank)
+            local = run(dW[lo:hi].contiguous(), dS[lo:hi].contiguous(), hi - lo)
+            got = lmh.gather_logits(torch, dist, local, vocab, world)
+            ctx.check_device_status()
+            if not torch.equal(got.view(torch.int16), full.view(torch.int16)):
+                ok, msg = False, f"M={M}: gathered logits differ from the whole head"
+                break
+        dist.barrier()
+        q.put((rank, ok, msg))
+        ctx.close()
+        dist.destroy_process_group()
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, False, traceback.format_exc() + repr(e)))
 
 
 def gpu_stack_worker(rank, world, port, q, tp_mode="fused", layers=2):

@@ -145,6 +145,54 @@ def test_stack_at_benchmark_width_matches_oracle_and_reference_chain(pkg, oracle
         ctx.close()
 
 
+def test_fast_ar_frame_matches_oracle_chain(pkg, oracle):
+    """One frame of the fast-AR codebook decoder at its real width: ten codebook steps of a 4-layer stack (hidden 2560,
+    32 q / 8 kv heads, SwiGLU 9728, no qk-norm, g64) at batch 8 over a cache that starts empty, each followed by the
+    final norm and the codebook head 2560 -> 4096 (the order of DualAREngine::fast_codebook_decode_device,
+    src/engine/dual_ar_engine.cc:769-844), against the CPU oracle chain fed with the same inputs step by step (each
+    side keeps its own cache). Bar per step: relative L2 distance of the logits within max(5e-3, 3 x the distance by
+    which a one-ulp jitter of the oracle's own attention output moves its logits)."""
+    from fish_audio_cpp_b200 import synth
+
+    ctx = pkg.Context(0, 1 << 22)
+    cfg = S.SlowARConfig(n_layer=4, group=64, qk_norm=False)
+    B, steps, vocab = 8, 10, 4096
+    st = S.SlowARStack(torch, ctx, cfg, B, 0, max_new=16, seed=41)
+    rng = np.random.default_rng(9)
+    hw, hs = synth.weights(rng, vocab, cfg.dim), synth.weight_scales(rng, vocab, cfg.dim // 64)
+    dhw, dhs = torch.from_numpy(hw).cuda(), torch.from_numpy(hs).cuda()
+    img = torch.empty((ctx.packed_weight_bytes(vocab, cfg.dim, 64),), dtype=torch.uint8, device="cuda")
+    ctx.pack_weight(dhw, dhs, vocab, cfg.dim, 64, img)
+    ctx.register_packed_weight(dhw, img, vocab, cfg.dim, 64)
+    try:
+        kc, vc = st.k_cache.cpu().numpy().copy(), st.v_cache.cpu().numpy().copy()
+        kj, vj = kc.copy(), vc.copy()
+        bt = st.block_table.cpu().numpy()
+        logits = torch.empty((B, vocab), dtype=torch.float16, device="cuda")
+        worst = 0.0
+        for step in range(steps):
+            x_in = (rng.standard_normal((B, cfg.dim)) * 0.5).astype(np.float16)
+            pos = np.full((B,), step, np.int32)
+            out = st.decode_step(torch.from_numpy(x_in).cuda())
+            ctx.linear(dhw, dhs, 64, out, logits, B, vocab, cfg.dim)
+            torch.cuda.synchronize()
+            ctx.check_device_status()
+            got = logits.cpu().numpy().astype(np.float32)
+            want_h = oracle_step(oracle, st, x_in, kc, vc, bt, pos)
+            want = oracle.linear(hw, hs, 64, want_h).astype(np.float32)
+            jit_h = oracle_step(oracle, st, x_in, kj, vj, bt, pos, jitter=np.random.default_rng(step))
+            noise = np.linalg.norm(oracle.linear(hw, hs, 64, jit_h).astype(np.float32) - want) / np.linalg.norm(want)
+            rel = np.linalg.norm(got - want) / np.linalg.norm(want)
+            worst = max(worst, rel / max(5e-3, 3.0 * noise))
+            assert rel < max(5e-3, 3.0 * noise), (step, rel, noise)
+        print(f"[fast-AR frame] worst step at {worst:.2f} of its bar")
+        assert int(st.positions[0]) == steps
+    finally:
+        ctx.register_packed_weight(dhw, None)
+        st.close()
+        ctx.close()
+
+
 @pytest.mark.parametrize("group,dim,n_kv,inter,layers,B,context", [
     (256, 512, 1, 512, 2, 3, 37), (64, 1024, 2, 768, 3, 8, 100), (128, 2560, 8, 1024, 2, 8, 530), (256, 2560, 8, 9728, 2, 5, 1024),
     (256, 2560, 8, 9728, 1, 8, 1024)])

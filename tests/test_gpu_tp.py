@@ -104,6 +104,25 @@ def test_two_rank_exchange_matches_oracle():
         assert ok, f"rank {rank}: {msg}"
 
 
+@pytest.mark.parametrize("world", [2, 8])
+def test_column_parallel_lm_head_matches_whole_head(world):
+    """The int8 LM head cut over the vocabulary: every rank runs the packed decode kernel over its own rows, the
+    slices are gathered over NCCL; the result must be the whole head's logits bit for bit (rows are independent)."""
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _tp_worker.free_port()
+    procs = [ctx.Process(target=_tp_worker.gpu_lm_head_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, ok, msg in res:
+        assert ok, f"rank {rank}: {msg}"
+
+
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_tp_decode_step_matches_single_gpu(world):
     """One decode step of a 1-layer and of a 2-layer stack of the benchmark's width at TP 2 / 4 / 8 against the same

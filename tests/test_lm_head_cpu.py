@@ -28,3 +28,19 @@ def test_compact_head_and_expansion():
     full = lmh.expand_logits(logits, rows, 64)
     assert full.shape == (2, 64) and np.array_equal(full[:, rows], logits)
     assert np.isneginf(np.delete(full, rows, axis=1)).all()
+
+
+@pytest.mark.parametrize("world", [1, 2, 4, 8])
+@pytest.mark.parametrize("vocab", [155776, 4097, 160])
+def test_vocab_shards_tile_the_rows_in_whole_row_tiles(world, vocab):
+    """Column-parallel LM head: the ranks' row ranges tile [0, vocab) without gap or overlap, every range but the
+    last is a whole number of 16-row tiles (what the packed decode stream needs), and they differ by at most one tile
+    plus the ragged tail."""
+    b = [lmh.vocab_shard(vocab, world, r) for r in range(world)]
+    assert b[0][0] == 0 and b[-1][1] == vocab
+    assert all(b[i][1] == b[i + 1][0] for i in range(world - 1))
+    assert all((hi - lo) % 16 == 0 for lo, hi in b[:-1]) and all(lo % 16 == 0 for lo, _ in b)
+    widths = [hi - lo for lo, hi in b]
+    assert max(widths) - min(widths) <= 16 + vocab % 16
+    with pytest.raises(ValueError):
+        lmh.vocab_shard(vocab, world, world)

@@ -62,3 +62,19 @@ def test_row_and_column_parallel_with_gloo():
         assert ok_col, "column-parallel shards must gather to the full result bit for bit"
         assert ok_quant, "per-(token, group) quantisation must not depend on the shard"
         assert ulp <= 1, f"row-parallel all-reduce differs by {ulp} fp16 ulp"
+
+
+@pytest.mark.timeout(120)
+def test_column_parallel_lm_head_with_gloo():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_worker.lm_head_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=100) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    assert sorted(b for _, _, b in res) == [(0, 112), (112, 213)]
+    for rank, same, _ in res:
+        assert same, f"rank {rank}: gathered logits must equal the whole head bit for bit"
