@@ -770,6 +770,60 @@ def step_timeline(torch, wl):
             "columns": ["kernel", "edge_us", "body_us"]}
 
 
+def gemm_timeline(torch, pkg, M=8192, groups=(256, 64)):
+    """Where a tile of the prefill GEMM spends its time (gate_up, M tokens): a diagnostic build of the library
+    (--define W8A8_TRACE) stamps the SM clock in CTA 0's MMA-issuing lane and first epilogue warp per K-group and in
+    its producer lane per K-block. Medians over four tiles' worth of groups, microseconds at 1965 MHz."""
+    import ctypes as C
+
+    from fish_audio_cpp_b200 import capi
+    fn = getattr(capi.load_library(), "w8a8_trace_read_gemm", None)
+    if fn is None:
+        return {"error": "the loaded library has no trace (build it with --define W8A8_TRACE and set W8A8_LIBRARY)"}
+    fn.restype, fn.argtypes = C.c_int, [C.c_void_p, C.c_int]
+    K, N = 2560, 19456
+    ctx = pkg.Context(torch.cuda.current_device(), 0)
+    out = {}
+    for g in groups:
+        G = K // g
+        W = torch.randint(-127, 128, (N, K), dtype=torch.int8, device="cuda")
+        ws = (torch.rand((N, G), device="cuda") * 4e-3 + 1e-3).half()
+        Xq = torch.randint(-127, 128, (M, K), dtype=torch.int8, device="cuda")
+        Xs = torch.rand((M, G), device="cuda") * 1e-2 + 1e-3
+        Y = torch.empty((M, N), dtype=torch.float16, device="cuda")
+        buf = np.zeros((3, 512, 4), np.uint64)
+        for _ in range(3):
+            ctx.linear_q(W, ws, g, Xq, Xs, Y, M, N, K)
+        torch.cuda.synchronize()
+        fn(buf.ctypes.data, buf.nbytes)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        ctx.linear_q(W, ws, g, Xq, Xs, Y, M, N, K)
+        e1.record()
+        torch.cuda.synchronize()
+        if fn(buf.ctypes.data, buf.nbytes) <= 0:
+            return {"error": "reading the trace failed"}
+        b = buf.astype(np.int64)
+        pro, mma, epi = b[0], b[1], b[2]
+        lo, hi = 2 * G, min(6 * G, 500)
+        us = lambda x: round(float(np.median(x)) / 1965.0, 3)  # noqa: E731
+        kbs = K // 128
+        out[f"g{g}"] = {
+            "launch_us": round(e0.elapsed_time(e1) * 1e3, 1),
+            "mma_lane_per_group": {"wait_operands": us(mma[lo:hi, 1] - mma[lo:hi, 0]), "wait_accumulator_slice": us(mma[lo:hi, 2] - mma[lo:hi, 1]),
+                                   "issue_mmas_and_commit": us(mma[lo:hi, 3] - mma[lo:hi, 2]), "period": us(np.diff(mma[lo:hi, 0]))},
+            "epilogue_warp_per_group": {"wait_sums": us(epi[lo:hi, 1] - epi[lo:hi, 0]), "load_and_promote_until_release": us(epi[lo:hi, 2] - epi[lo:hi, 1]),
+                                        "rest_of_promote": us(epi[lo:hi, 3] - epi[lo:hi, 2]), "period": us(np.diff(epi[lo:hi, 0]))},
+            "producer_lane_per_kblock": {"wait_free_stage": us(pro[2 * kbs:min(6 * kbs, 500), 1] - pro[2 * kbs:min(6 * kbs, 500), 0]),
+                                         "period": us(np.diff(pro[2 * kbs:min(6 * kbs, 500), 0]))},
+            # from the last promote of a tile to the first wait of the next: output conversion, store, scale preload
+            "between_tiles": round(float(epi[3 * G, 0] - epi[3 * G - 1, 3]) / 1965.0, 3) if 3 * G < 512 else None,
+        }
+        del W, ws, Xq, Xs, Y
+    ctx.close()
+    return out
+
+
 def int8_library_tops(torch):
     """cuBLASLt int8 -> int32 at 8192^3 through torch._int_mm: the measured int8 tensor figure of this GPU."""
     t = torch
@@ -905,8 +959,9 @@ def main():
     ap.add_argument("--no-pack", action="store_true", help="leave weights row-major (skip the loader-side pack)")
     ap.add_argument("--eager", action="store_true", help="launch kernels one by one instead of replaying a graph")
     ap.add_argument("--trace", action="store_true",
-                    help="decode_stack: add the per-kernel device timeline of one replayed step to the line (needs a "
-                         "library built with --define W8A8_TRACE, named by W8A8_LIBRARY)")
+                    help="decode_stack: add the per-kernel device timeline of one replayed step to the line; prefill: add "
+                         "the per-K-group timeline of the GEMM's MMA lane, epilogue and producer (both need a library "
+                         "built with --define W8A8_TRACE, named by W8A8_LIBRARY)")
     ap.add_argument("--timeline", action="store_true",
                     help="with --step-form one-launch: add the device-side per-phase medians of one step to the line")
     ap.add_argument("--step-form", choices=["one-launch", "chain"], default="chain",
@@ -1064,7 +1119,8 @@ def main():
                                    "W8A8 linear (row quantiser + tcgen05 GEMM) each per step", "cases_per_step": len(wl.cases),
                        "l2": "inputs larger than L2: 8 weight sets + 8 activation sets in rotation (> 600 MB)",
                        "parallelism": par,
-                       "library_int8_tops_8192cubed": int8_library_tops(torch)},
+                       "library_int8_tops_8192cubed": int8_library_tops(torch),
+                       **({"gemm_timeline": gemm_timeline(torch, ge.package())} if (args.trace and not reference) else {})},
             "roofline": {"bound": "tensor", "achieved": round(tops / world, 1), "peak": round(peak, 1), "unit": "TOP/s",
                          "frac": round(tops / world / peak, 4),
                          "traffic": int(GEMM_TRAFFIC_RATIO * sum(

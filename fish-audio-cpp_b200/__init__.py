@@ -13,6 +13,8 @@ from .capi import (  # noqa: F401
     EPI_SWIGLU,
     KERNEL_AUTO,
     KERNEL_GEMM,
+    KERNEL_GEMM_PAIR,
+    KERNEL_GEMM_SINGLE,
     KERNEL_GEMV,
     KERNEL_GEMV_PACKED,
     KERNEL_GEMV_TMA,

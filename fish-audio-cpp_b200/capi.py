@@ -7,6 +7,7 @@ from pathlib import Path
 ACT_PER_TOKEN_GROUP, ACT_PER_TOKEN = 0, 1
 EPI_NONE, EPI_RESIDUAL, EPI_SWIGLU = 0, 1, 2
 KERNEL_AUTO, KERNEL_GENERIC, KERNEL_GEMV, KERNEL_GEMM, KERNEL_GEMV_TMA, KERNEL_GEMV_PACKED = 0, 1, 2, 3, 4, 5
+KERNEL_GEMM_SINGLE, KERNEL_GEMM_PAIR = 6, 7
 
 _LIB = None
 

@@ -79,7 +79,7 @@ static int check_linear_common(const w8a8_ctx* ctx, const void* W, const void* w
             return fail(W8A8_ERR_INVALID_ARG, "W8A8_EPI_SWIGLU needs N %% 16 == 0 (got %d)", N);
         if (o->act_mode != W8A8_ACT_PER_TOKEN_GROUP && o->act_mode != W8A8_ACT_PER_TOKEN)
             return fail(W8A8_ERR_INVALID_ARG, "unknown act_mode %d", o->act_mode);
-        if (o->kernel < W8A8_KERNEL_AUTO || o->kernel > W8A8_KERNEL_GEMV_PACKED)
+        if (o->kernel < W8A8_KERNEL_AUTO || o->kernel > W8A8_KERNEL_GEMM_PAIR)
             return fail(W8A8_ERR_INVALID_ARG, "unknown kernel %d", o->kernel);
     }
     return W8A8_OK;
@@ -110,6 +110,8 @@ int dispatch_linear_q(const LinearArgs& a, int kernel, int* device_status, cudaS
         case W8A8_KERNEL_GENERIC: return launch_linear_generic(a, s);
         case W8A8_KERNEL_GEMV: return launch_linear_gemv(a, s);
         case W8A8_KERNEL_GEMM: return launch_linear_gemm(a, device_status, s);
+        case W8A8_KERNEL_GEMM_SINGLE: return launch_linear_gemm(a, device_status, s, 0);
+        case W8A8_KERNEL_GEMM_PAIR: return launch_linear_gemm(a, device_status, s, 1);
         case W8A8_KERNEL_GEMV_TMA: return launch_linear_gemv_tma(a, device_status, s);
         case W8A8_KERNEL_GEMV_PACKED: return launch_linear_gemv_packed(a, device_status, s);
         default: break;

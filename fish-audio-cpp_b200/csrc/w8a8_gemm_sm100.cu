@@ -677,7 +677,7 @@ bool gemm_supports(const LinearArgs& a) {
     return true;
 }
 
-int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t stream) {
+int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t stream, int form) {
     if (!gemm_supports(a)) return fail(W8A8_ERR_UNSUPPORTED, "tcgen05 GEMM does not take this shape");
     CUtensorMap map_x, map_w;
     int rc = make_tensor_map_2d_u8(&map_x, a.Xq, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.M),
@@ -688,12 +688,15 @@ int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t str
     if (rc) return rc;
     int sms = 148, dev = 0;
     if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    // CTA pairs (256-token tiles) once there are enough tokens to fill them (W8A8_GEMM_PAIR=0: never, =1: always)
+    // CTA pairs (256-token tiles) once there are enough tokens to fill them and the groups are long enough for the
+    // tensor pipe to matter: measured a few per cent faster at g = 256 and a few per cent slower at g = 64, where the
+    // promote bounds the kernel and the pair only adds latency between the two CTAs' epilogues and the one issuer
+    // (W8A8_GEMM_PAIR=0: never, =1: always).
     static const int pair_mode = [] {
         const char* v = std::getenv("W8A8_GEMM_PAIR");
         return v ? std::atoi(v) : -1;
     }();
-    const bool pair = pair_mode >= 0 ? pair_mode != 0 : a.M > BM;
+    const bool pair = form >= 0 ? form != 0 : pair_mode >= 0 ? pair_mode != 0 : (a.M > BM && a.g >= 128);
     if (pair) {  // a CTA of a pair loads 128 of the tile's 256 weight rows per box
         rc = make_tensor_map_2d_u8(&map_w, a.W, static_cast<uint64_t>(a.K), static_cast<uint64_t>(a.N),
                                    static_cast<uint64_t>(a.K), BK, BN / 2, 1);

@@ -146,6 +146,7 @@ int launch_tp_allreduce_rowquant(TpState* t, __half* x, const __half* partial, c
                                  __half* normed_out, int8_t* Xq, float* Xs, int* status, cudaStream_t stream);
 // w8a8_gemm_sm100.cu : tcgen05 + TMA.
 bool gemm_supports(const LinearArgs& a);
-int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t s);
+// form: -1 picks between one CTA per tile (0) and a CTA pair per tile (1) by shape
+int launch_linear_gemm(const LinearArgs& a, int* device_status, cudaStream_t s, int form = -1);
 
 }  // namespace w8a8

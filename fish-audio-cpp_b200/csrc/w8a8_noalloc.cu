@@ -89,7 +89,7 @@ int w8a8_linear_static_scratch(const void* W, const void* w_scale, int group_siz
             return fail(W8A8_ERR_INVALID_ARG, "W8A8_EPI_SWIGLU needs N %% 16 == 0 (got %d)", N);
         if (opts->act_mode != W8A8_ACT_PER_TOKEN_GROUP && opts->act_mode != W8A8_ACT_PER_TOKEN)
             return fail(W8A8_ERR_INVALID_ARG, "unknown act_mode %d", opts->act_mode);
-        if (opts->kernel < W8A8_KERNEL_AUTO || opts->kernel > W8A8_KERNEL_GEMV_PACKED)
+        if (opts->kernel < W8A8_KERNEL_AUTO || opts->kernel > W8A8_KERNEL_GEMM_PAIR)
             return fail(W8A8_ERR_INVALID_ARG, "unknown kernel %d", opts->kernel);
         act_mode = opts->act_mode;
         kernel = opts->kernel;

@@ -93,10 +93,12 @@ enum { /* forces a kernel family; default picks by shape */
     W8A8_KERNEL_AUTO = 0,
     W8A8_KERNEL_GENERIC = 1, /* scalar-order SIMT kernel, any shape */
     W8A8_KERNEL_GEMV = 2,    /* M <= 32: warp-MMA weight-streaming kernel, cluster split-K */
-    W8A8_KERNEL_GEMM = 3,    /* tcgen05 + TMA kernel */
+    W8A8_KERNEL_GEMM = 3,    /* tcgen05 + TMA kernel; picks between the two forms below by shape */
     W8A8_KERNEL_GEMV_TMA = 4, /* M <= 32: TMA-fed persistent stream-K kernel over the row-major matrix */
-    W8A8_KERNEL_GEMV_PACKED = 5 /* M <= 32: the same over a weight packed by w8a8_pack_weight (the default
-                                   once the weight is registered) */
+    W8A8_KERNEL_GEMV_PACKED = 5, /* M <= 32: the same over a weight packed by w8a8_pack_weight (the default
+                                    once the weight is registered) */
+    W8A8_KERNEL_GEMM_SINGLE = 6, /* tcgen05 kernel, one CTA per 128-token x 256-row tile */
+    W8A8_KERNEL_GEMM_PAIR = 7    /* tcgen05 kernel, a CTA pair (cta_group::2) per 256-token x 256-row tile */
 };
 
 typedef struct w8a8_linear_opts {

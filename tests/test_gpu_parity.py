@@ -532,19 +532,28 @@ GEMM_SHAPES = [(33, 128, 128, 64), (128, 128, 256, 256), (129, 136, 512, 128), (
                (64, 256, 1024, 64), (257, 128, 640, 640), (1, 128, 128, 128), (500, 16, 256, 64)]
 
 
-@pytest.mark.parametrize("M,N,K,g", GEMM_SHAPES)
-def test_gemm_tcgen05_small_shapes(ctx, oracle, pkg, M, N, K, g):
-    """The tcgen05 + TMA kernel: ragged token and row tails, every group size a multiple of 32 including
-    groups that straddle a 128-byte stage. Groups are added in ascending order exactly like the oracle,
-    so the fp16 output must agree bit for bit."""
-    (X, W, ws, Xq, Xs), Y, P = run_linear(ctx, oracle, M, N, K, g, seed=M + N + K, kernel=pkg.KERNEL_GEMM)
+GEMM_FORMS = ["KERNEL_GEMM_SINGLE", "KERNEL_GEMM_PAIR"]  # one CTA per tile; a CTA pair (cta_group::2) per 256-token tile
+
+
+@pytest.mark.parametrize("form", GEMM_FORMS)
+@pytest.mark.parametrize("M,N,K,g", GEMM_SHAPES + [(640, 520, 768, 256), (385, 2560, 512, 128)])
+def test_gemm_tcgen05_small_shapes(ctx, oracle, pkg, M, N, K, g, form):
+    """The tcgen05 + TMA kernel in both forms: ragged token and row tails (an odd number of 128-token tiles leaves the
+    second CTA of the last pair without rows; N = 520 and 136 end inside a 64-column store panel; N = 72 and 264 are
+    not multiples of 8 ... 16 bytes and take the direct-store epilogue), every group size a multiple of 32 including
+    groups that straddle a 128-byte stage. Groups are added in ascending order exactly like the oracle, so the fp16
+    output must agree bit for bit."""
+    (X, W, ws, Xq, Xs), Y, P = run_linear(ctx, oracle, M, N, K, g, seed=M + N + K, kernel=getattr(pkg, form))
     ctx.check_device_status()
     assert np.array_equal(P, oracle.group_sums(W, Xq, g)), "per-group int32 sums must be bit-exact"
     assert np.array_equal(Y.view(np.uint16), oracle.linear_q(W, ws, Xq, Xs, g).view(np.uint16))
 
 
-def test_gemm_tcgen05_epilogues(ctx, oracle, pkg):
-    M, inter, K, g = 150, 200, 512, 256
+@pytest.mark.parametrize("form", GEMM_FORMS)
+@pytest.mark.parametrize("M,inter", [(150, 200), (300, 328)])
+def test_gemm_tcgen05_epilogues(ctx, oracle, pkg, form, M, inter):
+    K, g = 512, 256
+    kern = getattr(pkg, form)
     rng = np.random.default_rng(29)
     X = synth.activations(rng, M, K)
     wg, wu = synth.weights(rng, inter, K), synth.weights(rng, inter, K)
@@ -552,12 +561,12 @@ def test_gemm_tcgen05_epilogues(ctx, oracle, pkg):
     Wp, Sp = oracle.pack_gate_up(wg, sg, wu, su)
     dX = dev(X)
     dA = torch.empty((M, inter), dtype=torch.float16, device="cuda")
-    ctx.linear(dev(Wp), dev(Sp), g, dX, dA, M, 2 * inter, K, epilogue=pkg.EPI_SWIGLU, kernel=pkg.KERNEL_GEMM)
+    ctx.linear(dev(Wp), dev(Sp), g, dX, dA, M, 2 * inter, K, epilogue=pkg.EPI_SWIGLU, kernel=kern)
     torch.cuda.synchronize()
     assert oracle.ulp_distance_fp16(dA.cpu().numpy(), oracle.linear(Wp, Sp, g, X, epilogue=oracle.EPI_SWIGLU)).max() <= 1
     R = rng.standard_normal((M, inter)).astype(np.float16)
     dR = dev(R)
-    ctx.linear(dev(wg), dev(sg), g, dX, dR, M, inter, K, epilogue=pkg.EPI_RESIDUAL, residual=dR, kernel=pkg.KERNEL_GEMM)
+    ctx.linear(dev(wg), dev(sg), g, dX, dR, M, inter, K, epilogue=pkg.EPI_RESIDUAL, residual=dR, kernel=kern)
     torch.cuda.synchronize()
     want = oracle.linear(wg, sg, g, X, epilogue=oracle.EPI_RESIDUAL, residual=R)
     assert np.array_equal(dR.cpu().numpy().view(np.uint16), want.view(np.uint16))
@@ -569,11 +578,12 @@ PREFILL_CASES = [(name, g, 2048) for name in ("qkv", "o", "gate_up", "down") for
 
 
 @pytest.mark.parametrize("name,g,M", PREFILL_CASES)
-def test_prefill_shapes_full_size(ctx, oracle, name, g, M):
+def test_prefill_shapes_full_size(ctx, oracle, pkg, name, g, M):
     """configs[2], all sixteen cases (four projections x g in {256, 64} x M in {2048, 8192}): the whole GEMM
     runs on the GPU; a random 48-token x 192-row sub-problem is recomputed by the oracle (each output
-    depends only on its own token row and weight row) and must agree bit for bit; two runs of the full
-    problem must agree bit for bit as well."""
+    depends only on its own token row and weight row) and must agree bit for bit; a second run of the full
+    problem, through the form of the kernel that the default did NOT pick (CTA pairs at g = 256, single CTAs at
+    g = 64 by default), must agree with the first bit for bit as well."""
     K, N = synth.PROJECTIONS[name]
     rng = np.random.default_rng(7 + g)
     X = synth.activations(rng, M, K)
@@ -585,7 +595,7 @@ def test_prefill_shapes_full_size(ctx, oracle, name, g, M):
     dX = dev(X)
     ctx.linear(dW, dS, g, dX, dY, M, N, K)
     dY2 = torch.empty_like(dY)
-    ctx.linear(dW, dS, g, dX, dY2, M, N, K)
+    ctx.linear(dW, dS, g, dX, dY2, M, N, K, kernel=pkg.KERNEL_GEMM_SINGLE if g >= 128 else pkg.KERNEL_GEMM_PAIR)
     torch.cuda.synchronize()
     ctx.check_device_status()
     assert torch.equal(dY.view(torch.int16), dY2.view(torch.int16))
@@ -782,9 +792,10 @@ def test_linear_against_reference_kernel(ctx, oracle, M, N, K, g):
         assert exact or exact_alt, "oracle promote order matches neither fma nor mul+add of the reference"
 
 
+@pytest.mark.parametrize("form", GEMM_FORMS)
 @pytest.mark.parametrize("g", [256, 64])
 @pytest.mark.parametrize("wval,qval", [(-128, 127), (127, 127), (-128, -127), (127, -127)])
-def test_gemm_tcgen05_extreme_codes(ctx, oracle, pkg, g, wval, qval):
+def test_gemm_tcgen05_extreme_codes(ctx, oracle, pkg, g, wval, qval, form):
     """Every product at its largest magnitude: a group of 256 sums to 128 * 127 * 256 = 4 161 536, just under the
     2^22 up to which the kernel's integer-add int32 -> fp32 conversion is exact. Sums and fp16 bits must match."""
     M, N, K = 130, 264, 512
@@ -798,7 +809,7 @@ def test_gemm_tcgen05_extreme_codes(ctx, oracle, pkg, g, wval, qval):
     Xs = rng.uniform(1e-3, 4e-2, size=(M, G)).astype(np.float32)
     dP = torch.full((M, N, G), -1, dtype=torch.int32, device="cuda")
     dY = torch.empty((M, N), dtype=torch.float16, device="cuda")
-    ctx.linear_q(dev(W), dev(ws), g, dev(Xq), dev(Xs), dY, M, N, K, dump=dP, kernel=pkg.KERNEL_GEMM)
+    ctx.linear_q(dev(W), dev(ws), g, dev(Xq), dev(Xs), dY, M, N, K, dump=dP, kernel=getattr(pkg, form))
     torch.cuda.synchronize()
     ctx.check_device_status()
     P = oracle.group_sums(W, Xq, g)
