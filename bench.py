@@ -766,8 +766,20 @@ def step_timeline(torch, wl):
         k = inst[per + j]
         name = TRACE_KERNELS.get(k["id"], str(k["id"])) + (f"[N={k['aux']}]" if k["aux"] else "")
         rows.append([name, round(float(np.median(edges[:, j])), 2), round(float(np.median(bodies[:, j])), 2)])
-    return {"per_layer": rows, "layer_us": round(float(np.median(edges, 0).sum() + np.median(bodies, 0).sum()), 2),
-            "columns": ["kernel", "edge_us", "body_us"]}
+    out = {"per_layer": rows, "layer_us": round(float(np.median(edges, 0).sum() + np.median(bodies, 0).sum()), 2),
+           "columns": ["kernel", "edge_us", "body_us"]}
+    import ctypes as C
+
+    from fish_audio_cpp_b200 import capi
+    fn = getattr(capi.load_library(), "w8a8_trace_read_attn_phases", None)
+    if fn is not None:  # phases of the attention launch of the step's last layer, CTA (0, 0, 0), microseconds from entry
+        buf = (C.c_ulonglong * 8)()
+        fn.restype = C.c_int
+        if fn(buf) == 8:
+            names = ["entry", "dependency_wait_returned", "q_and_new_rows_ready", "first_block_in_hand", "blocks_done",
+                     "warps_merged", "cluster_synced", "end"]
+            out["attention_phases_us"] = {n: round((buf[i] - buf[0]) / 1e3, 2) for i, n in enumerate(names)}
+    return out
 
 
 def gemm_timeline(torch, pkg, M=8192, groups=(256, 64)):
@@ -1049,6 +1061,10 @@ def main():
     # The clock record covers everything that runs under load from the first warm-up step on: warm-up, the timed
     # region, the end-to-end region, the dominant kernel timed alone; a short run keeps stepping until the sampler
     # has seen about 1.5 s of load.
+    # All ranks leave set-up together: the first (eager) step of a tensor-parallel stack waits in every exchange for
+    # the peers' rows, and a rank that enters it seconds before a peer has finished packing its weights sits out one
+    # bounded wait per exchange (72 per step, seconds each) before the run gets going.
+    barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
     t_load0 = time.perf_counter()
@@ -1075,9 +1091,17 @@ def main():
         e2e_ms = (time.perf_counter() - t0) * 1e3
     cases = [] if args.no_detail else wl.per_case()
     lin = wl.time_linears() if (args.workload == "decode_stack" and not reference) else None
-    while time.perf_counter() - t_load0 < 1.5:
+    # Keep stepping until the sampler has seen about 1.5 s of load. Every rank must run the SAME number of steps: a
+    # tensor-parallel step that one rank runs alone waits out every one of its exchanges (72 bounded waits of seconds
+    # each) and leaves that rank's exchange epoch ahead of its peers' for good. So the count is agreed first.
+    plan = torch.tensor([max(0.0, 1.5 - (time.perf_counter() - t_load0)), dev_ms / max(args.steps, 1) * 1e-3],
+                        dtype=torch.float64, device="cuda")
+    if dist is not None:
+        dist.all_reduce(plan, op=dist.ReduceOp.MAX)
+    remaining_s, step_s = plan.tolist()
+    for _ in range(int(remaining_s / max(step_s, 1e-5)) + 1 if remaining_s > 0 else 0):
         wl.step()
-        torch.cuda.synchronize()
+    torch.cuda.synchronize()
     clocks = sampler.stop()
     # every rank steps (the tensor-parallel exchange needs all of them); rank 0 reports its own GPU's timeline
     kernel_timeline = None

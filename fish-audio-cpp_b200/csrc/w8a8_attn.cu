@@ -243,6 +243,18 @@ __device__ __forceinline__ void consumer_barrier() {  // the eight consumer warp
 // (possibly before the new rows are there) and the new rows are put over it in shared memory.
 // Without ROPE the new rows were written by the launch before this one, so the sequence's last block is requested
 // only after the dependency wait.
+#ifdef W8A8_TRACE
+// Diagnostic build only: nanosecond stamps of the phases of CTA (0, 0, 0), written by consumer thread 0, kept from
+// the last launch; read out by w8a8_trace_read_attn_phases.
+__device__ unsigned long long g_attn_phase[8];
+#define ATTN_PHASE(i)                                                                     \
+    do {                                                                                  \
+        if (threadIdx.x == 0 && (blockIdx.x | blockIdx.y | blockIdx.z) == 0) g_attn_phase[i] = w8a8::trace::now(); \
+    } while (0)
+#else
+#define ATTN_PHASE(i) do {} while (0)
+#endif
+
 template <bool ROPE>
 __global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_constant__ CUtensorMap map_k,
                                                                const __grid_constant__ CUtensorMap map_v,
@@ -258,6 +270,7 @@ __global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_cons
     __shared__ __align__(16) __half out_s[kQPerKv * kHeadDim];
     __shared__ int s_fail;
     W8A8_TRACE_SCOPE();
+    ATTN_PHASE(0);
     ptx::pdl_launch_dependents();
 
     const int s = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z, S = p.S;
@@ -343,6 +356,7 @@ __global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_cons
         }
         ptx::pdl_wait();
         W8A8_TRACE_WAITED();
+        ATTN_PHASE(1);
         const int new_bi = pos / kBlockTokens;
         if constexpr (ROPE) {
             // six head rows of the new token: the group's four query heads, then its k and its v; a warp per row
@@ -397,6 +411,7 @@ __global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_cons
             }
         }
 
+        ATTN_PHASE(2);  // q (and the new k / v rows) are ready
         float m_run = -1e30f, l_run = 0.0f;
         float o[16][2];  // head g, dims 8 n + 2 t, 8 n + 2 t + 1
 #pragma unroll
@@ -408,6 +423,7 @@ __global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_cons
                 if (lane == 0) { atomicExch(p.status, 810 + st); s_fail = 1; }
                 break;
             }
+            if (li == warp) ATTN_PHASE(3);  // the warp's first block is in shared memory
             const uint32_t ks = ring + st * kStageBytes, vs = ks + kBlkBytes;
             const int tokens = min(kBlockTokens, seq_len - bi * kBlockTokens);
             if (ROPE && bi == new_bi) {  // the new token's rows over whatever the cache held there (lane: 4 dims)
@@ -470,6 +486,7 @@ __global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_cons
             __syncwarp();
             if (lane == 0) ptx::mbar_arrive(&empty_bar[st]);
         }
+        ATTN_PHASE(4);  // the warp's blocks are done
         // the four lanes of a quad hold the same head: their partial denominators add up
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
         l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
@@ -500,8 +517,10 @@ __global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_cons
         }
     }
     // ---- every thread of the cluster (the producer warps included) ----
+    ATTN_PHASE(5);  // warps merged
     cg::cluster_group cluster = cg::this_cluster();
     if (S > 1) cluster.sync(); else __syncthreads();
+    ATTN_PHASE(6);  // every CTA of the cluster has its partial state ready
     // ---- CTA 0 of the cluster merges the S context slices and writes the 4 heads ----
     if (s == 0 && threadIdx.x < kQPerKv * 32) {
         const int hh = threadIdx.x >> 5, d0 = (threadIdx.x & 31) * 4;
@@ -550,6 +569,7 @@ __global__ void __maxnreg__(120) paged_attention_decode_kernel(const __grid_cons
     if (s_fail) {  // a bounded wait ran out: give copies that may still be in flight time to land before the CTA goes
         for (int i = 0; i < 1000; ++i) __nanosleep(1000);
     }
+    ATTN_PHASE(7);
     W8A8_TRACE_END(4u);
 }
 
@@ -667,3 +687,9 @@ int launch_attention(const AttnParams& base, int B, int splits, cudaStream_t str
 }  // namespace w8a8
 
 W8A8_TRACE_READER(attn)
+#ifdef W8A8_TRACE
+extern "C" __attribute__((visibility("default"))) int w8a8_trace_read_attn_phases(unsigned long long* out8) {
+    if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+    return cudaMemcpyFromSymbol(out8, w8a8::g_attn_phase, 8 * sizeof(unsigned long long)) == cudaSuccess ? 8 : -1;
+}
+#endif

@@ -47,7 +47,9 @@ def expand_logits(compact, rows, vocab: int, fill=-np.inf):
 # ---- column-parallel over the vocabulary (tensor parallelism) ----
 # The reference runs on one GPU. Under tensor parallelism the head's rows are independent outputs (each has its own
 # weight scales, and the activation codes are the same on every rank), so a rank computes the logits of its own row
-# range with the same decode kernel and the ranges are concatenated: bit-identical to the single-GPU logits.
+# range with the same decode kernel and the ranges are concatenated. Codes, scales and per-group integer sums are
+# those of the whole head; the fp16 logits agree with a one-launch head up to fp32 re-association (the decode kernel
+# groups the sum along K by how many row tiles a CTA holds, which depends on the number of rows in the launch).
 
 def vocab_shard(vocab: int, world: int, rank: int, unit: int = 16):
     """Row range ``[lo, hi)`` of rank ``rank``: whole units of ``unit`` rows (the packed decode stream's row tile),
