@@ -934,6 +934,17 @@ def extra_metrics(torch, ctx, pk):
     return out
 
 
+def agreed_top_up_steps(torch, dist, remaining_s, step_s, device):
+    """How many more steps every rank runs so that about `remaining_s` more seconds of load are seen: each rank brings
+    its own clock reading and step time, all leave with the same count (the largest remaining time over the largest
+    step time, at least one step if any rank has time left). dist None: a single process."""
+    plan = torch.tensor([max(0.0, remaining_s), step_s], dtype=torch.float64, device=device)
+    if dist is not None:
+        dist.all_reduce(plan, op=dist.ReduceOp.MAX)
+    remaining, step = plan.tolist()
+    return int(remaining / max(step, 1e-5)) + 1 if remaining > 0 else 0
+
+
 def finish(dist, wl):
     """Leaves a multi-rank job without tearing NCCL down: a communicator destroyed while captured graphs
     that used it are alive has hung at exit, so graphs go first and the process exits hard."""
@@ -1094,12 +1105,8 @@ def main():
     # Keep stepping until the sampler has seen about 1.5 s of load. Every rank must run the SAME number of steps: a
     # tensor-parallel step that one rank runs alone waits out every one of its exchanges (72 bounded waits of seconds
     # each) and leaves that rank's exchange epoch ahead of its peers' for good. So the count is agreed first.
-    plan = torch.tensor([max(0.0, 1.5 - (time.perf_counter() - t_load0)), dev_ms / max(args.steps, 1) * 1e-3],
-                        dtype=torch.float64, device="cuda")
-    if dist is not None:
-        dist.all_reduce(plan, op=dist.ReduceOp.MAX)
-    remaining_s, step_s = plan.tolist()
-    for _ in range(int(remaining_s / max(step_s, 1e-5)) + 1 if remaining_s > 0 else 0):
+    for _ in range(agreed_top_up_steps(torch, dist, 1.5 - (time.perf_counter() - t_load0),
+                                       dev_ms / max(args.steps, 1) * 1e-3, "cuda")):
         wl.step()
     torch.cuda.synchronize()
     clocks = sampler.stop()

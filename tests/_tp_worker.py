@@ -72,6 +72,21 @@ def lm_head_worker(rank, world, port, q):
         dist.destroy_process_group()
 
 
+def top_up_worker(rank, world, port, q):
+    """Two benchmark ranks whose clocks disagree on whether the load window is over must still run the same number of
+    further steps (a tensor-parallel step that one rank runs alone waits out every exchange)."""
+    import bench
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        remaining = [0.2, -0.01][rank]   # rank 1 thinks the window is already over
+        step_s = [1e-3, 2e-3][rank]
+        q.put((rank, bench.agreed_top_up_steps(torch, dist, remaining, step_s, "cpu"),
+               bench.agreed_top_up_steps(torch, dist, -1.0, step_s, "cpu")))
+    finally:
+        dist.destroy_process_group()
+
+
 def free_port():
     import socket
     with socket.socket() as s:

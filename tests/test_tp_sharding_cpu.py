@@ -78,3 +78,18 @@ def test_column_parallel_lm_head_with_gloo():
     assert sorted(b for _, _, b in res) == [(0, 112), (112, 213)]
     for rank, same, _ in res:
         assert same, f"rank {rank}: gathered logits must equal the whole head bit for bit"
+
+
+@pytest.mark.timeout(120)
+def test_benchmark_ranks_agree_on_the_top_up_step_count():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_tp_worker.top_up_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=100) for _ in procs]
+    for p in procs:
+        p.join(timeout=30)
+    # 0.2 s left on the slower clock, 2 ms per step on the slower rank: 101 steps on both; nobody has time left: none
+    assert sorted(res) == [(0, 101, 0), (1, 101, 0)]
