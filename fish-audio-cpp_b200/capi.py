@@ -393,3 +393,71 @@ class Context:
                                                        _stream(stream), buf, 512)
         if rc:
             raise RuntimeError(buf.value.decode())
+
+
+# ---- native reader of the reference's .bin container (include/w8a8_container.h; host memory only) ----
+class TensorInfo(C.Structure):
+    _fields_ = [("name", C.c_char_p), ("dtype", C.c_int), ("ndim", C.c_int), ("shape", C.c_int64 * 8),
+                ("offset", C.c_uint64), ("nbytes", C.c_uint64), ("data", C.c_void_p)]
+
+
+CONTAINER_EXPORTS = ["w8a8_container_open", "w8a8_container_close", "w8a8_container_count",
+                     "w8a8_container_data_section_offset", "w8a8_container_tensor", "w8a8_container_find",
+                     "w8a8_container_group_size", "w8a8_container_pin"]
+
+
+def _check(rc, where):
+    if rc != 0:
+        raise W8A8Error(rc, where, load_library().w8a8_last_error().decode())
+
+
+class NativeContainer:
+    """The library's own reader of a ``.bin`` file (mapped read-only; ``bytes_of`` copies out of the mapping)."""
+
+    def __init__(self, path):
+        lib = load_library()
+        P, I = C.c_void_p, C.c_int
+        lib.w8a8_container_open.restype, lib.w8a8_container_open.argtypes = I, [C.c_char_p, C.POINTER(P)]
+        lib.w8a8_container_close.restype, lib.w8a8_container_close.argtypes = I, [P]
+        lib.w8a8_container_count.restype, lib.w8a8_container_count.argtypes = I, [P]
+        lib.w8a8_container_data_section_offset.restype = C.c_uint64
+        lib.w8a8_container_data_section_offset.argtypes = [P]
+        lib.w8a8_container_tensor.restype, lib.w8a8_container_tensor.argtypes = I, [P, I, C.POINTER(TensorInfo)]
+        lib.w8a8_container_find.restype, lib.w8a8_container_find.argtypes = I, [P, C.c_char_p]
+        lib.w8a8_container_group_size.restype = I
+        lib.w8a8_container_group_size.argtypes = [P, C.c_char_p, C.POINTER(I)]
+        lib.w8a8_container_pin.restype, lib.w8a8_container_pin.argtypes = I, [P]
+        self._lib, self._h = lib, P()
+        _check(lib.w8a8_container_open(str(path).encode(), C.byref(self._h)), "w8a8_container_open")
+
+    def close(self):
+        if self._h:
+            self._lib.w8a8_container_close(self._h)
+            self._h = C.c_void_p()
+
+    def __len__(self):
+        return self._lib.w8a8_container_count(self._h)
+
+    @property
+    def data_section_offset(self):
+        return self._lib.w8a8_container_data_section_offset(self._h)
+
+    def tensor(self, index):
+        info = TensorInfo()
+        _check(self._lib.w8a8_container_tensor(self._h, index, C.byref(info)), "w8a8_container_tensor")
+        return info
+
+    def find(self, name):
+        return self._lib.w8a8_container_find(self._h, name.encode())
+
+    def group_size(self, weight):
+        g = C.c_int()
+        _check(self._lib.w8a8_container_group_size(self._h, weight.encode(), C.byref(g)), "w8a8_container_group_size")
+        return g.value
+
+    def pin(self):
+        _check(self._lib.w8a8_container_pin(self._h), "w8a8_container_pin")
+
+    def bytes_of(self, index):
+        info = self.tensor(index)
+        return C.string_at(info.data, info.nbytes)

@@ -128,3 +128,104 @@ def test_writer_limits(tmp_path):
     assert c.entries["bf"].dtype_val == ct.DTYPE_BF16 and c.get("bf").tolist() == [0, 1, 2, 3]
     ct.write_container(tmp_path / "empty.bin", {})
     assert ct.Container(tmp_path / "empty.bin").names() == []
+
+
+# ---------------------------------------------------------------- the library's native reader (include/w8a8_container.h)
+@pytest.fixture(scope="module")
+def native(pkg):
+    from fish_audio_cpp_b200 import capi
+
+    c = capi.NativeContainer(GOLDEN / "container_small.bin")
+    yield c
+    c.close()
+
+
+def test_native_reader_sees_what_the_reference_wrote(native, golden):
+    """The C ABI reader over the file the reference's tools wrote: same tensors in the same order, same element
+    types, shapes, offsets and bytes as the Python reader and as the arrays the fixture was made from."""
+    c, want = golden
+    assert len(native) == len(want.files) and native.data_section_offset == 12 + 344 * len(want.files)
+    codes = {np.dtype("<f4"): 0, np.dtype("<f2"): 1, np.dtype("i1"): 3}
+    for i, name in enumerate(want.files):
+        info = native.tensor(i)
+        assert info.name.decode() == name and native.find(name) == i
+        assert info.dtype == codes[want[name].dtype] and info.ndim == want[name].ndim
+        assert tuple(info.shape[:info.ndim]) == want[name].shape and not any(info.shape[info.ndim:8])
+        e = c.entries[name]
+        assert (info.offset, info.nbytes) == (e.data_offset, e.data_size) and info.offset % 256 == 0
+        assert native.bytes_of(i) == want[name].tobytes()
+    assert native.find("nope") == -1
+
+
+def test_native_reader_loader_conventions(native, golden, pkg):
+    c, _ = golden
+    for name in c.w8a8_linears():  # infer_group_size_from_scale, dual_ar_engine.cc:17-24
+        assert native.group_size(name) == c.group_size(name), name
+    assert native.group_size(P0 + "feed_forward.w2.weight") == 300 and native.group_size(P0 + "attention.wo.weight") == 64
+    with pytest.raises(pkg.W8A8Error, match="not an int8 tensor with a _scale"):
+        native.group_size(P0 + "attention_norm.weight")
+    with pytest.raises(pkg.W8A8Error, match="Tensor not found"):
+        native.group_size("nope")
+    with pytest.raises(pkg.W8A8Error):
+        native.tensor(len(native))
+
+
+def test_native_reader_refuses_what_the_python_reader_refuses(tmp_path, pkg):
+    from fish_audio_cpp_b200 import capi
+
+    first = 12
+    cases = [("magic.bin", 0, struct.pack("<I", 0x12345678), "Invalid magic: 0x12345678, expected 0x46495348"),
+             ("version.bin", 4, struct.pack("<I", 2), "Unsupported version: 2"),
+             ("offset.bin", first + 256 + 8 + 64, struct.pack("<Q", 1 << 40), "outside the file"),
+             ("unaligned.bin", first + 256 + 8 + 64, struct.pack("<Q", 5121), "unaligned"),
+             ("size.bin", first + 256 + 8 + 64 + 8, struct.pack("<Q", 3), "do not match its shape"),
+             ("dtype.bin", first + 256, struct.pack("<I", 9), "unknown dtype 9"),
+             ("ndim.bin", first + 256 + 4, struct.pack("<I", 9), "9 dimensions"),
+             ("negative.bin", first + 256 + 8, struct.pack("<q", -4), "negative extent"),
+             ("huge.bin", first + 256 + 8, struct.pack("<q", 1 << 62), "overflow|do not match")]
+    for fname, at, patch, msg in cases:
+        with pytest.raises(pkg.W8A8Error, match=msg) as e:
+            capi.NativeContainer(_patched(tmp_path, fname, at, patch))
+        assert e.value.status == 1  # W8A8_ERR_INVALID_ARG
+    short = tmp_path / "short.bin"
+    short.write_bytes((GOLDEN / "container_small.bin").read_bytes()[:100])
+    with pytest.raises(pkg.W8A8Error, match="do not fit"):
+        capi.NativeContainer(short)
+    tiny = tmp_path / "tiny.bin"
+    tiny.write_bytes(b"FISH")
+    with pytest.raises(pkg.W8A8Error, match="preamble"):
+        capi.NativeContainer(tiny)
+    with pytest.raises(pkg.W8A8Error, match="Failed to open model file"):
+        capi.NativeContainer(tmp_path / "missing.bin")
+
+
+def test_native_reader_reads_a_sidecar_written_in_the_same_format(tmp_path, pkg):
+    """What write_container writes (the packed sidecar uses it) is a file the native reader takes: uint8 images come
+    back as int8 tensors of the same bytes, names of up to 255 bytes survive."""
+    from fish_audio_cpp_b200 import capi
+
+    rng = np.random.default_rng(1)
+    tensors = {"a" * 255: rng.integers(0, 256, (3, 5), dtype=np.uint8), "w_packed_meta": np.array([16, 256, 64], np.float32),
+               "h": rng.standard_normal((2, 3, 4)).astype(np.float16)}
+    path = tmp_path / "sidecar.bin"
+    ct.write_container(path, tensors)
+    c = capi.NativeContainer(path)
+    try:
+        assert len(c) == 3
+        for i, (name, arr) in enumerate(tensors.items()):
+            info = c.tensor(i)
+            assert info.name.decode() == name and tuple(info.shape[:info.ndim]) == arr.shape
+            assert c.bytes_of(i) == arr.tobytes()
+        assert c.tensor(0).dtype == 3
+    finally:
+        c.close()
+
+
+def test_native_reader_pin_without_a_device_is_an_error_not_a_crash(native, pkg):
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a device is present: pinning would succeed")
+    with pytest.raises(pkg.W8A8Error) as e:
+        native.pin()
+    assert e.value.status == 3  # W8A8_ERR_CUDA

@@ -24,6 +24,10 @@ def test_header_symbols_are_exported(pkg):
     from fish_audio_cpp_b200 import capi
 
     assert set(capi.EXPORTS) <= set(names)
+    host = declared_symbols(ROOT / "include" / "w8a8_container.h")
+    assert len(host) == 8 and set(capi.CONTAINER_EXPORTS) == set(host)
+    for n in host:
+        assert hasattr(lib, n), f"{n} declared in include/w8a8_container.h but not exported"
 
 
 def test_shim_exports_reference_signatures(pkg):
